@@ -1,0 +1,90 @@
+// C++ interface of the B200 (sm_100a) implementation of sphericart's CUDA calculators.
+//
+// Drop-in for the reference header sphericart/include/sphericart_cuda.hpp:33-187: the same
+// namespace, class names, constructor and compute / compute_with_gradients /
+// compute_with_hessians signatures, and the same object size and member offsets (the
+// reference's bindings allocate these objects themselves: sphericart-torch/src/torch.cpp:340-349,
+// sphericart-jax/src/sphericart_jax_cuda.cpp:25-40), so code compiled against either header links
+// against this library. One method is added, compute_vjp, which nothing in the reference calls.
+//
+// Contract of every compute call (reference: sphericart/src/sphericart_cuda.cpp:74-160):
+//  * xyz, sph, dsph, ddsph are DEVICE pointers to caller-owned contiguous buffers of
+//    n_samples x 3, n_samples x (l_max+1)^2, n_samples x 3 x (l_max+1)^2 and
+//    n_samples x 3 x 3 x (l_max+1)^2 elements; column (l, m) sits at l*l + l + m.
+//  * cuda_stream is a cudaStream_t cast to void* (nullptr = default stream). The call only
+//    enqueues work; it never synchronises and never allocates or frees the caller's buffers.
+//  * The work runs on the device that owns xyz; the caller's current device is restored.
+//  * n_samples == 0 returns at once, even with null outputs. A null sph (or a null dsph / ddsph
+//    when that output was asked for) and every CUDA failure throw std::runtime_error.
+//  * Calls on one calculator may come from several threads and streams at once.
+#ifndef SPHERICART_CUDA_HPP
+#define SPHERICART_CUDA_HPP
+
+#include <cstddef>
+#include <cstdint>
+#include <mutex>
+
+namespace sphericart {
+namespace cuda {
+
+/// Real spherical harmonics Y_l^m(r/|r|) for l <= l_max, T = float or double.
+template <typename T> class SphericalHarmonics {
+  public:
+    SphericalHarmonics(size_t l_max);
+    ~SphericalHarmonics();
+
+    /// Values only.
+    void compute(const T* xyz, const size_t n_samples, T* sph, void* cuda_stream = nullptr);
+
+    /// Values and gradients d/dx, d/dy, d/dz.
+    void compute_with_gradients(const T* xyz, const size_t n_samples, T* sph, T* dsph, void* cuda_stream = nullptr);
+
+    /// Values, gradients and Hessians (all nine second derivatives, both symmetric halves).
+    void compute_with_hessians(
+        const T* xyz, const size_t n_samples, T* sph, T* dsph, T* ddsph, void* cuda_stream = nullptr
+    );
+
+    /// Fused vector-Jacobian product (no counterpart in the reference's C++ classes):
+    /// xyz_grad[i][a] = sum_k sph_grad[i][k] * dsph[i][a][k], with dsph never written to memory.
+    /// sph_grad is n_samples x (l_max+1)^2, xyz_grad is n_samples x 3, both device pointers.
+    void compute_vjp(const T* xyz, const size_t n_samples, const T* sph_grad, T* xyz_grad, void* cuda_stream = nullptr);
+
+    template <typename U> friend class SolidHarmonics;
+
+  private:
+    // The member list mirrors the reference class so that sizeof and offsets agree. Members this
+    // implementation has no use for are kept as placeholders.
+    size_t l_max;
+    size_t nprefactors;            // 2 * (l_max+1)(l_max+2)/2 table entries
+    bool normalized;               // true: spherical harmonics, false: solid harmonics
+    T* prefactors_cpu = nullptr;   // host copy of the F and K tables
+    T* prefactors_cuda = nullptr;  // opaque handle to library-owned state (per-device tables, plans)
+    int device_count = 0;
+    int64_t CUDA_GRID_DIM_X_ = 8;  // placeholder
+    int64_t CUDA_GRID_DIM_Y_ = 8;  // placeholder
+    bool cached_compute_with_gradients = false;  // placeholder
+    bool cached_compute_with_hessian = false;    // placeholder
+    int64_t _current_shared_mem_allocation = 0;  // placeholder
+
+    void compute_internal(
+        const T* xyz,
+        const size_t n_samples,
+        bool compute_with_gradients,
+        bool compute_with_hessian,
+        T* sph,
+        T* dsph,
+        T* ddsph,
+        void* cuda_stream
+    );
+};
+
+/// Solid harmonics r^l Y_l^m (homogeneous polynomials of x, y, z): same interface.
+template <typename T> class SolidHarmonics : public SphericalHarmonics<T> {
+  public:
+    SolidHarmonics(size_t l_max);
+};
+
+}  // namespace cuda
+}  // namespace sphericart
+
+#endif

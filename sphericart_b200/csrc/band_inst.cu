@@ -1,0 +1,62 @@
+// Instantiates the band kernels for one (type, lanes-per-point) pair: compile with
+//   -DSPH_T=float|double -DSPH_G=1|2|4|8|16|32
+#include "sph_band.cuh"
+#include "sph_launch.hpp"
+
+#include <atomic>
+
+#ifndef SPH_T
+#error "compile with -DSPH_T=float or -DSPH_T=double"
+#endif
+#ifndef SPH_G
+#error "compile with -DSPH_G=<1,2,4,8,16,32>"
+#endif
+
+namespace sph_b200 {
+
+namespace {
+
+template <typename T, int LEVEL, bool NORM, int G, bool VJP>
+cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    auto kernel = sph_band_kernel<T, LEVEL, NORM, G, VJP>;
+    // shared memory differs between calculators, so the occupancy query is not cached by kernel
+    // alone; it is cheap next to the work these kernels do per launch.
+    const int max_blocks = persistent_grid(reinterpret_cast<const void*>(kernel), a.warps * 32, a.smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    constexpr int P = 32 / G;
+    const long long ngroups = (a.n + P - 1) / P;
+    const long long want = (ngroups + a.warps - 1) / a.warps;
+    const int grid = int(want < max_blocks ? want : max_blocks);
+    BandArgs<T> k{a.xyz, a.n,      a.sph,       a.dsph,        a.ddsph, a.sph_grad, a.xyz_grad,
+                  a.d_tables, a.d_plan, a.l_max, a.plan_ints, a.image_elems};
+    kernel<<<grid, a.warps * 32, a.smem, stream>>>(k);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+template <typename T, int G>
+cudaError_t BandLaunch<T, G>::run(int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
+                                  cudaStream_t stream) {
+    if (vjp) {
+        return normalized ? launch_band<T, 1, true, G, true>(a, device, stream)
+                          : launch_band<T, 1, false, G, true>(a, device, stream);
+    }
+    switch (level) {
+        case 0:
+            return normalized ? launch_band<T, 0, true, G, false>(a, device, stream)
+                              : launch_band<T, 0, false, G, false>(a, device, stream);
+        case 1:
+            return normalized ? launch_band<T, 1, true, G, false>(a, device, stream)
+                              : launch_band<T, 1, false, G, false>(a, device, stream);
+        case 2:
+            return normalized ? launch_band<T, 2, true, G, false>(a, device, stream)
+                              : launch_band<T, 2, false, G, false>(a, device, stream);
+        default:
+            return cudaErrorInvalidValue;
+    }
+}
+
+template struct BandLaunch<SPH_T, SPH_G>;
+
+}  // namespace sph_b200

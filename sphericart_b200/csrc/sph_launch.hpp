@@ -1,0 +1,56 @@
+// Host-side launch interface between the calculator classes (sphericart_cuda.cu) and the
+// translation units that instantiate the kernels (tile_inst.cu, band_inst.cu, each compiled
+// several times with different -D settings so the build parallelises).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace sph_b200 {
+
+constexpr int TILE_LMAX = 8;        // compile-time tile kernels cover l_max 0..8
+constexpr int MAX_DEVICES = 64;
+
+// Largest 32-point tile image a tile kernel is used for; larger cases go to the band kernel.
+constexpr size_t TILE_SMEM_LIMIT = 100 * 1024;
+
+// Number of CTAs that keep every SM of `device` full for a persistent launch of `kernel` with
+// the given block size and dynamic shared memory (also raises the kernel's dynamic shared
+// memory limit). Results are cached by the callers.
+int persistent_grid(const void* kernel, int block, size_t smem, int device);
+
+// Tile kernels, l_max = LMAX known at compile time. host_tables = F then K (n_table each).
+template <typename T, int LMAX> struct TileLaunch {
+    static size_t smem_per_warp(int level);
+    static cudaError_t forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
+                               const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream);
+    static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
+                           const T* host_tables, int warps, int device, cudaStream_t stream);
+};
+
+// Band kernels, run-time l_max. G lanes per point.
+template <typename T> struct BandLaunchArgs {
+    const T* xyz;
+    long long n;
+    T* sph;
+    T* dsph;
+    T* ddsph;
+    const T* sph_grad;
+    T* xyz_grad;
+    const T* d_tables;
+    const int* d_plan;
+    int l_max;
+    int plan_ints;
+    int image_elems;
+    int warps;
+    size_t smem;
+};
+
+template <typename T, int G> struct BandLaunch {
+    // level 0..2 forward, or vjp
+    static cudaError_t run(int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
+                           cudaStream_t stream);
+};
+
+}  // namespace sph_b200

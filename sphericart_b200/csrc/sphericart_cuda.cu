@@ -1,0 +1,584 @@
+// Host side of the library: the sphericart::cuda calculator classes and the C ABI.
+//
+// Mirrors the behaviour of sphericart/src/sphericart_cuda.cpp:40-196 (argument checks, device
+// follows the xyz pointer, lazy per-device state) and sphericart/src/sphericart-capi.cpp:637-876
+// (C wrappers), with statically compiled sm_100a kernels instead of run-time compilation.
+// There is deliberately no CPU code path: without a usable CUDA device every call fails.
+#include "sphericart_b200.h"
+#include "sphericart_cuda.hpp"
+
+#include "sph_core.cuh"
+#include "sph_launch.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace sph_b200 {
+
+namespace {
+
+void check(cudaError_t status, const char* what) {
+    if (status != cudaSuccess) {
+        throw std::runtime_error(std::string("sphericart::cuda: ") + what + " failed: " + cudaGetErrorString(status));
+    }
+}
+
+// Development knob, read once: an integer environment variable or a default.
+int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    if (v == nullptr || *v == '\0') return fallback;
+    return std::atoi(v);
+}
+
+struct DeviceProps {
+    bool known = false;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+};
+std::mutex g_props_mutex;
+DeviceProps g_props[MAX_DEVICES];
+
+const DeviceProps& device_props(int device) {
+    std::lock_guard<std::mutex> lock(g_props_mutex);
+    DeviceProps& p = g_props[device];
+    if (!p.known) {
+        int v = 0;
+        check(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+        p.sm_count = v;
+        check(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, device), "cudaDeviceGetAttribute");
+        p.smem_optin = size_t(v);
+        p.known = true;
+    }
+    return p;
+}
+
+}  // namespace
+
+int persistent_grid(const void* kernel, int block, size_t smem, int device) {
+    const DeviceProps& props = device_props(device);
+    if (smem > props.smem_optin) return 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return per_sm * props.sm_count;
+}
+
+// Prefactor tables in the working precision, built with the recipe of the reference
+// (sphericart/include/templates.hpp:54-97) so that both sides start from the same constants:
+// F[l][m] = (-1)^m sqrt((2l+1)/(2 pi) (l-m)!/(l+m)!) by iterated products, with 1/sqrt(2) folded
+// into m = 0; K[l][l] = Q_l^l = -(2l-1) K[l-1][l-1], K[l][m<l] = -1/((l+m+1)(l-m)).
+template <typename T> void build_tables(int l_max, T* out) {
+    const int nq = n_table(l_max);
+    T* F = out;
+    T* K = out + nq;
+    const T pi = static_cast<T>(3.141592653589793238462643383279502884L);
+    const T inv_sqrt_two = static_cast<T>(0.707106781186547524400844362104849039L);
+    for (int l = 0; l <= l_max; ++l) {
+        T acc = (2 * l + 1) / (2 * pi);
+        F[tri(l, 0)] = std::sqrt(acc) * inv_sqrt_two;
+        for (int m = 1; m <= l; ++m) {
+            acc *= static_cast<T>(1.0) / (l * (l + 1) + m * (1 - m));
+            F[tri(l, m)] = (m % 2 == 0) ? std::sqrt(acc) : -std::sqrt(acc);
+        }
+    }
+    K[0] = 1;
+    for (int l = 1; l <= l_max; ++l) {
+        K[tri(l, l)] = -(2 * l - 1) * K[tri(l - 1, l - 1)];
+        for (int m = l - 1; m >= 0; --m) K[tri(l, m)] = static_cast<T>(-1.0) / ((l + m + 1) * (l - m));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Band-kernel plan: lanes per point, bands of degrees, per-lane channel lists.
+struct BandPlan {
+    int lanes = 1;               // G
+    int warps = 1;               // warps per CTA
+    int image_elems = 0;         // per-warp image, elements of T
+    size_t smem = 0;             // dynamic shared memory per CTA
+    std::vector<int> ints;       // device plan (see sph_band.cuh)
+};
+
+// kind: 0..2 = forward level, 3 = VJP.
+BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
+    const int L = l_max;
+    const int ny = n_columns(L);
+    const int nq = n_table(L);
+    const bool vjp = kind == 3;
+    const int ncomp = vjp ? 1 : level_components(kind);
+    const size_t row_bytes = size_t(ncomp) * ny * elem;  // one point's image (VJP: its sph_grad row)
+    const size_t table_bytes = 2 * size_t(nq) * elem;
+
+    // lanes per point: the smallest power of two whose 32/G-point image stays within the
+    // per-warp budget, but never more lanes than there are channels worth sharing
+    const size_t budget = size_t(env_int("SPH_B200_BAND_IMAGE_KB", 64)) * 1024;
+    int G = 1;
+    while (G < 32 && size_t(32 / G) * row_bytes > budget) G *= 2;
+    const int forced = env_int("SPH_B200_BAND_LANES", 0);
+    if (forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16 || forced == 32) G = forced;
+    const int P = 32 / G;
+
+    // bands: everything in one band when a point's rows fit, else consecutive degrees per band
+    const size_t fixed = table_bytes + 4096;  // tables, plan, slack
+    const size_t csz_bytes = size_t(P) * 3 * (L + 1) * elem;
+    const size_t image_limit = smem_limit > fixed + csz_bytes ? smem_limit - fixed - csz_bytes : 0;
+    std::vector<std::pair<int, int>> bands;
+    if (size_t(P) * row_bytes <= image_limit || vjp) {
+        bands.push_back({0, L});
+    } else {
+        const size_t band_budget = std::min(image_limit, size_t(96) * 1024);
+        int lo = 0;
+        while (lo <= L) {
+            int hi = lo;
+            while (hi + 1 <= L &&
+                   size_t(P) * ncomp * size_t((hi + 2) * (hi + 2) - lo * lo) * elem <= band_budget) {
+                ++hi;
+            }
+            bands.push_back({lo, hi});
+            lo = hi + 1;
+        }
+    }
+
+    BandPlan plan;
+    plan.lanes = G;
+    int max_cols = 0;
+    for (auto& b : bands) max_cols = std::max(max_cols, (b.second + 1) * (b.second + 1) - b.first * b.first);
+    plan.image_elems = vjp ? P * ny : P * ncomp * max_cols;
+
+    // longest-first greedy deal of the channels l >= 2 of each band to the G lanes
+    std::vector<std::vector<std::vector<int>>> lists(bands.size(), std::vector<std::vector<int>>(G));
+    std::vector<int> band_steps(bands.size(), 0);
+    size_t slots = 1;
+    for (size_t b = 0; b < bands.size(); ++b) {
+        std::vector<int> load(G, 0);
+        for (int l = bands[b].second; l >= std::max(2, bands[b].first); --l) {
+            const int lane = int(std::min_element(load.begin(), load.end()) - load.begin());
+            lists[b][lane].push_back(l);
+            load[lane] += l + 1;
+        }
+        band_steps[b] = *std::max_element(load.begin(), load.end());
+        for (int g = 0; g < G; ++g) slots = std::max(slots, lists[b][g].size() + 1);
+    }
+    plan.ints.push_back(int(bands.size()));
+    plan.ints.push_back(int(slots));
+    for (size_t b = 0; b < bands.size(); ++b) {
+        plan.ints.push_back(bands[b].first);
+        plan.ints.push_back(bands[b].second);
+        plan.ints.push_back(band_steps[b]);
+        for (int g = 0; g < G; ++g) {
+            for (size_t s = 0; s < slots; ++s) plan.ints.push_back(s < lists[b][g].size() ? lists[b][g][s] : -1);
+        }
+    }
+
+    // warps per CTA: as many as fit next to the shared tables, at most 4
+    const size_t per_warp = csz_bytes + size_t(plan.image_elems) * elem;
+    const size_t plan_bytes = plan.ints.size() * sizeof(int);
+    int warps = 4;
+    const int forced_warps = env_int("SPH_B200_BAND_WARPS", 0);
+    if (forced_warps >= 1 && forced_warps <= 4) warps = forced_warps;
+    while (warps > 1 && table_bytes + plan_bytes + warps * per_warp > smem_limit) --warps;
+    // prefer a CTA size that packs the SM: with W warps per CTA, floor(limit / cta) CTAs fit
+    if (forced_warps == 0) {
+        int best = warps;
+        size_t best_warps_per_sm = 0;
+        for (int w = warps; w >= 1; --w) {
+            const size_t cta = table_bytes + plan_bytes + w * per_warp + 1024;
+            const size_t n_cta = std::min<size_t>(32, (smem_limit + 1024) / cta);
+            if (n_cta * w > best_warps_per_sm) {
+                best_warps_per_sm = n_cta * w;
+                best = w;
+            }
+        }
+        warps = best;
+    }
+    plan.warps = warps;
+    plan.smem = table_bytes + plan_bytes + warps * per_warp;
+    return plan;
+}
+
+// Library-owned state of one calculator, reached through the class's prefactors_cuda slot.
+template <typename T> struct CalculatorState {
+    std::mutex mutex;
+    BandPlan plans[4];
+    bool plan_ready[4] = {false, false, false, false};
+    struct PerDevice {
+        T* tables = nullptr;
+        int* plan[4] = {nullptr, nullptr, nullptr, nullptr};
+    };
+    PerDevice dev[MAX_DEVICES];
+};
+
+template <typename T>
+void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int kind, int device, size_t smem_limit,
+                    const BandPlan*& plan, const T*& d_tables, const int*& d_plan) {
+    std::lock_guard<std::mutex> lock(st.mutex);
+    if (!st.plan_ready[kind]) {
+        st.plans[kind] = make_band_plan(l_max, kind, sizeof(T), smem_limit);
+        st.plan_ready[kind] = true;
+    }
+    auto& d = st.dev[device];
+    if (d.tables == nullptr) {
+        const size_t bytes = 2 * size_t(n_table(l_max)) * sizeof(T);
+        check(cudaMalloc(reinterpret_cast<void**>(&d.tables), bytes), "cudaMalloc(prefactors)");
+        check(cudaMemcpy(d.tables, host_tables, bytes, cudaMemcpyHostToDevice), "cudaMemcpy(prefactors)");
+    }
+    if (d.plan[kind] == nullptr) {
+        const size_t bytes = st.plans[kind].ints.size() * sizeof(int);
+        check(cudaMalloc(reinterpret_cast<void**>(&d.plan[kind]), bytes), "cudaMalloc(plan)");
+        check(cudaMemcpy(d.plan[kind], st.plans[kind].ints.data(), bytes, cudaMemcpyHostToDevice), "cudaMemcpy(plan)");
+    }
+    plan = &st.plans[kind];
+    d_tables = d.tables;
+    d_plan = d.plan[kind];
+}
+
+// RAII: run on the device that owns `ptr`, restore the caller's device afterwards.
+struct DeviceScope {
+    int previous = -1;
+    int device = -1;
+    explicit DeviceScope(const void* ptr) {
+        cudaPointerAttributes attr;
+        check(cudaPointerGetAttributes(&attr, ptr), "cudaPointerGetAttributes");
+        if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) {
+            throw std::runtime_error("sphericart::cuda: xyz is not a device pointer");
+        }
+        device = attr.device;
+        check(cudaGetDevice(&previous), "cudaGetDevice");
+        if (device < 0 || device >= MAX_DEVICES) throw std::runtime_error("sphericart::cuda: unsupported device index");
+        if (previous != device) check(cudaSetDevice(device), "cudaSetDevice");
+    }
+    ~DeviceScope() {
+        if (previous != device && previous >= 0) cudaSetDevice(previous);
+    }
+};
+
+template <typename T> bool aligned16(const T* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
+    static size_t smem_per_warp(int l_max, int level) {
+        if (l_max == LMAX) return TileLaunch<T, LMAX>::smem_per_warp(level);
+        if constexpr (LMAX > 0) return TileDispatch<T, LMAX - 1>::smem_per_warp(l_max, level);
+        return 0;
+    }
+    static cudaError_t forward(int l_max, int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
+                               T* ddsph, const T* tables, int warps, bool use_bulk, int device, cudaStream_t stream) {
+        if (l_max == LMAX)
+            return TileLaunch<T, LMAX>::forward(level, normalized, xyz, n, sph, dsph, ddsph, tables, warps, use_bulk,
+                                                device, stream);
+        if constexpr (LMAX > 0)
+            return TileDispatch<T, LMAX - 1>::forward(l_max, level, normalized, xyz, n, sph, dsph, ddsph, tables, warps,
+                                                      use_bulk, device, stream);
+        return cudaErrorInvalidValue;
+    }
+    static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
+                           const T* tables, int warps, int device, cudaStream_t stream) {
+        if (l_max == LMAX)
+            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, device, stream);
+        if constexpr (LMAX > 0)
+            return TileDispatch<T, LMAX - 1>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, warps, device,
+                                                  stream);
+        return cudaErrorInvalidValue;
+    }
+};
+
+template <typename T>
+cudaError_t band_dispatch(int lanes, int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
+                          cudaStream_t stream) {
+    switch (lanes) {
+        case 1: return BandLaunch<T, 1>::run(level, vjp, normalized, a, device, stream);
+        case 2: return BandLaunch<T, 2>::run(level, vjp, normalized, a, device, stream);
+        case 4: return BandLaunch<T, 4>::run(level, vjp, normalized, a, device, stream);
+        case 8: return BandLaunch<T, 8>::run(level, vjp, normalized, a, device, stream);
+        case 16: return BandLaunch<T, 16>::run(level, vjp, normalized, a, device, stream);
+        case 32: return BandLaunch<T, 32>::run(level, vjp, normalized, a, device, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// Warps per CTA for a tile kernel: keep a CTA's images within ~48 KB so several CTAs share an SM.
+int tile_warps(size_t smem_per_warp) {
+    const int forced = env_int("SPH_B200_TILE_WARPS", 0);
+    if (forced >= 1 && forced <= 8) return forced;
+    const size_t w = smem_per_warp == 0 ? 8 : (48 * 1024) / smem_per_warp;
+    return int(std::min<size_t>(8, std::max<size_t>(1, w)));
+}
+
+// kind 0..2: forward level; 3: VJP (sph = sph_grad in, dsph = xyz_grad out).
+template <typename T>
+void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T>& st, int kind, const T* xyz,
+         size_t n_samples, T* sph, T* dsph, T* ddsph, const T* sph_grad, T* xyz_grad, void* cuda_stream) {
+    const int l_max = int(l_max_);
+    const long long n = (long long)n_samples;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    DeviceScope scope(xyz);
+    const DeviceProps& props = device_props(scope.device);
+    const bool vjp = kind == 3;
+    const bool force_band = env_int("SPH_B200_FORCE_BAND", 0) != 0;
+
+    if (l_max <= TILE_LMAX && !force_band) {
+        const size_t per_warp = vjp ? size_t(32) * n_columns(l_max) * sizeof(T)
+                                    : TileDispatch<T>::smem_per_warp(l_max, kind);
+        if (vjp) {
+            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, tile_warps(per_warp),
+                                       scope.device, stream),
+                  "tile VJP kernel launch");
+            return;
+        }
+        if (per_warp <= TILE_SMEM_LIMIT) {
+            bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
+            if (env_int("SPH_B200_NO_BULK", 0) != 0) use_bulk = false;
+            check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables,
+                                           tile_warps(per_warp), use_bulk, scope.device, stream),
+                  "tile kernel launch");
+            return;
+        }
+    }
+
+    const BandPlan* plan = nullptr;
+    const T* d_tables = nullptr;
+    const int* d_plan = nullptr;
+    band_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, plan, d_tables, d_plan);
+    if (plan->smem > props.smem_optin) {
+        throw std::runtime_error("sphericart::cuda: l_max is too large for this device's shared memory");
+    }
+    BandLaunchArgs<T> a{xyz,      n,      sph,   dsph,           ddsph,           sph_grad,         xyz_grad,
+                        d_tables, d_plan, l_max, int(plan->ints.size()), plan->image_elems, plan->warps, plan->smem};
+    check(band_dispatch<T>(plan->lanes, vjp ? 1 : kind, vjp, normalized, a, scope.device, stream), "band kernel launch");
+}
+
+}  // namespace sph_b200
+
+// ---------------------------------------------------------------------------------------------
+namespace sphericart {
+namespace cuda {
+
+using sph_b200::CalculatorState;
+
+template <typename T> static CalculatorState<T>* state_of(T* slot) { return reinterpret_cast<CalculatorState<T>*>(slot); }
+
+template <typename T> SphericalHarmonics<T>::SphericalHarmonics(size_t l_max) {
+    this->l_max = l_max;
+    this->nprefactors = (l_max + 1) * (l_max + 2);
+    this->normalized = true;
+    int count = 0;
+    cudaError_t status = cudaGetDeviceCount(&count);
+    if (status != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        throw std::runtime_error(
+            std::string("sphericart::cuda: no usable CUDA device (") + cudaGetErrorString(status) +
+            "); this library has no CPU code path"
+        );
+    }
+    this->device_count = count;
+    this->prefactors_cpu = new T[this->nprefactors];
+    sph_b200::build_tables<T>(int(l_max), this->prefactors_cpu);
+    this->prefactors_cuda = reinterpret_cast<T*>(new CalculatorState<T>());
+}
+
+template <typename T> SphericalHarmonics<T>::~SphericalHarmonics() {
+    delete[] this->prefactors_cpu;
+    this->prefactors_cpu = nullptr;
+    // Device tables are left to the driver at process exit, as the reference does
+    // (sphericart/src/sphericart_cuda.cpp:60-72): calculators often die during static
+    // destruction, after the CUDA runtime has shut down.
+    delete state_of<T>(this->prefactors_cuda);
+    this->prefactors_cuda = nullptr;
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute_internal(
+    const T* xyz,
+    const size_t n_samples,
+    bool compute_with_gradients,
+    bool compute_with_hessian,
+    T* sph,
+    T* dsph,
+    T* ddsph,
+    void* cuda_stream
+) {
+    if (n_samples == 0) return;  // callers may hold null pointers for empty arrays
+    if (xyz == nullptr) throw std::runtime_error("sphericart::cuda: xyz is a null pointer");
+    if (sph == nullptr) throw std::runtime_error("sphericart::cuda: sph is a null pointer; allocate it on the device");
+    if (compute_with_gradients && dsph == nullptr)
+        throw std::runtime_error("sphericart::cuda: gradients were requested but dsph is a null pointer");
+    if (compute_with_hessian && ddsph == nullptr)
+        throw std::runtime_error("sphericart::cuda: Hessians were requested but ddsph is a null pointer");
+    const int level = compute_with_hessian ? 2 : (compute_with_gradients ? 1 : 0);
+    sph_b200::run<T>(this->l_max, this->normalized, this->prefactors_cpu, *state_of<T>(this->prefactors_cuda), level, xyz,
+                     n_samples, sph, dsph, ddsph, nullptr, nullptr, cuda_stream);
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute(const T* xyz, const size_t n_samples, T* sph, void* cuda_stream) {
+    compute_internal(xyz, n_samples, false, false, sph, nullptr, nullptr, cuda_stream);
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute_with_gradients(const T* xyz, const size_t n_samples, T* sph, T* dsph, void* cuda_stream) {
+    compute_internal(xyz, n_samples, true, false, sph, dsph, nullptr, cuda_stream);
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute_with_hessians(
+    const T* xyz, const size_t n_samples, T* sph, T* dsph, T* ddsph, void* cuda_stream
+) {
+    compute_internal(xyz, n_samples, true, true, sph, dsph, ddsph, cuda_stream);
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute_vjp(
+    const T* xyz, const size_t n_samples, const T* sph_grad, T* xyz_grad, void* cuda_stream
+) {
+    if (n_samples == 0) return;
+    if (xyz == nullptr) throw std::runtime_error("sphericart::cuda: xyz is a null pointer");
+    if (sph_grad == nullptr) throw std::runtime_error("sphericart::cuda: sph_grad is a null pointer");
+    if (xyz_grad == nullptr) throw std::runtime_error("sphericart::cuda: xyz_grad is a null pointer");
+    sph_b200::run<T>(this->l_max, this->normalized, this->prefactors_cpu, *state_of<T>(this->prefactors_cuda), 3, xyz,
+                     n_samples, nullptr, nullptr, nullptr, sph_grad, xyz_grad, cuda_stream);
+}
+
+template <typename T> SolidHarmonics<T>::SolidHarmonics(size_t l_max) : SphericalHarmonics<T>(l_max) {
+    this->normalized = false;
+}
+
+// exported: the reference's torch and JAX bindings link against these C++ symbols directly
+template class __attribute__((visibility("default"))) SphericalHarmonics<float>;
+template class __attribute__((visibility("default"))) SphericalHarmonics<double>;
+template class __attribute__((visibility("default"))) SolidHarmonics<float>;
+template class __attribute__((visibility("default"))) SolidHarmonics<double>;
+
+}  // namespace cuda
+}  // namespace sphericart
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+namespace {
+
+thread_local std::string g_last_error;
+
+template <typename Calculator> Calculator* capi_new(size_t l_max) {
+    try {
+        return new Calculator(l_max);
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return nullptr;
+    } catch (...) {
+        g_last_error = "unknown exception";
+        return nullptr;
+    }
+}
+
+template <typename Calculator> void capi_delete(Calculator* calculator) {
+    try {
+        delete calculator;
+    } catch (...) {
+    }
+}
+
+// Reference convention for compute calls: report and abort (sphericart/src/sphericart-capi.cpp:653-696).
+template <typename Fn> void capi_or_abort(Fn&& fn) {
+    try {
+        fn();
+    } catch (const std::exception& e) {
+        std::printf("fatal error: %s\n", e.what());
+        std::fflush(stdout);
+        std::abort();
+    } catch (...) {
+        std::printf("fatal error: unknown exception type\n");
+        std::fflush(stdout);
+        std::abort();
+    }
+}
+
+template <typename Fn> int capi_try(Fn&& fn) {
+    try {
+        fn();
+        return 0;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return 1;
+    } catch (...) {
+        g_last_error = "unknown exception";
+        return 1;
+    }
+}
+
+template <typename Calculator, typename T>
+void level_call(Calculator* c, int level, const T* xyz, size_t n, T* sph, T* dsph, T* ddsph, void* stream) {
+    if (c == nullptr) throw std::runtime_error("sphericart::cuda: calculator is a null pointer");
+    switch (level) {
+        case 0: c->compute(xyz, n, sph, stream); break;
+        case 1: c->compute_with_gradients(xyz, n, sph, dsph, stream); break;
+        case 2: c->compute_with_hessians(xyz, n, sph, dsph, ddsph, stream); break;
+        default: throw std::runtime_error("sphericart::cuda: level must be 0, 1 or 2");
+    }
+}
+
+template <typename Calculator, typename T>
+void vjp_call(Calculator* c, const T* xyz, size_t n, const T* sph_grad, T* xyz_grad, void* stream) {
+    if (c == nullptr) throw std::runtime_error("sphericart::cuda: calculator is a null pointer");
+    c->compute_vjp(xyz, n, sph_grad, xyz_grad, stream);
+}
+
+}  // namespace
+
+extern "C" const char* sphericart_cuda_last_error(void) { return g_last_error.c_str(); }
+
+#define SPH_CAPI_FAMILY(KIND, SFX, T)                                                                               \
+    extern "C" sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* sphericart_cuda_##KIND##_harmonics_new##SFX( \
+        size_t l_max) {                                                                                             \
+        return capi_new<sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t>(l_max);                             \
+    }                                                                                                               \
+    extern "C" void sphericart_cuda_##KIND##_harmonics_delete##SFX(                                                 \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator) {                                       \
+        capi_delete(calculator);                                                                                    \
+    }                                                                                                               \
+    extern "C" void sphericart_cuda_##KIND##_harmonics_compute_array##SFX(                                          \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples, T* sph, \
+        void* cuda_stream) {                                                                                        \
+        capi_or_abort([&] { level_call(calculator, 0, xyz, n_samples, sph, (T*)nullptr, (T*)nullptr, cuda_stream); }); \
+    }                                                                                                               \
+    extern "C" void sphericart_cuda_##KIND##_harmonics_compute_array_with_gradients##SFX(                           \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples, T* sph, \
+        T* dsph, void* cuda_stream) {                                                                               \
+        capi_or_abort([&] { level_call(calculator, 1, xyz, n_samples, sph, dsph, (T*)nullptr, cuda_stream); });     \
+    }                                                                                                               \
+    extern "C" void sphericart_cuda_##KIND##_harmonics_compute_array_with_hessians##SFX(                            \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples, T* sph, \
+        T* dsph, T* ddsph, void* cuda_stream) {                                                                     \
+        capi_or_abort([&] { level_call(calculator, 2, xyz, n_samples, sph, dsph, ddsph, cuda_stream); });           \
+    }                                                                                                               \
+    extern "C" void sphericart_cuda_##KIND##_harmonics_compute_vjp##SFX(                                            \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples,         \
+        const T* sph_grad, T* xyz_grad, void* cuda_stream) {                                                        \
+        capi_or_abort([&] { vjp_call(calculator, xyz, n_samples, sph_grad, xyz_grad, cuda_stream); });              \
+    }                                                                                                               \
+    extern "C" int sphericart_cuda_##KIND##_harmonics_try_compute##SFX(                                             \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, int level, const T* xyz,                \
+        size_t n_samples, T* sph, T* dsph, T* ddsph, void* cuda_stream) {                                           \
+        return capi_try([&] { level_call(calculator, level, xyz, n_samples, sph, dsph, ddsph, cuda_stream); });     \
+    }                                                                                                               \
+    extern "C" int sphericart_cuda_##KIND##_harmonics_try_compute_vjp##SFX(                                         \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples,         \
+        const T* sph_grad, T* xyz_grad, void* cuda_stream) {                                                        \
+        return capi_try([&] { vjp_call(calculator, xyz, n_samples, sph_grad, xyz_grad, cuda_stream); });            \
+    }
+
+SPH_CAPI_FAMILY(spherical, , double)
+SPH_CAPI_FAMILY(spherical, _f, float)
+SPH_CAPI_FAMILY(solid, , double)
+SPH_CAPI_FAMILY(solid, _f, float)
+
+#undef SPH_CAPI_FAMILY

@@ -1,0 +1,115 @@
+// Instantiates the tile kernels for one (type, l_max) pair: compile with
+//   -DSPH_T=float|double -DSPH_LMAX=0..8
+#include "sph_launch.hpp"
+#include "sph_tile.cuh"
+
+#include <atomic>
+
+#ifndef SPH_T
+#error "compile with -DSPH_T=float or -DSPH_T=double"
+#endif
+#ifndef SPH_LMAX
+#error "compile with -DSPH_LMAX=<0..8>"
+#endif
+
+namespace sph_b200 {
+
+namespace {
+
+// Grid size per (kernel, device, warps per CTA), filled on first use. Races are benign: every
+// writer stores the same value.
+struct GridCache {
+    std::atomic<int> blocks[MAX_DEVICES][9];
+};
+
+template <typename Kernel> int cached_grid(GridCache& cache, Kernel kernel, int warps, size_t smem, int device) {
+    int v = cache.blocks[device][warps].load(std::memory_order_relaxed);
+    if (v == 0) {
+        v = persistent_grid(reinterpret_cast<const void*>(kernel), warps * 32, smem, device);
+        cache.blocks[device][warps].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+template <typename T, int LMAX> Tables<T, LMAX> make_tables(const T* host_tables) {
+    Tables<T, LMAX> t;
+    for (int i = 0; i < n_table(LMAX); ++i) {
+        t.F[i] = host_tables[i];
+        t.K[i] = host_tables[n_table(LMAX) + i];
+    }
+    return t;
+}
+
+template <typename T, int LMAX, int LEVEL, bool NORM>
+cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph, const T* host_tables, int warps,
+                           bool use_bulk, int device, cudaStream_t stream) {
+    static GridCache cache{};
+    auto kernel = sph_tile_kernel<T, LMAX, LEVEL, NORM>;
+    const size_t smem = size_t(warps) * tile_smem_bytes<T, LMAX, LEVEL>();
+    const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const long long want = (ntiles + warps - 1) / warps;
+    const int grid = int(want < max_blocks ? want : max_blocks);
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, n, sph, dsph, ddsph, make_tables<T, LMAX>(host_tables),
+                                               use_bulk ? 1 : 0);
+    return cudaGetLastError();
+}
+
+template <typename T, int LMAX, bool NORM>
+cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, int warps,
+                       int device, cudaStream_t stream) {
+    static GridCache cache{};
+    auto kernel = sph_vjp_tile_kernel<T, LMAX, NORM>;
+    const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>();
+    const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const long long want = (ntiles + warps - 1) / warps;
+    const int grid = int(want < max_blocks ? want : max_blocks);
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables));
+    return cudaGetLastError();
+}
+
+template <typename T, int LMAX, int LEVEL> constexpr bool tile_fits() {
+    return tile_smem_bytes<T, LMAX, LEVEL>() <= TILE_SMEM_LIMIT;
+}
+
+}  // namespace
+
+template <typename T, int LMAX> size_t TileLaunch<T, LMAX>::smem_per_warp(int level) {
+    return size_t(TILE_POINTS) * n_columns(LMAX) * level_components(level) * sizeof(T);
+}
+
+template <typename T, int LMAX>
+cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
+                                         T* ddsph, const T* host_tables, int warps, bool use_bulk, int device,
+                                         cudaStream_t stream) {
+#define SPH_CASE(LEVEL)                                                                                            \
+    if constexpr (tile_fits<T, LMAX, LEVEL>()) {                                                                   \
+        return normalized ? launch_forward<T, LMAX, LEVEL, true>(xyz, n, sph, dsph, ddsph, host_tables, warps,     \
+                                                                 use_bulk, device, stream)                        \
+                          : launch_forward<T, LMAX, LEVEL, false>(xyz, n, sph, dsph, ddsph, host_tables, warps,    \
+                                                                  use_bulk, device, stream);                       \
+    } else {                                                                                                       \
+        return cudaErrorInvalidConfiguration;                                                                      \
+    }
+    switch (level) {
+        case 0: SPH_CASE(0)
+        case 1: SPH_CASE(1)
+        case 2: SPH_CASE(2)
+        default: return cudaErrorInvalidValue;
+    }
+#undef SPH_CASE
+}
+
+template <typename T, int LMAX>
+cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
+                                     const T* host_tables, int warps, int device, cudaStream_t stream) {
+    return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, device, stream)
+                      : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, device, stream);
+}
+
+template struct TileLaunch<SPH_T, SPH_LMAX>;
+
+}  // namespace sph_b200

@@ -1,0 +1,158 @@
+"""Calculators for torch CUDA tensors on top of the C ABI.
+
+Same shape as the reference's array front end (``python/src/sphericart/spherical_harmonics.py:9-245``:
+``SphericalHarmonics(l_max).compute / compute_with_gradients / compute_with_hessians``), with
+torch CUDA tensors where the reference takes CuPy arrays, plus the fused ``compute_vjp`` and an
+autograd-aware ``forward`` that uses it (the reference's backward re-runs the gradients kernel
+and reduces with two more kernels: ``sphericart-torch/python/sphericart/torch/register.py:90-108``).
+
+Everything here launches CUDA kernels through ``libsphericart_b200.so``; CPU tensors are
+rejected, there is no other code path.
+"""
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _c_lib
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class _BaseHarmonics:
+    _prefix = ""
+    normalized = True
+
+    def __init__(self, l_max: int):
+        if l_max < 0:
+            raise ValueError("l_max must be non-negative")
+        self._l_max = int(l_max)
+        self._lib = _c_lib.get_library()
+        self._calculators = {}
+
+    @property
+    def l_max(self) -> int:
+        return self._l_max
+
+    def __del__(self):
+        lib = getattr(self, "_lib", None)
+        for dtype, handle in getattr(self, "_calculators", {}).items():
+            if handle:
+                sfx = "" if dtype == torch.float64 else "_f"
+                getattr(lib, f"{self._prefix}_delete{sfx}")(handle)
+        self._calculators = {}
+
+    # -- plumbing ---------------------------------------------------------------------------
+    def _calculator(self, dtype):
+        handle = self._calculators.get(dtype)
+        if handle is None:
+            sfx = "" if dtype == torch.float64 else "_f"
+            handle = getattr(self._lib, f"{self._prefix}_new{sfx}")(self._l_max)
+            if not handle:
+                raise RuntimeError("failed to create the CUDA calculator: " + _c_lib.last_error())
+            self._calculators[dtype] = handle
+        return handle
+
+    def _validate_xyz(self, xyz):
+        if not isinstance(xyz, torch.Tensor):
+            raise TypeError("xyz must be a torch.Tensor on a CUDA device")
+        if not xyz.is_cuda:
+            raise TypeError("xyz must live on a CUDA device: this library has no CPU code path")
+        if xyz.dtype not in (torch.float32, torch.float64):
+            raise TypeError("xyz must be a tensor of 32 or 64-bit floats")
+        if xyz.dim() != 2 or xyz.shape[1] != 3:
+            raise ValueError("xyz tensor must be a `N x 3` array")
+        return xyz.detach().contiguous()
+
+    def compute_raw(self, dtype, level, xyz_ptr, n_samples, sph_ptr, dsph_ptr=None, ddsph_ptr=None, stream=None):
+        """Thin wrapper of ``*_try_compute``: device pointers in, work enqueued on ``stream``."""
+        sfx = "" if dtype == torch.float64 else "_f"
+        status = getattr(self._lib, f"{self._prefix}_try_compute{sfx}")(
+            self._calculator(dtype), level, xyz_ptr, n_samples, sph_ptr, dsph_ptr, ddsph_ptr, stream)
+        if status != 0:
+            raise RuntimeError(_c_lib.last_error())
+
+    def compute_vjp_raw(self, dtype, xyz_ptr, n_samples, sph_grad_ptr, xyz_grad_ptr, stream=None):
+        sfx = "" if dtype == torch.float64 else "_f"
+        status = getattr(self._lib, f"{self._prefix}_try_compute_vjp{sfx}")(
+            self._calculator(dtype), xyz_ptr, n_samples, sph_grad_ptr, xyz_grad_ptr, stream)
+        if status != 0:
+            raise RuntimeError(_c_lib.last_error())
+
+    def _compute_impl(self, xyz, level, out=None):
+        xyz = self._validate_xyz(xyz)
+        n = xyz.shape[0]
+        ny = (self._l_max + 1) ** 2
+        if out is None:
+            sph = torch.empty((n, ny), dtype=xyz.dtype, device=xyz.device)
+            dsph = torch.empty((n, 3, ny), dtype=xyz.dtype, device=xyz.device) if level >= 1 else None
+            ddsph = torch.empty((n, 3, 3, ny), dtype=xyz.dtype, device=xyz.device) if level >= 2 else None
+        else:
+            sph, dsph, ddsph = (tuple(out) + (None, None))[:3]
+        stream = torch.cuda.current_stream(xyz.device).cuda_stream
+        self.compute_raw(xyz.dtype, level, _ptr(xyz), n, _ptr(sph), _ptr(dsph), _ptr(ddsph), stream)
+        return sph, dsph, ddsph
+
+    # -- public API -------------------------------------------------------------------------
+    def compute(self, xyz, out=None) -> torch.Tensor:
+        """Harmonics for an ``(n_samples, 3)`` CUDA tensor -> ``(n_samples, (l_max+1)^2)``."""
+        return self._compute_impl(xyz, 0, out)[0]
+
+    def compute_with_gradients(self, xyz, out=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Values and Cartesian gradients ``(n_samples, 3, (l_max+1)^2)``."""
+        return self._compute_impl(xyz, 1, out)[:2]
+
+    def compute_with_hessians(self, xyz, out=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Values, gradients and Hessians ``(n_samples, 3, 3, (l_max+1)^2)``."""
+        return self._compute_impl(xyz, 2, out)
+
+    def compute_vjp(self, xyz, sph_grad, out=None) -> torch.Tensor:
+        """``xyz_grad[i, a] = sum_k sph_grad[i, k] * dsph[i, a, k]`` in one kernel, no dsph in memory."""
+        xyz = self._validate_xyz(xyz)
+        n = xyz.shape[0]
+        ny = (self._l_max + 1) ** 2
+        if sph_grad.shape != (n, ny) or sph_grad.dtype != xyz.dtype or sph_grad.device != xyz.device:
+            raise ValueError("sph_grad must match xyz in dtype and device and have shape (n_samples, (l_max+1)^2)")
+        sph_grad = sph_grad.detach().contiguous()
+        xyz_grad = torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None else out
+        stream = torch.cuda.current_stream(xyz.device).cuda_stream
+        self.compute_vjp_raw(xyz.dtype, _ptr(xyz), n, _ptr(sph_grad), _ptr(xyz_grad), stream)
+        return xyz_grad
+
+    def forward(self, xyz) -> torch.Tensor:
+        """Values with autograd support: the backward pass is the fused VJP kernel."""
+        return _HarmonicsFunction.apply(xyz, self)
+
+    __call__ = forward
+
+
+class _HarmonicsFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xyz, calculator):
+        ctx.calculator = calculator
+        ctx.save_for_backward(xyz)
+        return calculator.compute(xyz)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_sph):
+        (xyz,) = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None
+        return ctx.calculator.compute_vjp(xyz, grad_sph), None
+
+
+class SphericalHarmonics(_BaseHarmonics):
+    """Real spherical harmonics Y_l^m of the direction of each point, up to degree ``l_max``."""
+
+    _prefix = "sphericart_cuda_spherical_harmonics"
+    normalized = True
+
+
+class SolidHarmonics(_BaseHarmonics):
+    """Solid harmonics r^l Y_l^m (homogeneous polynomials of x, y, z), up to degree ``l_max``."""
+
+    _prefix = "sphericart_cuda_solid_harmonics"
+    normalized = False
