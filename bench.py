@@ -1,0 +1,375 @@
+"""Benchmark of the harmonics hot path.
+
+    python bench.py --gpus 1 --steps 200 --warmup 10
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference --steps K --warmup W      # the reference's CPU path
+
+Workload: the case the headline metric is quoted on - SphericalHarmonics (normalised), l_max = 8,
+float32, values + gradients, 4,194,304 points per GPU drawn iid N(0,1) per coordinate (seed 1000 +
+rank). One step = one pass of the kernel over the rank's points. Points are independent, so ranks
+share nothing: no collective is on the data path (NCCL is used only for the barrier around the
+timed region and to take the maximum time over ranks); scaling is weak.
+
+Prints ONE JSON line on rank 0.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from sphericart_b200 import workloads  # noqa: E402
+
+METRIC = "points/sec, fp32 l_max=8 Y+dY (SphericalHarmonics)"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def _recorded_traffic(workload_name):
+    """DRAM bytes per launch taken from an ncu capture and recorded under profiles/ (or None)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            entry = json.load(f)[workload_name]
+        return entry
+    except Exception:
+        return None
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock, power and throttle reasons of one GPU through NVML (read-only)."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, uuid, period=0.01):
+        super().__init__(daemon=True)
+        self.period = period
+        self.samples = []  # (t, sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID("GPU-" + uuid)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((time.perf_counter(), mhz, int(reasons)))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop.set()
+
+    def summary(self, t0, t1):
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        note = "sampled during the timed region"
+        if not inside:
+            inside = self.samples
+            note = "timed region shorter than the sampling period: samples span warm-up and timed region"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "NVML unavailable"}
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        reasons = sorted(name for bit, name in self.REASONS.items() if mask & bit)
+        return {"sm_mhz": statistics.median(s[1] for s in inside), "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(inside), "note": note}
+
+
+def _dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+def reduce_max(value, world, device=None):
+    """Maximum of a Python float over ranks (device-timed durations are reduced this way)."""
+    if world == 1:
+        return value
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def reduce_sum(value, world, device=None):
+    if world == 1:
+        return value
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def cpu_reference_rate(wl, sample_points, seconds_budget=12.0, min_reps=3, max_reps=40):
+    """Times the reference's CPU path (or the restatement when the reference library is not
+    there) on ``sample_points`` points of the workload with all host threads.
+    Returns (points_per_second_median, kind, cores, reps, seconds_per_pass)."""
+    from oracle import oracle
+
+    xyz = workloads.make_points("metric", n_points=sample_points)
+    ny = wl.ny
+    sph = np.empty((sample_points, ny), dtype=wl.np_dtype)
+    dsph = np.empty((sample_points, 3, ny), dtype=wl.np_dtype)
+    if oracle.have_ref():
+        calc = oracle.RefCalculator(wl.l_max, wl.normalized, wl.np_dtype)
+        kind, cores = "reference", calc.omp_num_threads()
+
+        def one_pass():
+            calc.compute(xyz, wl.level, out=(sph, dsph, None))
+    else:
+        kind, cores = "port", os.cpu_count() or 1
+
+        def one_pass():
+            oracle.port_compute(xyz, wl.l_max, wl.normalized, wl.level, nthreads=0, out=(sph, dsph, None))
+
+    one_pass()  # first touch of the outputs + warm-up
+    one_pass()
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_reps and (len(times) < min_reps or time.perf_counter() - t_start < seconds_budget):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return sample_points / med, kind, cores, len(times), med
+
+
+def run_reference_arm(args):
+    rank, _, world = _dist_env()
+    if rank != 0:
+        return
+    wl, _ = workloads.CONFIGS["metric"]
+    from oracle import oracle
+
+    sample = 1 << 20
+    xyz = workloads.make_points("metric", n_points=sample)
+    sph = np.empty((sample, wl.ny), dtype=wl.np_dtype)
+    dsph = np.empty((sample, 3, wl.ny), dtype=wl.np_dtype)
+    if oracle.have_ref():
+        calc = oracle.RefCalculator(wl.l_max, wl.normalized, wl.np_dtype)
+        kind, cores = "reference", calc.omp_num_threads()
+
+        def step():
+            calc.compute(xyz, wl.level, out=(sph, dsph, None))
+    else:
+        kind, cores = "port", os.cpu_count() or 1
+
+        def step():
+            oracle.port_compute(xyz, wl.l_max, wl.normalized, wl.level, nthreads=0, out=(sph, dsph, None))
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    elapsed = time.perf_counter() - t0
+    value = sample * args.steps / elapsed
+    sample_text = (f"{sample} points of the workload per step (seed 1000), reference CPU library via its C API, "
+                   f"OpenMP threads = {cores}" if kind == "reference" else
+                   f"{sample} points per step, CPU restatement (reference library not built on this machine)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * elapsed / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.name, "l_max": wl.l_max, "level": "values+gradients",
+                   "points_per_step": sample, "device": "host CPU"},
+        "cpu_baseline": {"value": value, "unit": "points/s", "cores": cores, "kind": kind, "sample": sample_text},
+        "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--points", type=int, default=None, help="points per GPU (default: the workload's 4,194,304)")
+    ap.add_argument("--e2e-steps", type=int, default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+
+    import sphericart_b200
+    from sphericart_b200.host_pipeline import HostPipeline
+
+    rank, local, world = _dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU code path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    wl, _ = workloads.CONFIGS["metric"]
+    n = args.points or wl.n_points
+    warmup = max(args.warmup, 3)
+    xyz_host = torch.from_numpy(workloads.make_points("metric", n_points=n, seed_offset=rank))
+    xyz = xyz_host.to(device)
+    calc = sphericart_b200.SphericalHarmonics(wl.l_max)
+    ny = wl.ny
+    sph = torch.empty((n, ny), dtype=torch.float32, device=device)
+    dsph = torch.empty((n, 3, ny), dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream(device)
+
+    launches = 0
+
+    def step():
+        nonlocal launches
+        calc.compute_raw(torch.float32, wl.level, xyz.data_ptr(), n, sph.data_ptr(), dsph.data_ptr(), None,
+                         stream.cuda_stream)
+        launches += 1
+
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid))
+    sampler.start()
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    launches = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    torch.cuda.synchronize(device)
+    t_wall1 = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    sampler.stop()
+    my_ms = ev0.elapsed_time(ev1)
+    timed_launches = launches
+    total_ms = reduce_max(my_ms, world, device)
+    total_points = reduce_sum(float(n), world, device)
+    ms_per_step = total_ms / args.steps
+    value = total_points * args.steps / (total_ms * 1e-3)
+
+    # end to end through the host-buffer front end: pinned host xyz -> device -> kernel -> pinned host outputs
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = args.e2e_steps or max(1, min(args.steps, 5))
+        pipe = HostPipeline(calc, wl.level, torch.float32, device)
+        xyz_pin = xyz_host.pin_memory()
+        sph_pin = torch.empty((n, ny), dtype=torch.float32, pin_memory=True)
+        dsph_pin = torch.empty((n, 3, ny), dtype=torch.float32, pin_memory=True)
+        pipe.run(xyz_pin, [sph_pin, dsph_pin])  # warm-up
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            pipe.run(xyz_pin, [sph_pin, dsph_pin])
+        e1.record(stream)
+        torch.cuda.synchronize(device)
+        e2e_ms = reduce_max(e0.elapsed_time(e1), world, device)
+        bi, bo = pipe.bytes_per_point()
+        e2e = {"value": total_points * e2e_steps / (e2e_ms * 1e-3), "unit": "points/s",
+               "h2d_bytes_per_step": int(bi * total_points), "d2h_bytes_per_step": int(bo * total_points),
+               "steps": e2e_steps,
+               "path": "HostPipeline: pinned host xyz -> H2D -> kernel -> D2H of sph and dsph into pinned host "
+                       "arrays, 3 streams, 262144-point chunks; bound by PCIe device-to-host bandwidth"}
+        del sph_pin, dsph_pin
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = _peaks()
+    bytes_per_launch = wl.bytes_per_point() * n
+    achieved = bytes_per_launch / (my_ms / args.steps * 1e-3) / 1e9
+    traffic = _recorded_traffic(wl.name)
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": (traffic or {}).get("dram_bytes_per_launch"),
+                "peak_source": f"of {peak_kind}", "kernel": "sph_tile_kernel<float,8,1,true>",
+                "algorithmic_bytes_per_launch": bytes_per_launch,
+                "traffic_note": (traffic or {}).get("note")}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        sample = 1 << 21
+        rate, kind, cores, reps, sec = cpu_reference_rate(wl, sample)
+        cpu = {"value": rate, "unit": "points/s", "cores": cores, "kind": kind,
+               "sample": f"first {sample} points of the workload (seed 1000), median of {reps} passes of "
+                         f"{sec * 1e3:.1f} ms after 2 warm-up passes, preallocated outputs"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.name, "class": "SphericalHarmonics", "l_max": wl.l_max,
+                   "level": "values+gradients", "points_per_gpu": n, "bytes_per_point": wl.bytes_per_point(),
+                   "l2_policy": "outputs (5.4 GB per step per GPU) are far larger than L2; no flush needed",
+                   "parallelism": f"points sharded over {world} GPU(s), no collective"},
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e,
+        "gpu_launches": timed_launches,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

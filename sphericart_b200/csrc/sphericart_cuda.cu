@@ -30,11 +30,27 @@ void check(cudaError_t status, const char* what) {
     }
 }
 
-// Development knob, read once: an integer environment variable or a default.
+// Development knobs, read from the environment once per process (0 = use the built-in choice).
+struct Knobs {
+    int band_image_kb;  // per-warp image budget of the band kernel, KiB
+    int band_lanes;     // force lanes per point (1..32, power of two)
+    int band_warps;     // force warps per CTA of the band kernel (1..4)
+    int tile_warps;     // force warps per CTA of the tile kernels (1..8)
+    int force_band;     // route l_max <= 8 through the band kernel too
+    int no_bulk;        // copy tiles out with plain stores instead of TMA bulk stores
+};
+
 int env_int(const char* name, int fallback) {
     const char* v = std::getenv(name);
     if (v == nullptr || *v == '\0') return fallback;
     return std::atoi(v);
+}
+
+const Knobs& knobs() {
+    static const Knobs k = {env_int("SPH_B200_BAND_IMAGE_KB", 64), env_int("SPH_B200_BAND_LANES", 0),
+                            env_int("SPH_B200_BAND_WARPS", 0),     env_int("SPH_B200_TILE_WARPS", 0),
+                            env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0)};
+    return k;
 }
 
 struct DeviceProps {
@@ -123,10 +139,10 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
 
     // lanes per point: the smallest power of two whose 32/G-point image stays within the
     // per-warp budget, but never more lanes than there are channels worth sharing
-    const size_t budget = size_t(env_int("SPH_B200_BAND_IMAGE_KB", 64)) * 1024;
+    const size_t budget = size_t(knobs().band_image_kb) * 1024;
     int G = 1;
     while (G < 32 && size_t(32 / G) * row_bytes > budget) G *= 2;
-    const int forced = env_int("SPH_B200_BAND_LANES", 0);
+    const int forced = knobs().band_lanes;
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16 || forced == 32) G = forced;
     const int P = 32 / G;
 
@@ -186,7 +202,7 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
     const size_t per_warp = csz_bytes + size_t(plan.image_elems) * elem;
     const size_t plan_bytes = plan.ints.size() * sizeof(int);
     int warps = 4;
-    const int forced_warps = env_int("SPH_B200_BAND_WARPS", 0);
+    const int forced_warps = knobs().band_warps;
     if (forced_warps >= 1 && forced_warps <= 4) warps = forced_warps;
     while (warps > 1 && table_bytes + plan_bytes + warps * per_warp > smem_limit) --warps;
     // prefer a CTA size that packs the SM: with W warps per CTA, floor(limit / cta) CTAs fit
@@ -309,7 +325,7 @@ cudaError_t band_dispatch(int lanes, int level, bool vjp, bool normalized, const
 
 // Warps per CTA for a tile kernel: keep a CTA's images within ~48 KB so several CTAs share an SM.
 int tile_warps(size_t smem_per_warp) {
-    const int forced = env_int("SPH_B200_TILE_WARPS", 0);
+    const int forced = knobs().tile_warps;
     if (forced >= 1 && forced <= 8) return forced;
     const size_t w = smem_per_warp == 0 ? 8 : (48 * 1024) / smem_per_warp;
     return int(std::min<size_t>(8, std::max<size_t>(1, w)));
@@ -325,7 +341,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
     DeviceScope scope(xyz);
     const DeviceProps& props = device_props(scope.device);
     const bool vjp = kind == 3;
-    const bool force_band = env_int("SPH_B200_FORCE_BAND", 0) != 0;
+    const bool force_band = knobs().force_band != 0;
 
     if (l_max <= TILE_LMAX && !force_band) {
         const size_t per_warp = vjp ? size_t(32) * n_columns(l_max) * sizeof(T)
@@ -338,7 +354,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         }
         if (per_warp <= TILE_SMEM_LIMIT) {
             bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
-            if (env_int("SPH_B200_NO_BULK", 0) != 0) use_bulk = false;
+            if (knobs().no_bulk != 0) use_bulk = false;
             check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables,
                                            tile_warps(per_warp), use_bulk, scope.device, stream),
                   "tile kernel launch");

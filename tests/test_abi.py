@@ -1,0 +1,112 @@
+"""CPU-side checks of the drop-in boundary: the shared library loads, exports every function
+the C header declares and the C++ calculator symbols, keeps the reference's object layout, and
+fails loudly (no fallback) when there is no GPU."""
+
+import os
+import re
+import subprocess
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "sphericart_b200.h")
+REFERENCE_HEADER_DIR = "/root/reference/sphericart/include"
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return re.findall(r"SPHERICART_EXPORT\s+[\w\s\*]+?\b(sphericart_cuda_\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_function():
+    from sphericart_b200 import _c_lib
+
+    lib = _c_lib.get_library()
+    declared = _declared_functions()
+    assert len(declared) == 33, declared
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert sorted(declared) == sorted(_c_lib.exported_names())
+
+
+def test_header_cites_the_reference_for_every_reference_entry_point():
+    text = open(HEADER).read()
+    for kind in ("spherical", "solid"):
+        for sfx in ("", "_f"):
+            for fn in ("new", "delete", "compute_array", "compute_array_with_gradients", "compute_array_with_hessians"):
+                name = f"sphericart_cuda_{kind}_harmonics_{fn}{sfx}("
+                idx = text.index(name)
+                preceding = text[max(0, idx - 200):idx]
+                assert "replaces sphericart/include/sphericart.h:" in preceding, name
+
+
+def test_cxx_calculator_symbols_are_exported():
+    from sphericart_b200 import _c_lib
+
+    out = subprocess.run(["nm", "-DC", "--defined-only", _c_lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    for cls in ("SphericalHarmonics", "SolidHarmonics"):
+        for t in ("float", "double"):
+            assert f"sphericart::cuda::{cls}<{t}>::{cls}(unsigned long)" in out
+    for t in ("float", "double"):
+        for method in ("compute(", "compute_with_gradients(", "compute_with_hessians(", "compute_vjp("):
+            assert f"sphericart::cuda::SphericalHarmonics<{t}>::{method}" in out
+
+
+def test_object_layout_matches_the_reference_header(tmp_path):
+    """Bindings built against the reference header allocate the calculators themselves, so size and
+    alignment must agree. Needs the reference checkout; skipped where it is absent."""
+    if not os.path.exists(os.path.join(REFERENCE_HEADER_DIR, "sphericart_cuda.hpp")):
+        pytest.skip("reference headers not available on this machine")
+    prog = r"""
+#include <cstdio>
+#include "sphericart_cuda.hpp"
+int main() {
+    std::printf("%zu %zu %zu %zu\n", sizeof(sphericart::cuda::SphericalHarmonics<float>),
+                alignof(sphericart::cuda::SphericalHarmonics<float>),
+                sizeof(sphericart::cuda::SolidHarmonics<double>), alignof(sphericart::cuda::SolidHarmonics<double>));
+}
+"""
+    src = tmp_path / "layout.cpp"
+    src.write_text(prog)
+    results = []
+    for inc in (os.path.join(ROOT, "include"), REFERENCE_HEADER_DIR):
+        exe = tmp_path / ("layout_" + str(len(results)))
+        subprocess.run(["g++", "-std=c++17", "-I", inc, str(src), "-o", str(exe)], check=True)
+        results.append(subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout)
+    assert results[0] == results[1], results
+
+
+def test_front_end_validates_before_touching_the_device():
+    import sphericart_b200 as sb
+
+    calc = sb.SphericalHarmonics(3)
+    with pytest.raises(TypeError, match="CUDA"):
+        calc.compute(torch.zeros(4, 3))
+    with pytest.raises(TypeError):
+        calc.compute([[0.0, 0.0, 1.0]])
+    with pytest.raises(ValueError):
+        sb.SolidHarmonics(-1)
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_no_gpu_means_failure_not_fallback():
+    from sphericart_b200 import _c_lib
+
+    lib = _c_lib.get_library()
+    handle = lib.sphericart_cuda_spherical_harmonics_new_f(4)
+    assert not handle, "calculator creation must fail without a CUDA device"
+    assert "no CPU code path" in _c_lib.last_error()
+
+
+def test_product_code_never_touches_the_oracle():
+    """The checker is test infrastructure: nothing under the package may import or load it."""
+    pkg = os.path.join(ROOT, "sphericart_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if "_build" in dirpath:
+            continue
+        for name in files:
+            if name.endswith((".py", ".cu", ".cuh", ".hpp", ".h")):
+                text = open(os.path.join(dirpath, name)).read()
+                assert "oracle" not in text.lower(), (dirpath, name)
