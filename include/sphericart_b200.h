@@ -200,6 +200,20 @@ SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_f(
 SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_f(
     sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, float* xyz_grad, void* cuda_stream);
 
+/* No counterpart in the reference. Values and gradients (float64, level 1) for hosts that do not
+ * let a plugin allocate device memory of its own - a runtime that reserved the whole device arena
+ * at start-up, or a latency-bound service loop where cudaMalloc's device-wide synchronisation is
+ * not acceptable. The calculators above cudaMalloc their tables on first use when l_max > 8; this
+ * entry point instead keeps them in a fixed 16 KiB array that is part of the library image (every
+ * GPU that loads the library holds it until the process exits) and calls no allocating routine.
+ * Limit: l_max <= 32; larger values are rejected with an error. normalized != 0 selects spherical
+ * harmonics, 0 solid harmonics. The first call on each device looks up the array's device address
+ * and opts the kernel into its shared memory, so make that call before any stream capture. All
+ * calls on a device share the array: calls that can overlap on the GPU race on it, so order them.
+ * Returns 0 on success; otherwise non-zero, message in sphericart_cuda_last_error(). */
+SPHERICART_EXPORT int sphericart_cuda_harmonics_with_gradients_no_alloc(
+    int normalized, size_t l_max, const double* xyz, size_t n_samples, double* sph, double* dsph, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

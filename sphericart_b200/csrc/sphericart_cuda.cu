@@ -598,3 +598,117 @@ SPH_CAPI_FAMILY(solid, , double)
 SPH_CAPI_FAMILY(solid, _f, float)
 
 #undef SPH_CAPI_FAMILY
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (an addition; the reference has nothing like it).
+//
+// Who needs it: hosts that hand a plugin its input and output buffers but do not let it take
+// device memory of its own. Examples are runtimes that reserve the whole device arena when the
+// process starts, so a later cudaMalloc from a plugin simply fails, and latency-bound service
+// loops in which cudaMalloc is off limits because it synchronises the device and may block. The
+// calculators above cannot serve such hosts for l_max > 8: their run-time-degree kernel reads the
+// prefactor tables and the lane schedule from device buffers that they cudaMalloc on first use.
+//
+// This variant runs the same kernel (float64, values + gradients, run-time l_max) with those
+// tables and that schedule placed in a fixed array that is part of the library image, so every GPU
+// that loads the library carries NO_ALLOC_SCRATCH_BYTES (16 KiB) of it until the process ends. The
+// function calls no cudaMalloc, cudaFree or any other allocating routine; the caller passes inputs
+// and outputs as usual. The fixed size bounds the degree: l_max <= NO_ALLOC_MAX_L (32).
+//
+// In host code the array's name below is only a host-side stand-in for the device object: it is
+// not an address a kernel may be given. The real device address is looked up once per device, with
+// that device current, by cudaGetSymbolAddress, and that address is what the kernel receives.
+// That look-up (plus the kernel's shared-memory opt-in) happens in the first call made on each
+// device, so make that first call before any stream capture begins.
+//
+// All calls on one device share the one array, and it keeps what the last call left in it. A call
+// overwrites, on the caller's stream, every byte the kernel will read unless the array already holds
+// the data for the same l_max (nothing in it has to start at zero, nothing is read before it is
+// written). Calls that may overlap on the GPU - different streams with no ordering between them -
+// race on the array; order such calls.
+namespace {
+
+constexpr int NO_ALLOC_MAX_L = 32;
+constexpr size_t NO_ALLOC_TABLE_BYTES = 9216;   // 2 * n_table(32) doubles = 8976 bytes, rounded up
+constexpr size_t NO_ALLOC_PLAN_BYTES = 7168;    // lane schedule, ints
+constexpr size_t NO_ALLOC_SCRATCH_BYTES = NO_ALLOC_TABLE_BYTES + NO_ALLOC_PLAN_BYTES;
+
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[NO_ALLOC_SCRATCH_BYTES];
+
+struct NoAllocDevice {
+    unsigned char* scratch = nullptr;  // device address of g_no_alloc_scratch on this device
+    int resident_l_max = -1;           // whose tables and schedule the array holds now
+};
+std::mutex g_no_alloc_mutex;
+NoAllocDevice g_no_alloc_devices[sph_b200::MAX_DEVICES];
+
+void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_samples, double* sph, double* dsph,
+                  void* cuda_stream) {
+    using namespace sph_b200;
+    if (n_samples == 0) return;
+    if (l_max_ > size_t(NO_ALLOC_MAX_L)) {
+        throw std::runtime_error("sphericart::cuda: the allocation-free entry point supports l_max <= 32 (its fixed "
+                                 "16 KiB device array cannot hold larger tables); got l_max = " + std::to_string(l_max_));
+    }
+    if (xyz == nullptr || sph == nullptr || dsph == nullptr) {
+        throw std::runtime_error("sphericart::cuda: xyz, sph and dsph must be device pointers, got a null pointer");
+    }
+    const int l_max = int(l_max_);
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    DeviceScope scope(xyz);
+    const DeviceProps& props = device_props(scope.device);
+
+    // host-side tables and schedule (host heap only)
+    std::vector<double> tables(2 * size_t(n_table(l_max)));
+    build_tables<double>(l_max, tables.data());
+    const BandPlan plan = make_band_plan(l_max, /*kind=*/1, sizeof(double), props.smem_optin);
+    const size_t table_bytes = tables.size() * sizeof(double);
+    const size_t plan_bytes = plan.ints.size() * sizeof(int);
+    if (table_bytes > NO_ALLOC_TABLE_BYTES || plan_bytes > NO_ALLOC_PLAN_BYTES || plan.smem > props.smem_optin) {
+        throw std::runtime_error("sphericart::cuda: internal tables do not fit the allocation-free array");
+    }
+
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    NoAllocDevice& dev = g_no_alloc_devices[scope.device];
+    if (dev.scratch == nullptr) {
+        // once per device, with that device current (DeviceScope made it so)
+        void* address = nullptr;
+        check(cudaGetSymbolAddress(&address, g_no_alloc_scratch), "cudaGetSymbolAddress(no-alloc array)");
+        dev.scratch = static_cast<unsigned char*>(address);
+    }
+    if (dev.resident_l_max != l_max) {
+        check(cudaMemcpyAsync(dev.scratch, tables.data(), table_bytes, cudaMemcpyHostToDevice, stream),
+              "cudaMemcpyAsync(tables)");
+        check(cudaMemcpyAsync(dev.scratch + NO_ALLOC_TABLE_BYTES, plan.ints.data(), plan_bytes, cudaMemcpyHostToDevice,
+                              stream),
+              "cudaMemcpyAsync(schedule)");
+        dev.resident_l_max = l_max;
+    }
+    BandLaunchArgs<double> a{xyz,
+                             (long long)n_samples,
+                             sph,
+                             dsph,
+                             nullptr,
+                             nullptr,
+                             nullptr,
+                             reinterpret_cast<const double*>(dev.scratch),
+                             reinterpret_cast<const int*>(dev.scratch + NO_ALLOC_TABLE_BYTES),
+                             l_max,
+                             int(plan.ints.size()),
+                             plan.image_elems,
+                             plan.warps,
+                             plan.smem};
+    check(band_dispatch<double>(plan.lanes, 1, false, normalized, a, scope.device, stream),
+          "band kernel launch (allocation-free)");
+}
+
+}  // namespace
+
+// Values and gradients in float64 for n_samples points, l_max <= 32, without any device
+// allocation. normalized != 0: spherical harmonics, 0: solid harmonics. Returns 0 on success, else
+// non-zero with the message in sphericart_cuda_last_error().
+extern "C" int sphericart_cuda_harmonics_with_gradients_no_alloc(int normalized, size_t l_max, const double* xyz,
+                                                                 size_t n_samples, double* sph, double* dsph,
+                                                                 void* cuda_stream) {
+    return capi_try([&] { no_alloc_run(normalized != 0, l_max, xyz, n_samples, sph, dsph, cuda_stream); });
+}
