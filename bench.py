@@ -161,6 +161,7 @@ def cpu_reference_rate(wl, sample_points, seconds_budget=12.0, min_reps=3, max_r
     Returns (points_per_second_median, kind, cores, reps, seconds_per_pass)."""
     from oracle import oracle
 
+    oracle.use_all_host_threads()
     xyz = workloads.make_points("metric", n_points=sample_points)
     ny = wl.ny
     sph = np.empty((sample_points, ny), dtype=wl.np_dtype)
@@ -196,6 +197,7 @@ def run_reference_arm(args):
     wl, _ = workloads.CONFIGS["metric"]
     from oracle import oracle
 
+    host_threads = oracle.use_all_host_threads()
     sample = 1 << 20
     xyz = workloads.make_points("metric", n_points=sample)
     sph = np.empty((sample, wl.ny), dtype=wl.np_dtype)
@@ -207,7 +209,7 @@ def run_reference_arm(args):
         def step():
             calc.compute(xyz, wl.level, out=(sph, dsph, None))
     else:
-        kind, cores = "port", os.cpu_count() or 1
+        kind, cores = "port", host_threads
 
         def step():
             oracle.port_compute(xyz, wl.l_max, wl.normalized, wl.level, nthreads=0, out=(sph, dsph, None))
@@ -245,6 +247,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--config", default="metric", choices=sorted(workloads.CONFIGS),
+                    help="metric = the headline case; cfg1..cfg5 = the other benchmark configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -265,24 +269,41 @@ def main():
 
         dist.init_process_group("nccl", device_id=device)
 
-    wl, _ = workloads.CONFIGS["metric"]
+    wl, _ = workloads.CONFIGS[args.config]
     n = args.points or wl.n_points
     warmup = max(args.warmup, 3)
-    xyz_host = torch.from_numpy(workloads.make_points("metric", n_points=n, seed_offset=rank))
+    tdtype = torch.float64 if wl.dtype == "f64" else torch.float32
+    xyz_host = torch.from_numpy(workloads.make_points(args.config, n_points=n, seed_offset=rank))
     xyz = xyz_host.to(device)
-    calc = sphericart_b200.SphericalHarmonics(wl.l_max)
+    calc = (sphericart_b200.SphericalHarmonics if wl.normalized else sphericart_b200.SolidHarmonics)(wl.l_max)
     ny = wl.ny
-    sph = torch.empty((n, ny), dtype=torch.float32, device=device)
-    dsph = torch.empty((n, 3, ny), dtype=torch.float32, device=device)
+    sph = torch.empty((n, ny), dtype=tdtype, device=device)
+    dsph = torch.empty((n, 3, ny), dtype=tdtype, device=device) if wl.level >= 1 else None
+    ddsph = torch.empty((n, 3, 3, ny), dtype=tdtype, device=device) if wl.level >= 2 else None
+    sph_grad = xyz_grad = None
+    if wl.vjp:
+        sph_grad = torch.from_numpy(workloads.make_upstream_grad(args.config, n_points=n, seed_offset=rank)).to(device)
+        xyz_grad = torch.empty((n, 3), dtype=tdtype, device=device)
     stream = torch.cuda.current_stream(device)
+    ptr = lambda t: None if t is None else t.data_ptr()  # noqa: E731
 
     launches = 0
 
     def step():
         nonlocal launches
-        calc.compute_raw(torch.float32, wl.level, xyz.data_ptr(), n, sph.data_ptr(), dsph.data_ptr(), None,
-                         stream.cuda_stream)
+        calc.compute_raw(tdtype, wl.level, xyz.data_ptr(), n, ptr(sph), ptr(dsph), ptr(ddsph), stream.cuda_stream)
         launches += 1
+        if wl.vjp:
+            calc.compute_vjp_raw(tdtype, xyz.data_ptr(), n, sph_grad.data_ptr(), xyz_grad.data_ptr(), stream.cuda_stream)
+            launches += 1
+
+    # bytes one step moves by the algorithm's own count (forward, plus the fused backward where the
+    # configuration has one)
+    elem = 8 if wl.dtype == "f64" else 4
+    step_bytes_per_point = elem * (3 + ny * (1, 4, 13)[wl.level]) + (elem * (3 + ny + 3) if wl.vjp else 0)
+    out_bytes = step_bytes_per_point * n
+    # outputs smaller than a few L2 sizes would stay cached between steps: flush L2 between timed steps
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if out_bytes < (512 << 20) else None
 
     sampler = ClockSampler(str(torch.cuda.get_device_properties(device).uuid))
     sampler.start()
@@ -293,19 +314,31 @@ def main():
         dist.barrier()
     torch.cuda.synchronize(device)
     launches = 0
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.perf_counter()
-    ev0.record(stream)
-    for _ in range(args.steps):
-        step()
-    ev1.record(stream)
-    torch.cuda.synchronize(device)
+    if flush is None:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        torch.cuda.synchronize(device)
+        my_ms = ev0.elapsed_time(ev1)
+    else:
+        pairs = []
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            step()
+            e1.record(stream)
+            pairs.append((e0, e1))
+        torch.cuda.synchronize(device)
+        my_ms = sum(a.elapsed_time(b) for a, b in pairs)
     t_wall1 = time.perf_counter()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
     sampler.stop()
-    my_ms = ev0.elapsed_time(ev1)
     timed_launches = launches
     total_ms = reduce_max(my_ms, world, device)
     total_points = reduce_sum(float(n), world, device)
@@ -314,12 +347,12 @@ def main():
 
     # end to end through the host-buffer front end: pinned host xyz -> device -> kernel -> pinned host outputs
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and args.config == "metric":
         e2e_steps = args.e2e_steps or max(1, min(args.steps, 5))
-        pipe = HostPipeline(calc, wl.level, torch.float32, device)
+        pipe = HostPipeline(calc, wl.level, tdtype, device)
         xyz_pin = xyz_host.pin_memory()
-        sph_pin = torch.empty((n, ny), dtype=torch.float32, pin_memory=True)
-        dsph_pin = torch.empty((n, 3, ny), dtype=torch.float32, pin_memory=True)
+        sph_pin = torch.empty((n, ny), dtype=tdtype, pin_memory=True)
+        dsph_pin = torch.empty((n, 3, ny), dtype=tdtype, pin_memory=True)
         pipe.run(xyz_pin, [sph_pin, dsph_pin])  # warm-up
         if world > 1:
             dist.barrier()
@@ -345,17 +378,20 @@ def main():
         return
 
     peak, peak_kind = _peaks()
-    bytes_per_launch = wl.bytes_per_point() * n
+    bytes_per_launch = out_bytes
     achieved = bytes_per_launch / (my_ms / args.steps * 1e-3) / 1e9
     traffic = _recorded_traffic(wl.name, n)
+    kernel = ("sph_tile_kernel" if wl.l_max <= 8 else "sph_band_kernel") + \
+        f"<{'double' if wl.dtype == 'f64' else 'float'}, l_max={wl.l_max}, level={wl.level}>" + \
+        (" + fused VJP kernel" if wl.vjp else "")
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": (traffic or {}).get("dram_bytes_per_launch"),
-                "peak_source": f"of {peak_kind}", "kernel": "sph_tile_kernel<float,8,1,true>",
+                "peak_source": f"of {peak_kind}", "kernel": kernel,
                 "algorithmic_bytes_per_launch": bytes_per_launch,
                 "traffic_note": (traffic or {}).get("note")}
 
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.config == "metric":
         sample = 1 << 21
         rate, kind, cores, reps, sec = cpu_reference_rate(wl, sample)
         cpu = {"value": rate, "unit": "points/s", "cores": cores, "kind": kind,
@@ -363,12 +399,19 @@ def main():
                          f"{sec * 1e3:.1f} ms after 2 warm-up passes, preallocated outputs"}
 
     line = {
-        "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if args.config == "metric" else f"points/sec, {wl.name}",
+        "value": value, "unit": "points/s", "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl.name, "class": "SphericalHarmonics", "l_max": wl.l_max,
-                   "level": "values+gradients", "points_per_gpu": n, "bytes_per_point": wl.bytes_per_point(),
-                   "l2_policy": "outputs (5.4 GB per step per GPU) are far larger than L2; no flush needed",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "class": "SphericalHarmonics" if wl.normalized else "SolidHarmonics",
+                   "l_max": wl.l_max,
+                   "level": ("values", "values+gradients", "values+gradients+hessians")[wl.level] +
+                            (" then fused VJP" if wl.vjp else ""),
+                   "points_per_gpu": n, "bytes_per_point": step_bytes_per_point,
+                   "l2_policy": (f"{out_bytes / 1e9:.2f} GB written per step per GPU, far larger than L2: no flush"
+                                 if flush is None else
+                                 "small outputs: a 256 MB buffer is rewritten between timed steps to flush L2, "
+                                 "each step timed with its own event pair"),
                    "parallelism": f"points sharded over {world} GPU(s), no collective"},
         "roofline": roofline, "cpu_baseline": cpu, "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e,
         "gpu_launches": timed_launches,

@@ -32,6 +32,18 @@ def build(quiet=True):
         print(out.stdout)
 
 
+def use_all_host_threads():
+    """Make OpenMP use every core this process may run on, whatever OMP_NUM_THREADS says (launchers
+    such as torchrun export OMP_NUM_THREADS=1 to their workers). Call before creating a
+    calculator: the reference sizes its per-thread buffers from omp_get_max_threads() at
+    construction (sphericart/src/sphericart.cpp:36). Returns the thread count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    load_port()  # pulls in libgomp
+    gomp = ctypes.CDLL("libgomp.so.1")
+    gomp.omp_set_num_threads(ctypes.c_int(n))
+    return n
+
+
 def _ctype(dtype):
     return ctypes.c_double if np.dtype(dtype) == np.float64 else ctypes.c_float
 
