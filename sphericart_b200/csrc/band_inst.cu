@@ -27,8 +27,21 @@ cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t str
     const long long ngroups = (a.n + P - 1) / P;
     const long long want = (ngroups + a.warps - 1) / a.warps;
     const int grid = int(want < max_blocks ? want : max_blocks);
-    BandArgs<T> k{a.xyz, a.n,      a.sph,       a.dsph,        a.ddsph, a.sph_grad, a.xyz_grad,
-                  a.d_tables, a.d_plan, a.l_max, a.plan_ints, a.image_elems};
+    static_assert(BAND_MAX_BANDS == MAX_BANDS, "band limits must agree");
+    BandArgs<T> k{};
+    k.xyz = a.xyz;
+    k.n = a.n;
+    k.sph = a.sph;
+    k.dsph = a.dsph;
+    k.ddsph = a.ddsph;
+    k.sph_grad = a.sph_grad;
+    k.xyz_grad = a.xyz_grad;
+    k.tables = a.d_tables;
+    k.l_max = a.l_max;
+    k.nbands = a.nbands;
+    k.max_cols = a.max_cols;
+    k.use_bulk = a.use_bulk ? 1 : 0;
+    for (int b = 0; b <= MAX_BANDS; ++b) k.band_lo[b] = a.band_lo[b];
     kernel<<<grid, a.warps * 32, a.smem, stream>>>(k);
     return cudaGetLastError();
 }

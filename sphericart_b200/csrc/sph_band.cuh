@@ -2,35 +2,63 @@
 // vector-Jacobian product. Used wherever the compile-time tile kernels do not apply: l_max > 8,
 // and the cases whose 32-point tile image would not fit shared memory.
 //
-// Work split. A group of G lanes (G = 1, 2, 4, ... 32) shares one point, so a warp holds
-// P = 32 / G consecutive points. The degrees l >= 2 are independent channels (each runs its own
-// downward-in-m recurrence), and a channel costs l + 1 steps; the host deals the channels to the
-// G lanes with a longest-first greedy schedule so every lane gets nearly the same number of
-// steps, and each lane walks its list in ONE flat loop (channel changes happen inside the loop),
-// so lanes that own several short channels finish together with the lane that owns the longest.
+// Two phases per point, G lanes (1, 2, 4, ... 32) sharing a point, P = 32 / G points per warp:
+//
+//  A. The point's whole table Q_l^m (0 <= m <= l <= l_max) is built in shared memory with the
+//     reference's downward-in-m recurrence, one row (one degree) per lane, together with
+//     c_m, s_m and 2(m+1)z. Rows carry four zeros after the diagonal and c, s carry two zeros
+//     before m = 0, so that "term absent" cases of the derivative formulas read a zero instead of
+//     branching.
+//  B. The (l, m) pairs are independent once the table exists. They are dealt round-robin to the
+//     G lanes (pair t goes to lane t mod G), so the load is balanced to within one pair for any
+//     l_max, consecutive lanes work on consecutive m of the same degree (their table reads and
+//     their writes into the output image are consecutive words: no bank conflicts), and there is
+//     no per-lane recurrence state, hence no serial dependence between a lane's steps.
 //
 // Data movement. The P points' complete output rows are built in shared memory exactly as they
-// lie in global memory ([P][ny], [P][3][ny], [P][9][ny] are contiguous spans of the outputs) and
-// copied out by the whole warp with fully coalesced stores. When even a single point's rows do
-// not fit, the degrees are cut into bands of consecutive l and the image holds one band of
-// columns at a time. c_m, s_m and 2(m+1)z of each point are computed once and kept in shared
-// memory; the prefactor tables are staged into shared memory once per CTA.
+// lie in global memory ([P][ny], [P][3][ny], [P][9][ny] are contiguous spans of the outputs).
+// Each span is handed to the TMA engine as a 1-D bulk store (cp.async.bulk.global.shared::cta);
+// because a span may start at any 4- or 8-byte boundary, its image is placed in shared memory at
+// the same offset modulo 16 bytes, the few elements before the first and after the last 16-byte
+// boundary are written with plain stores, and the aligned body goes through the engine. When even
+// one point's rows do not fit shared memory the degrees are cut into bands of consecutive l; the
+// image then holds one band of columns at a time and is copied out with coalesced plain stores.
 //
-// No inter-warp, inter-CTA or inter-GPU communication; the only barrier is the one after the
-// table load. Replaces spherical_harmonics_kernel (sphericart/src/sphericart_impl.cu:207-615)
-// and, for the VJP, the reference's materialise-then-reduce backward
-// (sphericart-torch/python/sphericart/torch/register.py:90-108).
+// No inter-warp, inter-CTA or inter-GPU communication; the only block-wide barrier is the one
+// after the prefactor tables are staged. Replaces spherical_harmonics_kernel
+// (sphericart/src/sphericart_impl.cu:207-615) and, for the VJP, the reference's
+// materialise-then-reduce backward (sphericart-torch/python/sphericart/torch/register.py:90-108).
 #pragma once
 
+#include <cstdint>
+
 #include "sph_core.cuh"
+#include "sph_tile.cuh"  // bulk-store helpers
 
 namespace sph_b200 {
 
-// Layout of the host-built plan (ints, in global memory, staged to shared memory):
-//   [0] number of bands   [1] slots per lane (channel list length, -1 terminated)
-//   then per band: l_lo, l_hi, steps (largest per-lane step count), G * slots channel ids
-constexpr int PLAN_HEADER = 2;
-constexpr int PLAN_BAND_HEADER = 3;
+constexpr int MAX_BANDS = 32;
+constexpr int BAND_ROW_PAD = 4;  // zeros after the diagonal of every Q row
+
+// Row stride of the per-point Q table: room for the padding, and even so that lanes working on
+// different rows at the same distance from the diagonal hit different banks.
+__host__ __device__ constexpr int band_row_stride(int l_max) { return (l_max + 1 + BAND_ROW_PAD) + ((l_max + 1 + BAND_ROW_PAD) & 1); }
+
+// Elements of per-point state: 2 + (l_max+1) for c, the same for s, l_max+1 for 2(m+1)z, the Q table.
+__host__ __device__ constexpr int band_point_state(int l_max) {
+    return 2 * (l_max + 3) + (l_max + 1) + (l_max + 1) * band_row_stride(l_max);
+}
+
+// Round an element count up so that the next region starts 16-byte aligned.
+template <typename T> __host__ __device__ constexpr int align16_elems(int n) {
+    constexpr int q = 16 / int(sizeof(T));
+    return (n + q - 1) / q * q;
+}
+
+// Image regions of one warp (elements): each has one 16-byte slot of slack for the alignment shift.
+template <typename T> __host__ __device__ constexpr int band_region(int points, int comps, int cols) {
+    return align16_elems<T>(points * comps * cols) + 16 / int(sizeof(T));
+}
 
 template <typename T> struct BandArgs {
     const T* xyz;
@@ -38,44 +66,48 @@ template <typename T> struct BandArgs {
     T* sph;
     T* dsph;
     T* ddsph;
-    const T* sph_grad;   // VJP only
-    T* xyz_grad;         // VJP only
-    const T* tables;     // F then K, n_table(l_max) entries each
-    const int* plan;
+    const T* sph_grad;  // VJP only
+    T* xyz_grad;        // VJP only
+    const T* tables;    // F then K, n_table(l_max) entries each
     int l_max;
-    int plan_ints;
-    int image_elems;     // per-warp image size in elements of T
+    int nbands;
+    int max_cols;       // widest band, columns
+    int use_bulk;       // single band and TMA copy-out allowed
+    short band_lo[MAX_BANDS + 1];  // band b covers degrees band_lo[b] .. band_lo[b+1] - 1
 };
 
 template <typename T, int LEVEL, bool NORM, int G, bool VJP>
-__global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
+__global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ BandArgs<T> a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int P = 32 / G;
-    constexpr int NCOMP = level_components(LEVEL);
     const int L = a.l_max;
     const int ny = (L + 1) * (L + 1);
     const int nq = (L + 1) * (L + 2) / 2;
+    const int RS = band_row_stride(L);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    const int g = lane % G;    // lane within the point's group
-    const int pt = lane / G;   // point slot within the warp
+    const int g = lane % G;   // lane within the point's group
+    const int pt = lane / G;  // point slot within the warp
 
-    // shared memory carve-up: tables | per-warp (c, s, 2mz) | per-warp image | plan
+    // shared memory carve-up: F | K | per warp: P point states, then the image regions
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
-    const int csz_elems = P * 3 * (L + 1);
-    T* warp_base = sK + nq + size_t(warp) * (csz_elems + a.image_elems);
-    T* sc = warp_base + pt * 3 * (L + 1);
-    T* ss = sc + (L + 1);
+    const int state_elems = align16_elems<T>(P * band_point_state(L));
+    const int reg0 = VJP ? align16_elems<T>(P * ny) : band_region<T>(P, 1, a.max_cols);
+    const int reg1 = (!VJP && LEVEL >= 1) ? band_region<T>(P, 3, a.max_cols) : 0;
+    const int reg2 = (!VJP && LEVEL >= 2) ? band_region<T>(P, 9, a.max_cols) : 0;
+    T* warp_base = sF + align16_elems<T>(2 * nq) + size_t(warp) * (state_elems + reg0 + reg1 + reg2);
+    T* state = warp_base + pt * band_point_state(L);
+    T* sc = state + 2;             // sc[-2], sc[-1] are zeros
+    T* ss = sc + (L + 1) + 2;      // ss[-2], ss[-1] are zeros
     T* stz = ss + (L + 1);
-    T* image = warp_base + csz_elems;
-    int* splan = reinterpret_cast<int*>(sK + nq + size_t(nwarps) * (csz_elems + a.image_elems));
+    T* sQ = stz + (L + 1);         // sQ[l * RS + m]
+    T* region0 = warp_base + state_elems;
+    T* region1 = region0 + reg0;
+    T* region2 = region1 + reg1;
 
     for (int e = threadIdx.x; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
-    for (int e = threadIdx.x; e < a.plan_ints; e += blockDim.x) splan[e] = a.plan[e];
     __syncthreads();
-    const int nbands = splan[0];
-    const int slots = splan[1];
 
     const long long ngroups = (a.n + P - 1) / P;
     const long long stride = (long long)gridDim.x * nwarps;
@@ -102,14 +134,16 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
         const T x2 = x * x, y2 = y * y, xy = x * y;
         const T rho = x2 + y2;
 
-        __syncwarp();  // the previous group's readers of c/s/tz and of the image are done
+        __syncwarp();  // the previous group's phase B has finished reading the state
 
-        // c_m, s_m, 2(m+1)z: every lane of the group runs the recurrence, lane g keeps m = g mod G
+        // ---- phase A1: c_m, s_m, 2(m+1)z. Every lane of the group runs the (serial) recurrence,
+        // lane g keeps the entries m = g mod G.
         {
             T cc = T(1), cs = T(0);
             const T twoz = z + z;
             T ctz = twoz;
             if (g == 0) {
+                sc[-2] = sc[-1] = ss[-2] = ss[-1] = T(0);
                 sc[0] = cc;
                 ss[0] = cs;
                 stz[0] = ctz;
@@ -127,24 +161,61 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
                 }
             }
         }
+        __syncwarp();
+
+        // ---- phase A2: the Q table, one degree per lane, downward in m
+        for (int l = g; l <= L; l += G) {
+            T* row = sQ + l * RS;
+            const T* Kl = sK + tri(l, 0);
+            T q2 = Kl[l];  // Q_l^l is tabulated
+            row[l] = q2;
+#pragma unroll
+            for (int j = 1; j <= BAND_ROW_PAD; ++j) row[l + j] = T(0);
+            if (l >= 1) {
+                T q1 = -z * q2;  // Q_l^{l-1}
+                row[l - 1] = q1;
+                for (int m = l - 2; m >= 0; --m) {
+                    const T q0 = Kl[m] * (stz[m] * q1 + rho * q2);
+                    row[m] = q0;
+                    q2 = q1;
+                    q1 = q0;
+                }
+            }
+        }
+
+        // output images: placed so that shared and global addresses agree modulo 16 bytes
+        T* gsph = VJP ? nullptr : a.sph + first * ny;
+        T* gd = (VJP || LEVEL < 1) ? nullptr : a.dsph + first * 3 * ny;
+        T* gdd = (VJP || LEVEL < 2) ? nullptr : a.ddsph + first * 9 * ny;
+        int shift0 = 0, shift1 = 0, shift2 = 0;
+        if (a.use_bulk) {
+            shift0 = int((reinterpret_cast<uintptr_t>(gsph) & 15u) / sizeof(T));
+            if constexpr (LEVEL >= 1) shift1 = int((reinterpret_cast<uintptr_t>(gd) & 15u) / sizeof(T));
+            if constexpr (LEVEL >= 2) shift2 = int((reinterpret_cast<uintptr_t>(gdd) & 15u) / sizeof(T));
+        }
+        T* image0 = region0 + shift0;
+        T* image1 = region1 + shift1;
+        T* image2 = region2 + shift2;
 
         [[maybe_unused]] T ax = T(0), ay = T(0), az = T(0);  // VJP accumulators
         if constexpr (VJP) {
-            // stage the P rows of the upstream gradient (one contiguous span) into the image
+            // the P rows of the upstream gradient are one contiguous span: coalesced load
             const T* gsrc = a.sph_grad + first * ny;
-            for (int e = lane; e < nvalid * ny; e += 32) image[e] = gsrc[e];
+            for (int e = lane; e < nvalid * ny; e += 32) region0[e] = gsrc[e];
+        } else {
+            // the engine must be done reading the images of the previous group
+            if (a.use_bulk && lane == 0) bulk_wait_read_all();
         }
-        __syncwarp();
+        __syncwarp();  // table, c/s and (VJP) gradient rows visible; images free
 
-        for (int b = 0; b < nbands; ++b) {
-            const int* band = splan + PLAN_HEADER + b * (PLAN_BAND_HEADER + G * slots);
-            const int l_lo = band[0], l_hi = band[1], nsteps = band[2];
-            const int kb = l_lo * l_lo;                       // first column of the band
-            const int cols = (l_hi + 1) * (l_hi + 1) - kb;    // columns in the band
-            T* img_sph = image + pt * cols;
-            T* img_d = image + P * cols + pt * 3 * cols;
-            T* img_dd = image + 4 * P * cols + pt * 9 * cols;
-            const T* grow = image + pt * ny;  // VJP: this point's upstream-gradient row
+        for (int b = 0; b < a.nbands; ++b) {
+            const int l_lo = a.band_lo[b], l_hi = a.band_lo[b + 1] - 1;
+            const int kb = l_lo * l_lo;                     // first column of the band
+            const int cols = (l_hi + 1) * (l_hi + 1) - kb;  // columns in the band
+            T* img_sph = image0 + pt * cols - kb;           // indexed by the global column k
+            T* img_d = image1 + pt * 3 * cols - kb;
+            T* img_dd = image2 + pt * 9 * cols - kb;
+            const T* grow = region0 + pt * ny;              // VJP: this point's upstream-gradient row
 
             auto put = [&](int k, Column<T> v) {
                 if constexpr (NORM && LEVEL >= 1) to_cartesian<T, LEVEL>(v, us);
@@ -154,23 +225,22 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
                     ay += gk * v.gy;
                     az += gk * v.gz;
                 } else {
-                    const int kc = k - kb;
-                    img_sph[kc] = v.y;
+                    img_sph[k] = v.y;
                     if constexpr (LEVEL >= 1) {
-                        img_d[kc] = v.gx;
-                        img_d[cols + kc] = v.gy;
-                        img_d[2 * cols + kc] = v.gz;
+                        img_d[k] = v.gx;
+                        img_d[cols + k] = v.gy;
+                        img_d[2 * cols + k] = v.gz;
                     }
                     if constexpr (LEVEL >= 2) {
-                        img_dd[0 * cols + kc] = v.hxx;
-                        img_dd[1 * cols + kc] = v.hxy;
-                        img_dd[2 * cols + kc] = v.hxz;
-                        img_dd[3 * cols + kc] = v.hxy;
-                        img_dd[4 * cols + kc] = v.hyy;
-                        img_dd[5 * cols + kc] = v.hyz;
-                        img_dd[6 * cols + kc] = v.hxz;
-                        img_dd[7 * cols + kc] = v.hyz;
-                        img_dd[8 * cols + kc] = v.hzz;
+                        img_dd[0 * cols + k] = v.hxx;
+                        img_dd[1 * cols + k] = v.hxy;
+                        img_dd[2 * cols + k] = v.hxz;
+                        img_dd[3 * cols + k] = v.hxy;
+                        img_dd[4 * cols + k] = v.hyy;
+                        img_dd[5 * cols + k] = v.hyz;
+                        img_dd[6 * cols + k] = v.hxz;
+                        img_dd[7 * cols + k] = v.hyz;
+                        img_dd[8 * cols + k] = v.hzz;
                     }
                 }
             };
@@ -195,52 +265,45 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
                 }
             }
 
-            // flat loop over this lane's channels
-            const int* mine = band + PLAN_BAND_HEADER + g * slots;
-            int ci = 0;
-            int l = valid ? mine[0] : -1;
-            int m = l;
-            T q1 = T(0), q2 = T(0);                     // Q_l^{m+1},     Q_l^{m+2}
-            [[maybe_unused]] T p1 = T(0), p2 = T(0);    // Q_{l-1}^{m+1}, Q_{l-1}^{m+2}
-            [[maybe_unused]] T r1 = T(0), r2 = T(0);    // Q_{l-2}^{m+1}, Q_{l-2}^{m+2}
-            for (int step = 0; step < nsteps; ++step) {
-                if (l < 0) continue;
-                const int rl = tri(l, 0);
-                const T tzm = stz[m];
+            // ---- phase B: pairs (l, m), l >= 2, dealt round-robin to the group's lanes
+            int l = l_lo < 2 ? 2 : l_lo;
+            int m = g;
+            while (l <= l_hi && m > l) {
+                m -= l + 1;
+                ++l;
+            }
+            if (!valid) l = l_hi + 1;
+            while (l <= l_hi) {
+                const T* Ql = sQ + l * RS;
+                const T f = sF[tri(l, m)];
                 const T cm = sc[m], sm = ss[m];
-                // Q_l^m: Q_l^l is tabulated, Q_l^{l-1} = -z Q_l^l, then the recurrence
-                const T q0 = (m == l) ? sK[rl + l] : ((m == l - 1) ? -z * q1 : sK[rl + m] * (tzm * q1 + rho * q2));
-                const T f = sF[rl + m];
-                const T pq = q0 * f;
-                Column<T> vp{}, vm{};
+                const T pq = Ql[m] * f;
+                Column<T> vp{}, vm{};  // +m (cosine-like) and -m (sine-like) columns
                 vp.y = pq * cm;
                 vm.y = pq * sm;
                 if constexpr (LEVEL >= 1) {
-                    // Q_{l-1}^m by the same recurrence with row l-1 of K, started from Q_{l-1}^{l-1}
-                    const int rl1 = rl - l;  // tri(l-1, 0)
-                    const T p0 = (m >= l) ? T(0) : ((m == l - 1) ? sK[rl1 + m] : sK[rl1 + m] * (tzm * p1 + rho * p2));
-                    const int m1 = m >= 1 ? m - 1 : 0;
-                    const T cm1 = sc[m1], sm1 = ss[m1];
+                    const T* Ql1 = Ql - RS;
+                    const T q1a = Ql1[m + 1];  // Q_{l-1}^{m+1}, zero past the diagonal
+                    const T q1b = Ql1[m];      // Q_{l-1}^{m}
+                    const T cm1 = sc[m - 1], sm1 = ss[m - 1];
                     const T fm = T(m);
                     const T pqm = pq * fm;
                     const T pqs = pqm * sm1, pqc = pqm * cm1;
-                    const T pdq = f * p1;
+                    const T pdq = f * q1a;
                     const T pdqx = pdq * x, pdqy = pdq * y;
                     vm.gx = pdqx * sm + pqs;
                     vp.gx = pdqx * cm + pqc;
                     vm.gy = pdqy * sm + pqc;
                     vp.gy = pdqy * cm - pqs;
                     const T flm = T(l + m);
-                    const T pdz = f * flm * p0;
+                    const T pdz = f * flm * q1b;
                     vm.gz = pdz * sm;
                     vp.gz = pdz * cm;
                     if constexpr (LEVEL >= 2) {
-                        const int rl2 = rl1 - (l - 1);  // tri(l-2, 0)
-                        const T r0 = (m >= l - 1) ? T(0)
-                                                  : ((m == l - 2) ? sK[rl2 + m] : sK[rl2 + m] * (tzm * r1 + rho * r2));
-                        const int m2 = m >= 2 ? m - 2 : 0;
-                        const T cm2 = sc[m2], sm2 = ss[m2];
-                        const T A = f * p1, D = f * p0, B = f * r2, E = f * r1, C = f * r0;
+                        const T* Ql2 = Ql1 - RS;
+                        const T cm2 = sc[m - 2], sm2 = ss[m - 2];
+                        const T A = f * q1a, D = f * q1b;
+                        const T B = f * Ql2[m + 2], E = f * Ql2[m + 1], C = f * Ql2[m];
                         const T fmm = T(m * (m - 1));
                         const T Pc = fmm * pq * cm2, Ps = fmm * pq * sm2;
                         const T f2m = T(2 * m);
@@ -257,64 +320,59 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
                         vm.hxz = x * flm * E * sm + flm * D * fm * sm1;
                         vp.hyz = y * flm * E * cm - flm * D * fm * sm1;
                         vm.hyz = y * flm * E * sm + flm * D * fm * cm1;
-                        r2 = r1;
-                        r1 = r0;
                     }
-                    p2 = p1;
-                    p1 = p0;
                 }
-                q2 = q1;
-                q1 = q0;
                 const int mid = l * l + l;
                 put(mid + m, vp);
-                if (m > 0) {
-                    put(mid - m, vm);
-                    --m;
-                } else {
-                    // next channel: rows l-1 and l-2 start from "nothing above the diagonal"
-                    ++ci;
-                    l = mine[ci];
-                    m = l;
-                    if constexpr (LEVEL >= 1) p1 = p2 = T(0);
-                    if constexpr (LEVEL >= 2) r1 = r2 = T(0);
+                if (m > 0) put(mid - m, vm);
+                m += G;
+                while (l <= l_hi && m > l) {
+                    m -= l + 1;
+                    ++l;
                 }
             }
 
             if constexpr (!VJP) {
-                __syncwarp();  // image complete
-                const long long row0 = first;
-                if (cols == ny) {
-                    // the image IS the global layout of these points: three linear copies
-                    T* dst = a.sph + row0 * ny;
-                    for (int e = lane; e < nvalid * ny; e += 32) dst[e] = image[e];
-                    if constexpr (LEVEL >= 1) {
-                        T* dst1 = a.dsph + row0 * 3 * ny;
-                        const T* src1 = image + P * cols;
-                        for (int e = lane; e < nvalid * 3 * ny; e += 32) dst1[e] = src1[e];
-                    }
-                    if constexpr (LEVEL >= 2) {
-                        T* dst2 = a.ddsph + row0 * 9 * ny;
-                        const T* src2 = image + 4 * P * cols;
-                        for (int e = lane; e < nvalid * 9 * ny; e += 32) dst2[e] = src2[e];
-                    }
+                if (a.use_bulk) {
+                    // single band: each image is one span of the output. Elements before the first and
+                    // after the last 16-byte boundary go out with plain stores, the body through TMA.
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    constexpr int Q16 = 16 / int(sizeof(T));
+                    auto copy_out = [&](T* gdst, const T* img, int shift, int count) {
+                        const int head = shift == 0 ? 0 : (Q16 - shift < count ? Q16 - shift : count);
+                        const int body = (count - head) / Q16 * Q16;
+                        const int tail = count - head - body;
+                        if (lane < head) gdst[lane] = img[lane];
+                        if (lane >= 8 && lane - 8 < tail) gdst[head + body + lane - 8] = img[head + body + lane - 8];
+                        if (lane == 0 && body > 0)
+                            bulk_store_smem_to_global(gdst + head, img + head, unsigned(body) * unsigned(sizeof(T)));
+                    };
+                    copy_out(gsph, image0, shift0, nvalid * ny);
+                    if constexpr (LEVEL >= 1) copy_out(gd, image1, shift1, nvalid * 3 * ny);
+                    if constexpr (LEVEL >= 2) copy_out(gdd, image2, shift2, nvalid * 9 * ny);
+                    if (lane == 0) bulk_commit();
                 } else {
-                    // one band of columns: a fragment of `cols` elements per (point, component)
-                    for (int r = 0; r < nvalid; ++r)
-                        for (int e = lane; e < cols; e += 32) a.sph[(row0 + r) * ny + kb + e] = image[r * cols + e];
-                    if constexpr (LEVEL >= 1) {
-                        const T* src1 = image + P * cols;
-                        for (int r = 0; r < nvalid * 3; ++r)
-                            for (int e = lane; e < cols; e += 32)
-                                a.dsph[(row0 * 3 + r) * ny + kb + e] = src1[r * cols + e];
+                    __syncwarp();  // image complete
+                    if (cols == ny) {
+                        for (int e = lane; e < nvalid * ny; e += 32) gsph[e] = image0[e];
+                        if constexpr (LEVEL >= 1)
+                            for (int e = lane; e < nvalid * 3 * ny; e += 32) gd[e] = image1[e];
+                        if constexpr (LEVEL >= 2)
+                            for (int e = lane; e < nvalid * 9 * ny; e += 32) gdd[e] = image2[e];
+                    } else {
+                        // one band of columns: a fragment of `cols` elements per (point, component)
+                        for (int r = 0; r < nvalid; ++r)
+                            for (int e = lane; e < cols; e += 32) gsph[size_t(r) * ny + kb + e] = image0[r * cols + e];
+                        if constexpr (LEVEL >= 1)
+                            for (int r = 0; r < nvalid * 3; ++r)
+                                for (int e = lane; e < cols; e += 32) gd[size_t(r) * ny + kb + e] = image1[r * cols + e];
+                        if constexpr (LEVEL >= 2)
+                            for (int r = 0; r < nvalid * 9; ++r)
+                                for (int e = lane; e < cols; e += 32) gdd[size_t(r) * ny + kb + e] = image2[r * cols + e];
                     }
-                    if constexpr (LEVEL >= 2) {
-                        const T* src2 = image + 4 * P * cols;
-                        for (int r = 0; r < nvalid * 9; ++r)
-                            for (int e = lane; e < cols; e += 32)
-                                a.ddsph[(row0 * 9 + r) * ny + kb + e] = src2[r * cols + e];
-                    }
+                    __syncwarp();  // image free for the next band
                 }
-                __syncwarp();  // image free for the next band
             }
         }
 
@@ -333,6 +391,8 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const BandArgs<T> a) {
             }
         }
     }
+    // shared memory must outlive the engine's reads
+    if (!VJP && a.use_bulk && lane == 0) bulk_wait_read_all();
 }
 
 }  // namespace sph_b200

@@ -30,6 +30,8 @@ template <typename T, int LMAX> struct TileLaunch {
 };
 
 // Band kernels, run-time l_max. G lanes per point.
+constexpr int BAND_MAX_BANDS = 32;
+
 template <typename T> struct BandLaunchArgs {
     const T* xyz;
     long long n;
@@ -39,10 +41,11 @@ template <typename T> struct BandLaunchArgs {
     const T* sph_grad;
     T* xyz_grad;
     const T* d_tables;
-    const int* d_plan;
     int l_max;
-    int plan_ints;
-    int image_elems;
+    int nbands;
+    int max_cols;
+    bool use_bulk;
+    short band_lo[BAND_MAX_BANDS + 1];
     int warps;
     size_t smem;
 };

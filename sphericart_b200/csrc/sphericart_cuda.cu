@@ -118,109 +118,112 @@ template <typename T> void build_tables(int l_max, T* out) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Band-kernel plan: lanes per point, bands of degrees, per-lane channel lists.
+// Band-kernel plan: lanes per point, warps per CTA, bands of degrees, shared-memory size.
 struct BandPlan {
-    int lanes = 1;               // G
-    int warps = 1;               // warps per CTA
-    int image_elems = 0;         // per-warp image, elements of T
-    size_t smem = 0;             // dynamic shared memory per CTA
-    std::vector<int> ints;       // device plan (see sph_band.cuh)
+    int lanes = 1;      // G
+    int warps = 1;      // warps per CTA
+    int nbands = 1;
+    int max_cols = 0;   // widest band, columns
+    bool single_band = true;
+    short band_lo[BAND_MAX_BANDS + 1] = {};
+    size_t smem = 0;    // dynamic shared memory per CTA
+    bool feasible = true;
 };
+
+// Sizes shared with the kernel (sph_band.cuh), restated for a run-time element size.
+size_t band_align16(size_t elems, size_t elem) {
+    const size_t q = 16 / elem;
+    return (elems + q - 1) / q * q;
+}
+int band_row_stride_host(int l_max) { return (l_max + 5) + ((l_max + 5) & 1); }
+size_t band_point_state_host(int l_max) {
+    return 2 * size_t(l_max + 3) + size_t(l_max + 1) + size_t(l_max + 1) * band_row_stride_host(l_max);
+}
 
 // kind: 0..2 = forward level, 3 = VJP.
 BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
     const int L = l_max;
-    const int ny = n_columns(L);
-    const int nq = n_table(L);
+    const size_t ny = size_t(n_columns(L));
+    const size_t nq = size_t(n_table(L));
     const bool vjp = kind == 3;
-    const int ncomp = vjp ? 1 : level_components(kind);
-    const size_t row_bytes = size_t(ncomp) * ny * elem;  // one point's image (VJP: its sph_grad row)
-    const size_t table_bytes = 2 * size_t(nq) * elem;
+    const size_t ncomp = vjp ? 1 : size_t(level_components(kind));
+    const size_t table_elems = band_align16(2 * nq, elem);
+    const size_t slack = 16 / elem;
 
-    // lanes per point: the smallest power of two whose 32/G-point image stays within the
-    // per-warp budget, but never more lanes than there are channels worth sharing
+    auto per_warp_elems = [&](int P, size_t cols) {
+        size_t e = band_align16(size_t(P) * band_point_state_host(L), elem);
+        if (vjp) return e + band_align16(size_t(P) * ny, elem);
+        e += band_align16(size_t(P) * cols, elem) + slack;
+        if (kind >= 1) e += band_align16(size_t(P) * 3 * cols, elem) + slack;
+        if (kind >= 2) e += band_align16(size_t(P) * 9 * cols, elem) + slack;
+        return e;
+    };
+
+    // Lanes per point. The pair loop is balanced for any G, so G is chosen for occupancy and for
+    // amortising the per-group prologue: about four pairs per lane at least, and a warp's images
+    // within the budget.
     const size_t budget = size_t(knobs().band_image_kb) * 1024;
-    int G = 1;
-    while (G < 32 && size_t(32 / G) * row_bytes > budget) G *= 2;
+    const int pairs = n_table(L) - 3;
+    int G = 32;
+    while (G > 1 && pairs / G < 4) G /= 2;
+    while (G < 32 && per_warp_elems(32 / G, ny) * elem > budget) G *= 2;
     const int forced = knobs().band_lanes;
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16 || forced == 32) G = forced;
     const int P = 32 / G;
 
-    // bands: everything in one band when a point's rows fit, else consecutive degrees per band
-    const size_t fixed = table_bytes + 4096;  // tables, plan, slack
-    const size_t csz_bytes = size_t(P) * 3 * (L + 1) * elem;
-    const size_t image_limit = smem_limit > fixed + csz_bytes ? smem_limit - fixed - csz_bytes : 0;
-    std::vector<std::pair<int, int>> bands;
-    if (size_t(P) * row_bytes <= image_limit || vjp) {
-        bands.push_back({0, L});
-    } else {
-        const size_t band_budget = std::min(image_limit, size_t(96) * 1024);
-        int lo = 0;
-        while (lo <= L) {
-            int hi = lo;
-            while (hi + 1 <= L &&
-                   size_t(P) * ncomp * size_t((hi + 2) * (hi + 2) - lo * lo) * elem <= band_budget) {
-                ++hi;
-            }
-            bands.push_back({lo, hi});
-            lo = hi + 1;
-        }
-    }
-
     BandPlan plan;
     plan.lanes = G;
-    int max_cols = 0;
-    for (auto& b : bands) max_cols = std::max(max_cols, (b.second + 1) * (b.second + 1) - b.first * b.first);
-    plan.image_elems = vjp ? P * ny : P * ncomp * max_cols;
-
-    // longest-first greedy deal of the channels l >= 2 of each band to the G lanes
-    std::vector<std::vector<std::vector<int>>> lists(bands.size(), std::vector<std::vector<int>>(G));
-    std::vector<int> band_steps(bands.size(), 0);
-    size_t slots = 1;
-    for (size_t b = 0; b < bands.size(); ++b) {
-        std::vector<int> load(G, 0);
-        for (int l = bands[b].second; l >= std::max(2, bands[b].first); --l) {
-            const int lane = int(std::min_element(load.begin(), load.end()) - load.begin());
-            lists[b][lane].push_back(l);
-            load[lane] += l + 1;
+    const size_t usable = smem_limit > table_elems * elem + 1024 ? smem_limit - table_elems * elem - 1024 : 0;
+    if (vjp || per_warp_elems(P, ny) * elem <= usable) {
+        plan.nbands = 1;
+        plan.band_lo[0] = 0;
+        plan.band_lo[1] = short(L + 1);
+        plan.max_cols = int(ny);
+    } else {
+        // consecutive degrees per band, each band's image within ~half of shared memory
+        const size_t band_budget = std::min(usable, size_t(112) * 1024);
+        int nb = 0, lo = 0, max_cols = 0;
+        while (lo <= L) {
+            int hi = lo;
+            auto cols_of = [&](int h) { return size_t((h + 1) * (h + 1) - lo * lo); };
+            if (per_warp_elems(P, cols_of(hi)) * elem > usable) { plan.feasible = false; break; }
+            while (hi + 1 <= L && per_warp_elems(P, cols_of(hi + 1)) * elem <= band_budget) ++hi;
+            if (nb >= BAND_MAX_BANDS) { plan.feasible = false; break; }
+            plan.band_lo[nb++] = short(lo);
+            max_cols = std::max(max_cols, int(cols_of(hi)));
+            lo = hi + 1;
         }
-        band_steps[b] = *std::max_element(load.begin(), load.end());
-        for (int g = 0; g < G; ++g) slots = std::max(slots, lists[b][g].size() + 1);
-    }
-    plan.ints.push_back(int(bands.size()));
-    plan.ints.push_back(int(slots));
-    for (size_t b = 0; b < bands.size(); ++b) {
-        plan.ints.push_back(bands[b].first);
-        plan.ints.push_back(bands[b].second);
-        plan.ints.push_back(band_steps[b]);
-        for (int g = 0; g < G; ++g) {
-            for (size_t s = 0; s < slots; ++s) plan.ints.push_back(s < lists[b][g].size() ? lists[b][g][s] : -1);
-        }
+        plan.band_lo[nb] = short(L + 1);
+        plan.nbands = nb;
+        plan.max_cols = max_cols;
+        plan.single_band = false;
     }
 
-    // warps per CTA: as many as fit next to the shared tables, at most 4
-    const size_t per_warp = csz_bytes + size_t(plan.image_elems) * elem;
-    const size_t plan_bytes = plan.ints.size() * sizeof(int);
+    // warps per CTA: up to 4; pick the count that packs the most warps into an SM
+    const size_t per_warp = per_warp_elems(P, size_t(plan.max_cols)) * elem;
+    const size_t table_bytes = table_elems * elem;
     int warps = 4;
     const int forced_warps = knobs().band_warps;
-    if (forced_warps >= 1 && forced_warps <= 4) warps = forced_warps;
-    while (warps > 1 && table_bytes + plan_bytes + warps * per_warp > smem_limit) --warps;
-    // prefer a CTA size that packs the SM: with W warps per CTA, floor(limit / cta) CTAs fit
-    if (forced_warps == 0) {
-        int best = warps;
-        size_t best_warps_per_sm = 0;
-        for (int w = warps; w >= 1; --w) {
-            const size_t cta = table_bytes + plan_bytes + w * per_warp + 1024;
-            const size_t n_cta = std::min<size_t>(32, (smem_limit + 1024) / cta);
-            if (n_cta * w > best_warps_per_sm) {
-                best_warps_per_sm = n_cta * w;
+    if (forced_warps >= 1 && forced_warps <= 4) {
+        warps = forced_warps;
+    } else {
+        int best = 1;
+        size_t best_per_sm = 0;
+        for (int w = 4; w >= 1; --w) {
+            const size_t cta = table_bytes + w * per_warp;
+            if (cta > smem_limit) continue;
+            const size_t n_cta = std::min<size_t>(32, (smem_limit + 1024) / (cta + 1024));
+            const size_t per_sm = std::min<size_t>(64, n_cta * w);
+            if (per_sm > best_per_sm) {
+                best_per_sm = per_sm;
                 best = w;
             }
         }
         warps = best;
     }
     plan.warps = warps;
-    plan.smem = table_bytes + plan_bytes + warps * per_warp;
+    plan.smem = table_bytes + warps * per_warp;
+    if (plan.smem > smem_limit) plan.feasible = false;
     return plan;
 }
 
@@ -229,35 +232,46 @@ template <typename T> struct CalculatorState {
     std::mutex mutex;
     BandPlan plans[4];
     bool plan_ready[4] = {false, false, false, false};
-    struct PerDevice {
-        T* tables = nullptr;
-        int* plan[4] = {nullptr, nullptr, nullptr, nullptr};
-    };
-    PerDevice dev[MAX_DEVICES];
+    T* tables[MAX_DEVICES] = {};  // device copies of the F and K tables, made on first use per device
 };
 
 template <typename T>
 void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int kind, int device, size_t smem_limit,
-                    const BandPlan*& plan, const T*& d_tables, const int*& d_plan) {
+                    const BandPlan*& plan, const T*& d_tables) {
     std::lock_guard<std::mutex> lock(st.mutex);
     if (!st.plan_ready[kind]) {
         st.plans[kind] = make_band_plan(l_max, kind, sizeof(T), smem_limit);
         st.plan_ready[kind] = true;
     }
-    auto& d = st.dev[device];
-    if (d.tables == nullptr) {
+    if (st.tables[device] == nullptr) {
         const size_t bytes = 2 * size_t(n_table(l_max)) * sizeof(T);
-        check(cudaMalloc(reinterpret_cast<void**>(&d.tables), bytes), "cudaMalloc(prefactors)");
-        check(cudaMemcpy(d.tables, host_tables, bytes, cudaMemcpyHostToDevice), "cudaMemcpy(prefactors)");
-    }
-    if (d.plan[kind] == nullptr) {
-        const size_t bytes = st.plans[kind].ints.size() * sizeof(int);
-        check(cudaMalloc(reinterpret_cast<void**>(&d.plan[kind]), bytes), "cudaMalloc(plan)");
-        check(cudaMemcpy(d.plan[kind], st.plans[kind].ints.data(), bytes, cudaMemcpyHostToDevice), "cudaMemcpy(plan)");
+        check(cudaMalloc(reinterpret_cast<void**>(&st.tables[device]), bytes), "cudaMalloc(prefactors)");
+        check(cudaMemcpy(st.tables[device], host_tables, bytes, cudaMemcpyHostToDevice), "cudaMemcpy(prefactors)");
     }
     plan = &st.plans[kind];
-    d_tables = d.tables;
-    d_plan = d.plan[kind];
+    d_tables = st.tables[device];
+}
+
+template <typename T>
+BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, bool vjp, const T* d_tables, const T* xyz,
+                                   long long n, T* sph, T* dsph, T* ddsph, const T* sph_grad, T* xyz_grad) {
+    BandLaunchArgs<T> a{};
+    a.xyz = xyz;
+    a.n = n;
+    a.sph = sph;
+    a.dsph = dsph;
+    a.ddsph = ddsph;
+    a.sph_grad = sph_grad;
+    a.xyz_grad = xyz_grad;
+    a.d_tables = d_tables;
+    a.l_max = l_max;
+    a.nbands = plan.nbands;
+    a.max_cols = plan.max_cols;
+    a.use_bulk = !vjp && plan.single_band && knobs().no_bulk == 0;
+    for (int b = 0; b <= BAND_MAX_BANDS; ++b) a.band_lo[b] = plan.band_lo[b];
+    a.warps = plan.warps;
+    a.smem = plan.smem;
+    return a;
 }
 
 // RAII: run on the device that owns `ptr`, restore the caller's device afterwards.
@@ -364,13 +378,12 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
 
     const BandPlan* plan = nullptr;
     const T* d_tables = nullptr;
-    const int* d_plan = nullptr;
-    band_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, plan, d_tables, d_plan);
-    if (plan->smem > props.smem_optin) {
+    band_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, plan, d_tables);
+    if (!plan->feasible) {
         throw std::runtime_error("sphericart::cuda: l_max is too large for this device's shared memory");
     }
-    BandLaunchArgs<T> a{xyz,      n,      sph,   dsph,           ddsph,           sph_grad,         xyz_grad,
-                        d_tables, d_plan, l_max, int(plan->ints.size()), plan->image_elems, plan->warps, plan->smem};
+    const BandLaunchArgs<T> a =
+        band_launch_args<T>(*plan, l_max, vjp, d_tables, xyz, n, sph, dsph, ddsph, sph_grad, xyz_grad);
     check(band_dispatch<T>(plan->lanes, vjp ? 1 : kind, vjp, normalized, a, scope.device, stream), "band kernel launch");
 }
 
@@ -607,10 +620,10 @@ SPH_CAPI_FAMILY(solid, _f, float)
 // process starts, so a later cudaMalloc from a plugin simply fails, and latency-bound service
 // loops in which cudaMalloc is off limits because it synchronises the device and may block. The
 // calculators above cannot serve such hosts for l_max > 8: their run-time-degree kernel reads the
-// prefactor tables and the lane schedule from device buffers that they cudaMalloc on first use.
+// prefactor tables from a device buffer that they cudaMalloc on first use.
 //
 // This variant runs the same kernel (float64, values + gradients, run-time l_max) with those
-// tables and that schedule placed in a fixed array that is part of the library image, so every GPU
+// tables placed in a fixed array that is part of the library image, so every GPU
 // that loads the library carries NO_ALLOC_SCRATCH_BYTES (16 KiB) of it until the process ends. The
 // function calls no cudaMalloc, cudaFree or any other allocating routine; the caller passes inputs
 // and outputs as usual. The fixed size bounds the degree: l_max <= NO_ALLOC_MAX_L (32).
@@ -629,15 +642,13 @@ SPH_CAPI_FAMILY(solid, _f, float)
 namespace {
 
 constexpr int NO_ALLOC_MAX_L = 32;
-constexpr size_t NO_ALLOC_TABLE_BYTES = 9216;   // 2 * n_table(32) doubles = 8976 bytes, rounded up
-constexpr size_t NO_ALLOC_PLAN_BYTES = 7168;    // lane schedule, ints
-constexpr size_t NO_ALLOC_SCRATCH_BYTES = NO_ALLOC_TABLE_BYTES + NO_ALLOC_PLAN_BYTES;
+constexpr size_t NO_ALLOC_SCRATCH_BYTES = 16384;  // holds 2 * n_table(32) doubles = 8976 bytes
 
 static __device__ __align__(256) unsigned char g_no_alloc_scratch[NO_ALLOC_SCRATCH_BYTES];
 
 struct NoAllocDevice {
     unsigned char* scratch = nullptr;  // device address of g_no_alloc_scratch on this device
-    int resident_l_max = -1;           // whose tables and schedule the array holds now
+    int resident_l_max = -1;           // whose tables the array holds now
 };
 std::mutex g_no_alloc_mutex;
 NoAllocDevice g_no_alloc_devices[sph_b200::MAX_DEVICES];
@@ -658,13 +669,12 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
     DeviceScope scope(xyz);
     const DeviceProps& props = device_props(scope.device);
 
-    // host-side tables and schedule (host heap only)
+    // host-side tables and launch plan (host heap only)
     std::vector<double> tables(2 * size_t(n_table(l_max)));
     build_tables<double>(l_max, tables.data());
     const BandPlan plan = make_band_plan(l_max, /*kind=*/1, sizeof(double), props.smem_optin);
     const size_t table_bytes = tables.size() * sizeof(double);
-    const size_t plan_bytes = plan.ints.size() * sizeof(int);
-    if (table_bytes > NO_ALLOC_TABLE_BYTES || plan_bytes > NO_ALLOC_PLAN_BYTES || plan.smem > props.smem_optin) {
+    if (table_bytes > NO_ALLOC_SCRATCH_BYTES || !plan.feasible) {
         throw std::runtime_error("sphericart::cuda: internal tables do not fit the allocation-free array");
     }
 
@@ -679,25 +689,11 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
     if (dev.resident_l_max != l_max) {
         check(cudaMemcpyAsync(dev.scratch, tables.data(), table_bytes, cudaMemcpyHostToDevice, stream),
               "cudaMemcpyAsync(tables)");
-        check(cudaMemcpyAsync(dev.scratch + NO_ALLOC_TABLE_BYTES, plan.ints.data(), plan_bytes, cudaMemcpyHostToDevice,
-                              stream),
-              "cudaMemcpyAsync(schedule)");
         dev.resident_l_max = l_max;
     }
-    BandLaunchArgs<double> a{xyz,
-                             (long long)n_samples,
-                             sph,
-                             dsph,
-                             nullptr,
-                             nullptr,
-                             nullptr,
-                             reinterpret_cast<const double*>(dev.scratch),
-                             reinterpret_cast<const int*>(dev.scratch + NO_ALLOC_TABLE_BYTES),
-                             l_max,
-                             int(plan.ints.size()),
-                             plan.image_elems,
-                             plan.warps,
-                             plan.smem};
+    const BandLaunchArgs<double> a =
+        band_launch_args<double>(plan, l_max, false, reinterpret_cast<const double*>(dev.scratch), xyz,
+                                 (long long)n_samples, sph, dsph, nullptr, nullptr, nullptr);
     check(band_dispatch<double>(plan.lanes, 1, false, normalized, a, scope.device, stream),
           "band kernel launch (allocation-free)");
 }
