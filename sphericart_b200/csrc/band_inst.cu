@@ -16,9 +16,9 @@ namespace sph_b200 {
 
 namespace {
 
-template <typename T, int LEVEL, bool NORM, int G, bool VJP>
+template <typename T, int LEVEL, bool NORM, int G, bool VJP, bool DIRECT>
 cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t stream) {
-    auto kernel = sph_band_kernel<T, LEVEL, NORM, G, VJP>;
+    auto kernel = sph_band_kernel<T, LEVEL, NORM, G, VJP, DIRECT>;
     // shared memory differs between calculators, so the occupancy query is not cached by kernel
     // alone; it is cheap next to the work these kernels do per launch.
     const int max_blocks = persistent_grid(reinterpret_cast<const void*>(kernel), a.warps * 32, a.smem, device);
@@ -27,7 +27,6 @@ cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t str
     const long long ngroups = (a.n + P - 1) / P;
     const long long want = (ngroups + a.warps - 1) / a.warps;
     const int grid = int(want < max_blocks ? want : max_blocks);
-    static_assert(BAND_MAX_BANDS == MAX_BANDS, "band limits must agree");
     BandArgs<T> k{};
     k.xyz = a.xyz;
     k.n = a.n;
@@ -38,12 +37,24 @@ cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t str
     k.xyz_grad = a.xyz_grad;
     k.tables = a.d_tables;
     k.l_max = a.l_max;
-    k.nbands = a.nbands;
-    k.max_cols = a.max_cols;
-    k.use_bulk = a.use_bulk ? 1 : 0;
-    for (int b = 0; b <= MAX_BANDS; ++b) k.band_lo[b] = a.band_lo[b];
+    k.mode = a.mode;
     kernel<<<grid, a.warps * 32, a.smem, stream>>>(k);
     return cudaGetLastError();
+}
+
+template <typename T, int LEVEL, int G>
+cudaError_t launch_forward(bool normalized, const BandLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    if (a.mode == BAND_DIRECT) {
+        // the direct-store variant exists for whole-warp-per-point launches only
+        if constexpr (G == 32) {
+            return normalized ? launch_band<T, LEVEL, true, G, false, true>(a, device, stream)
+                              : launch_band<T, LEVEL, false, G, false, true>(a, device, stream);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    }
+    return normalized ? launch_band<T, LEVEL, true, G, false, false>(a, device, stream)
+                      : launch_band<T, LEVEL, false, G, false, false>(a, device, stream);
 }
 
 }  // namespace
@@ -52,21 +63,14 @@ template <typename T, int G>
 cudaError_t BandLaunch<T, G>::run(int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
                                   cudaStream_t stream) {
     if (vjp) {
-        return normalized ? launch_band<T, 1, true, G, true>(a, device, stream)
-                          : launch_band<T, 1, false, G, true>(a, device, stream);
+        return normalized ? launch_band<T, 1, true, G, true, false>(a, device, stream)
+                          : launch_band<T, 1, false, G, true, false>(a, device, stream);
     }
     switch (level) {
-        case 0:
-            return normalized ? launch_band<T, 0, true, G, false>(a, device, stream)
-                              : launch_band<T, 0, false, G, false>(a, device, stream);
-        case 1:
-            return normalized ? launch_band<T, 1, true, G, false>(a, device, stream)
-                              : launch_band<T, 1, false, G, false>(a, device, stream);
-        case 2:
-            return normalized ? launch_band<T, 2, true, G, false>(a, device, stream)
-                              : launch_band<T, 2, false, G, false>(a, device, stream);
-        default:
-            return cudaErrorInvalidValue;
+        case 0: return launch_forward<T, 0, G>(normalized, a, device, stream);
+        case 1: return launch_forward<T, 1, G>(normalized, a, device, stream);
+        case 2: return launch_forward<T, 2, G>(normalized, a, device, stream);
+        default: return cudaErrorInvalidValue;
     }
 }
 

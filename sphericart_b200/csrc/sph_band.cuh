@@ -6,23 +6,26 @@
 //
 //  A. The point's whole table Q_l^m (0 <= m <= l <= l_max) is built in shared memory with the
 //     reference's downward-in-m recurrence, one row (one degree) per lane, together with
-//     c_m, s_m and 2(m+1)z. Rows carry four zeros after the diagonal and c, s carry two zeros
-//     before m = 0, so that "term absent" cases of the derivative formulas read a zero instead of
-//     branching.
+//     c_m, s_m and 2(m+1)z. Rows carry four zeros after the diagonal, two all-zero rows precede
+//     row 0, and c, s carry two zeros before m = 0, so that every "term absent" case of the
+//     derivative formulas (and the degrees 0 and 1) reads a zero instead of branching.
 //  B. The (l, m) pairs are independent once the table exists. They are dealt round-robin to the
 //     G lanes (pair t goes to lane t mod G), so the load is balanced to within one pair for any
 //     l_max, consecutive lanes work on consecutive m of the same degree (their table reads and
-//     their writes into the output image are consecutive words: no bank conflicts), and there is
-//     no per-lane recurrence state, hence no serial dependence between a lane's steps.
+//     their output writes are consecutive words), and there is no per-lane recurrence state,
+//     hence no serial dependence between a lane's steps; two pairs are in flight per lane.
 //
-// Data movement. The P points' complete output rows are built in shared memory exactly as they
-// lie in global memory ([P][ny], [P][3][ny], [P][9][ny] are contiguous spans of the outputs).
-// Each span is handed to the TMA engine as a 1-D bulk store (cp.async.bulk.global.shared::cta);
-// because a span may start at any 4- or 8-byte boundary, its image is placed in shared memory at
-// the same offset modulo 16 bytes, the few elements before the first and after the last 16-byte
-// boundary are written with plain stores, and the aligned body goes through the engine. When even
-// one point's rows do not fit shared memory the degrees are cut into bands of consecutive l; the
-// image then holds one band of columns at a time and is copied out with coalesced plain stores.
+// Data movement, two modes chosen on the host:
+//  * IMAGE: the P points' complete output rows are built in shared memory exactly as they lie in
+//    global memory ([P][ny], [P][3][ny], [P][9][ny] are contiguous spans of the outputs) and each
+//    span is handed to the TMA engine as a 1-D bulk store (cp.async.bulk.global.shared::cta).
+//    A span may start at any 4- or 8-byte boundary, so its image is placed in shared memory at the
+//    same offset modulo 16 bytes; the few elements before the first and after the last 16-byte
+//    boundary are written with plain stores and the aligned body goes through the engine.
+//  * DIRECT: for rows so long that an image would leave room for only a few warps per SM, phase B
+//    stores straight to global memory. Consecutive lanes hold consecutive m, so every store
+//    instruction writes one contiguous run of a row; neighbouring runs are written by the same
+//    warp moments later and merge in L2. No image, so many more warps fit and hide latency.
 //
 // No inter-warp, inter-CTA or inter-GPU communication; the only block-wide barrier is the one
 // after the prefactor tables are staged. Replaces spherical_harmonics_kernel
@@ -37,16 +40,18 @@
 
 namespace sph_b200 {
 
-constexpr int MAX_BANDS = 32;
-constexpr int BAND_ROW_PAD = 4;  // zeros after the diagonal of every Q row
+constexpr int BAND_ROW_PAD = 4;    // zeros after the diagonal of every Q row
+constexpr int BAND_ZERO_ROWS = 2;  // all-zero rows standing in for degrees -1 and -2
 
 // Row stride of the per-point Q table: room for the padding, and even so that lanes working on
 // different rows at the same distance from the diagonal hit different banks.
-__host__ __device__ constexpr int band_row_stride(int l_max) { return (l_max + 1 + BAND_ROW_PAD) + ((l_max + 1 + BAND_ROW_PAD) & 1); }
+__host__ __device__ constexpr int band_row_stride(int l_max) {
+    return (l_max + 1 + BAND_ROW_PAD) + ((l_max + 1 + BAND_ROW_PAD) & 1);
+}
 
 // Elements of per-point state: 2 + (l_max+1) for c, the same for s, l_max+1 for 2(m+1)z, the Q table.
 __host__ __device__ constexpr int band_point_state(int l_max) {
-    return 2 * (l_max + 3) + (l_max + 1) + (l_max + 1) * band_row_stride(l_max);
+    return 2 * (l_max + 3) + (l_max + 1) + (l_max + 1 + BAND_ZERO_ROWS) * band_row_stride(l_max);
 }
 
 // Round an element count up so that the next region starts 16-byte aligned.
@@ -60,6 +65,8 @@ template <typename T> __host__ __device__ constexpr int band_region(int points, 
     return align16_elems<T>(points * comps * cols) + 16 / int(sizeof(T));
 }
 
+enum BandMode : int { BAND_IMAGE_BULK = 0, BAND_IMAGE_PLAIN = 1, BAND_DIRECT = 2 };
+
 template <typename T> struct BandArgs {
     const T* xyz;
     long long n;
@@ -70,13 +77,95 @@ template <typename T> struct BandArgs {
     T* xyz_grad;        // VJP only
     const T* tables;    // F then K, n_table(l_max) entries each
     int l_max;
-    int nbands;
-    int max_cols;       // widest band, columns
-    int use_bulk;       // single band and TMA copy-out allowed
-    short band_lo[MAX_BANDS + 1];  // band b covers degrees band_lo[b] .. band_lo[b+1] - 1
+    int mode;           // BAND_IMAGE_BULK or BAND_IMAGE_PLAIN (ignored by the VJP and by DIRECT kernels)
 };
 
-template <typename T, int LEVEL, bool NORM, int G, bool VJP>
+// Everything phase B reads for one (l, m) pair.
+template <typename T, int LEVEL> struct PairInputs {
+    int l, m;
+    T f, q, cm, sm;
+    T q1a, q1b, cm1, sm1;      // Q_{l-1}^{m+1}, Q_{l-1}^{m}, c_{m-1}, s_{m-1}
+    T q2a, q2b, q2c, cm2, sm2; // Q_{l-2}^{m+2}, Q_{l-2}^{m+1}, Q_{l-2}^{m}, c_{m-2}, s_{m-2}
+};
+
+template <typename T, int LEVEL>
+__device__ __forceinline__ PairInputs<T, LEVEL> band_load_pair(int l, int m, int RS, const T* sF, const T* sQ,
+                                                               const T* sc, const T* ss) {
+    PairInputs<T, LEVEL> in;
+    in.l = l;
+    in.m = m;
+    const T* Ql = sQ + l * RS;
+    in.f = sF[tri(l, m)];
+    in.q = Ql[m];
+    in.cm = sc[m];
+    in.sm = ss[m];
+    if constexpr (LEVEL >= 1) {
+        const T* Ql1 = Ql - RS;
+        in.q1a = Ql1[m + 1];
+        in.q1b = Ql1[m];
+        in.cm1 = sc[m - 1];
+        in.sm1 = ss[m - 1];
+    }
+    if constexpr (LEVEL >= 2) {
+        const T* Ql2 = Ql - 2 * RS;
+        in.q2a = Ql2[m + 2];
+        in.q2b = Ql2[m + 1];
+        in.q2c = Ql2[m];
+        in.cm2 = sc[m - 2];
+        in.sm2 = ss[m - 2];
+    }
+    return in;
+}
+
+// Raw columns +m (cosine-like) and -m (sine-like) of one pair; same expressions as the
+// reference's channel code (sphericart/include/templates_core.hpp:201-292, 392-426) with the
+// out-of-range Q entries reading as zero.
+template <typename T, int LEVEL>
+__device__ __forceinline__ void band_eval_pair(const PairInputs<T, LEVEL>& in, T x, T y, T x2, T y2, T xy,
+                                               Column<T>& vp, Column<T>& vm) {
+    const T f = in.f, cm = in.cm, sm = in.sm;
+    const T pq = in.q * f;
+    vp.y = pq * cm;
+    vm.y = pq * sm;
+    if constexpr (LEVEL >= 1) {
+        const T cm1 = in.cm1, sm1 = in.sm1;
+        const T fm = T(in.m);
+        const T pqm = pq * fm;
+        const T pqs = pqm * sm1, pqc = pqm * cm1;
+        const T pdq = f * in.q1a;
+        const T pdqx = pdq * x, pdqy = pdq * y;
+        vm.gx = pdqx * sm + pqs;
+        vp.gx = pdqx * cm + pqc;
+        vm.gy = pdqy * sm + pqc;
+        vp.gy = pdqy * cm - pqs;
+        const T flm = T(in.l + in.m);
+        const T pdz = f * flm * in.q1b;
+        vm.gz = pdz * sm;
+        vp.gz = pdz * cm;
+        if constexpr (LEVEL >= 2) {
+            const T A = f * in.q1a, D = f * in.q1b;
+            const T B = f * in.q2a, E = f * in.q2b, C = f * in.q2c;
+            const T fmm = T(in.m * (in.m - 1));
+            const T Pc = fmm * pq * in.cm2, Ps = fmm * pq * in.sm2;
+            const T f2m = T(2 * in.m);
+            vp.hxx = A * cm + x2 * B * cm + f2m * x * A * cm1 + Pc;
+            vm.hxx = A * sm + x2 * B * sm + f2m * x * A * sm1 + Ps;
+            vp.hyy = A * cm + y2 * B * cm - f2m * y * A * sm1 - Pc;
+            vm.hyy = A * sm + y2 * B * sm + f2m * y * A * cm1 - Ps;
+            const T fz = T((in.l + in.m) * (in.l + in.m - 1));
+            vp.hzz = fz * C * cm;
+            vm.hzz = fz * C * sm;
+            vp.hxy = xy * B * cm + y * A * fm * cm1 - x * A * fm * sm1 - Ps;
+            vm.hxy = xy * B * sm + y * A * fm * sm1 + x * A * fm * cm1 + Pc;
+            vp.hxz = x * flm * E * cm + flm * D * fm * cm1;
+            vm.hxz = x * flm * E * sm + flm * D * fm * sm1;
+            vp.hyz = y * flm * E * cm - flm * D * fm * sm1;
+            vm.hyz = y * flm * E * sm + flm * D * fm * cm1;
+        }
+    }
+}
+
+template <typename T, int LEVEL, bool NORM, int G, bool VJP, bool DIRECT>
 __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ BandArgs<T> a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int P = 32 / G;
@@ -88,25 +177,31 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
     const int nwarps = blockDim.x >> 5;
     const int g = lane % G;   // lane within the point's group
     const int pt = lane / G;  // point slot within the warp
+    constexpr bool direct = DIRECT;  // store straight to global memory, no image
+    static_assert(!(VJP && DIRECT), "the VJP has no output image");
+    const bool bulk = !VJP && !DIRECT && a.mode == BAND_IMAGE_BULK;
 
     // shared memory carve-up: F | K | per warp: P point states, then the image regions
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
     const int state_elems = align16_elems<T>(P * band_point_state(L));
-    const int reg0 = VJP ? align16_elems<T>(P * ny) : band_region<T>(P, 1, a.max_cols);
-    const int reg1 = (!VJP && LEVEL >= 1) ? band_region<T>(P, 3, a.max_cols) : 0;
-    const int reg2 = (!VJP && LEVEL >= 2) ? band_region<T>(P, 9, a.max_cols) : 0;
+    const int reg0 = VJP ? align16_elems<T>(P * ny) : (direct ? 0 : band_region<T>(P, 1, ny));
+    const int reg1 = (!VJP && !direct && LEVEL >= 1) ? band_region<T>(P, 3, ny) : 0;
+    const int reg2 = (!VJP && !direct && LEVEL >= 2) ? band_region<T>(P, 9, ny) : 0;
     T* warp_base = sF + align16_elems<T>(2 * nq) + size_t(warp) * (state_elems + reg0 + reg1 + reg2);
     T* state = warp_base + pt * band_point_state(L);
     T* sc = state + 2;             // sc[-2], sc[-1] are zeros
     T* ss = sc + (L + 1) + 2;      // ss[-2], ss[-1] are zeros
     T* stz = ss + (L + 1);
-    T* sQ = stz + (L + 1);         // sQ[l * RS + m]
+    T* sQ = stz + (L + 1) + BAND_ZERO_ROWS * RS;  // sQ[l * RS + m], rows -2 and -1 are zeros
     T* region0 = warp_base + state_elems;
     T* region1 = region0 + reg0;
     T* region2 = region1 + reg1;
 
     for (int e = threadIdx.x; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
+    // the zero rows and the zeros before c_0, s_0 never change
+    for (int e = g; e < BAND_ZERO_ROWS * RS; e += G) sQ[e - BAND_ZERO_ROWS * RS] = T(0);
+    if (g == 0) sc[-2] = sc[-1] = ss[-2] = ss[-1] = T(0);
     __syncthreads();
 
     const long long ngroups = (a.n + P - 1) / P;
@@ -143,7 +238,6 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
             const T twoz = z + z;
             T ctz = twoz;
             if (g == 0) {
-                sc[-2] = sc[-1] = ss[-2] = ss[-1] = T(0);
                 sc[0] = cc;
                 ss[0] = cs;
                 stz[0] = ctz;
@@ -183,12 +277,13 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
             }
         }
 
-        // output images: placed so that shared and global addresses agree modulo 16 bytes
+        // where this point's rows go
         T* gsph = VJP ? nullptr : a.sph + first * ny;
         T* gd = (VJP || LEVEL < 1) ? nullptr : a.dsph + first * 3 * ny;
         T* gdd = (VJP || LEVEL < 2) ? nullptr : a.ddsph + first * 9 * ny;
+        // image mode: images placed so that shared and global addresses agree modulo 16 bytes
         int shift0 = 0, shift1 = 0, shift2 = 0;
-        if (a.use_bulk) {
+        if (bulk) {
             shift0 = int((reinterpret_cast<uintptr_t>(gsph) & 15u) / sizeof(T));
             if constexpr (LEVEL >= 1) shift1 = int((reinterpret_cast<uintptr_t>(gd) & 15u) / sizeof(T));
             if constexpr (LEVEL >= 2) shift2 = int((reinterpret_cast<uintptr_t>(gdd) & 15u) / sizeof(T));
@@ -196,6 +291,11 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         T* image0 = region0 + shift0;
         T* image1 = region1 + shift1;
         T* image2 = region2 + shift2;
+        // destination of this lane's point, indexed by the column k: the image or global memory
+        T* out_sph = direct ? gsph + size_t(pt) * ny : image0 + pt * ny;
+        T* out_d = direct ? gd + size_t(pt) * 3 * ny : image1 + pt * 3 * ny;
+        T* out_dd = direct ? gdd + size_t(pt) * 9 * ny : image2 + pt * 9 * ny;
+        const T* grow = region0 + pt * ny;  // VJP: this point's upstream-gradient row
 
         [[maybe_unused]] T ax = T(0), ay = T(0), az = T(0);  // VJP accumulators
         if constexpr (VJP) {
@@ -204,175 +304,96 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
             for (int e = lane; e < nvalid * ny; e += 32) region0[e] = gsrc[e];
         } else {
             // the engine must be done reading the images of the previous group
-            if (a.use_bulk && lane == 0) bulk_wait_read_all();
+            if (bulk && lane == 0) bulk_wait_read_all();
         }
         __syncwarp();  // table, c/s and (VJP) gradient rows visible; images free
 
-        for (int b = 0; b < a.nbands; ++b) {
-            const int l_lo = a.band_lo[b], l_hi = a.band_lo[b + 1] - 1;
-            const int kb = l_lo * l_lo;                     // first column of the band
-            const int cols = (l_hi + 1) * (l_hi + 1) - kb;  // columns in the band
-            T* img_sph = image0 + pt * cols - kb;           // indexed by the global column k
-            T* img_d = image1 + pt * 3 * cols - kb;
-            T* img_dd = image2 + pt * 9 * cols - kb;
-            const T* grow = region0 + pt * ny;              // VJP: this point's upstream-gradient row
-
-            auto put = [&](int k, Column<T> v) {
-                if constexpr (NORM && LEVEL >= 1) to_cartesian<T, LEVEL>(v, us);
-                if constexpr (VJP) {
-                    const T gk = grow[k];
-                    ax += gk * v.gx;
-                    ay += gk * v.gy;
-                    az += gk * v.gz;
-                } else {
-                    img_sph[k] = v.y;
-                    if constexpr (LEVEL >= 1) {
-                        img_d[k] = v.gx;
-                        img_d[cols + k] = v.gy;
-                        img_d[2 * cols + k] = v.gz;
-                    }
-                    if constexpr (LEVEL >= 2) {
-                        img_dd[0 * cols + k] = v.hxx;
-                        img_dd[1 * cols + k] = v.hxy;
-                        img_dd[2 * cols + k] = v.hxz;
-                        img_dd[3 * cols + k] = v.hxy;
-                        img_dd[4 * cols + k] = v.hyy;
-                        img_dd[5 * cols + k] = v.hyz;
-                        img_dd[6 * cols + k] = v.hxz;
-                        img_dd[7 * cols + k] = v.hyz;
-                        img_dd[8 * cols + k] = v.hzz;
-                    }
+        auto put = [&](int k, Column<T> v) {
+            if constexpr (NORM && LEVEL >= 1) to_cartesian<T, LEVEL>(v, us);
+            if constexpr (VJP) {
+                const T gk = grow[k];
+                ax += gk * v.gx;
+                ay += gk * v.gy;
+                az += gk * v.gz;
+            } else {
+                out_sph[k] = v.y;
+                if constexpr (LEVEL >= 1) {
+                    out_d[k] = v.gx;
+                    out_d[ny + k] = v.gy;
+                    out_d[2 * ny + k] = v.gz;
                 }
-            };
-
-            // l = 0 and l = 1: closed forms, done by the group's first lane
-            if (g == 0 && valid && l_lo == 0) {
-                Column<T> v{};
-                v.y = T(0.282094791773878);
-                put(0, v);
-                if (L >= 1) {
-                    const T a1 = T(0.48860251190292);
-                    Column<T> vy{}, vz{}, vx{};
-                    vy.y = a1 * y;
-                    vy.gy = a1;
-                    vz.y = a1 * z;
-                    vz.gz = a1;
-                    vx.y = a1 * x;
-                    vx.gx = a1;
-                    put(1, vy);
-                    put(2, vz);
-                    put(3, vx);
+                if constexpr (LEVEL >= 2) {
+                    out_dd[0 * ny + k] = v.hxx;
+                    out_dd[1 * ny + k] = v.hxy;
+                    out_dd[2 * ny + k] = v.hxz;
+                    out_dd[3 * ny + k] = v.hxy;
+                    out_dd[4 * ny + k] = v.hyy;
+                    out_dd[5 * ny + k] = v.hyz;
+                    out_dd[6 * ny + k] = v.hxz;
+                    out_dd[7 * ny + k] = v.hyz;
+                    out_dd[8 * ny + k] = v.hzz;
                 }
             }
-
-            // ---- phase B: pairs (l, m), l >= 2, dealt round-robin to the group's lanes
-            int l = l_lo < 2 ? 2 : l_lo;
-            int m = g;
-            while (l <= l_hi && m > l) {
+        };
+        auto finish_pair = [&](const PairInputs<T, LEVEL>& in) {
+            Column<T> vp{}, vm{};
+            band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
+            const int mid = in.l * in.l + in.l;
+            put(mid + in.m, vp);
+            if (in.m > 0) put(mid - in.m, vm);
+        };
+        auto advance = [&](int& l, int& m) {
+            m += G;
+            while (l <= L && m > l) {
                 m -= l + 1;
                 ++l;
             }
-            if (!valid) l = l_hi + 1;
-            while (l <= l_hi) {
-                const T* Ql = sQ + l * RS;
-                const T f = sF[tri(l, m)];
-                const T cm = sc[m], sm = ss[m];
-                const T pq = Ql[m] * f;
-                Column<T> vp{}, vm{};  // +m (cosine-like) and -m (sine-like) columns
-                vp.y = pq * cm;
-                vm.y = pq * sm;
-                if constexpr (LEVEL >= 1) {
-                    const T* Ql1 = Ql - RS;
-                    const T q1a = Ql1[m + 1];  // Q_{l-1}^{m+1}, zero past the diagonal
-                    const T q1b = Ql1[m];      // Q_{l-1}^{m}
-                    const T cm1 = sc[m - 1], sm1 = ss[m - 1];
-                    const T fm = T(m);
-                    const T pqm = pq * fm;
-                    const T pqs = pqm * sm1, pqc = pqm * cm1;
-                    const T pdq = f * q1a;
-                    const T pdqx = pdq * x, pdqy = pdq * y;
-                    vm.gx = pdqx * sm + pqs;
-                    vp.gx = pdqx * cm + pqc;
-                    vm.gy = pdqy * sm + pqc;
-                    vp.gy = pdqy * cm - pqs;
-                    const T flm = T(l + m);
-                    const T pdz = f * flm * q1b;
-                    vm.gz = pdz * sm;
-                    vp.gz = pdz * cm;
-                    if constexpr (LEVEL >= 2) {
-                        const T* Ql2 = Ql1 - RS;
-                        const T cm2 = sc[m - 2], sm2 = ss[m - 2];
-                        const T A = f * q1a, D = f * q1b;
-                        const T B = f * Ql2[m + 2], E = f * Ql2[m + 1], C = f * Ql2[m];
-                        const T fmm = T(m * (m - 1));
-                        const T Pc = fmm * pq * cm2, Ps = fmm * pq * sm2;
-                        const T f2m = T(2 * m);
-                        vp.hxx = A * cm + x2 * B * cm + f2m * x * A * cm1 + Pc;
-                        vm.hxx = A * sm + x2 * B * sm + f2m * x * A * sm1 + Ps;
-                        vp.hyy = A * cm + y2 * B * cm - f2m * y * A * sm1 - Pc;
-                        vm.hyy = A * sm + y2 * B * sm + f2m * y * A * cm1 - Ps;
-                        const T fz = T((l + m) * (l + m - 1));
-                        vp.hzz = fz * C * cm;
-                        vm.hzz = fz * C * sm;
-                        vp.hxy = xy * B * cm + y * A * fm * cm1 - x * A * fm * sm1 - Ps;
-                        vm.hxy = xy * B * sm + y * A * fm * sm1 + x * A * fm * cm1 + Pc;
-                        vp.hxz = x * flm * E * cm + flm * D * fm * cm1;
-                        vm.hxz = x * flm * E * sm + flm * D * fm * sm1;
-                        vp.hyz = y * flm * E * cm - flm * D * fm * sm1;
-                        vm.hyz = y * flm * E * sm + flm * D * fm * cm1;
-                    }
-                }
-                const int mid = l * l + l;
-                put(mid + m, vp);
-                if (m > 0) put(mid - m, vm);
-                m += G;
-                while (l <= l_hi && m > l) {
-                    m -= l + 1;
-                    ++l;
-                }
-            }
+        };
 
-            if constexpr (!VJP) {
-                if (a.use_bulk) {
-                    // single band: each image is one span of the output. Elements before the first and
-                    // after the last 16-byte boundary go out with plain stores, the body through TMA.
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    constexpr int Q16 = 16 / int(sizeof(T));
-                    auto copy_out = [&](T* gdst, const T* img, int shift, int count) {
-                        const int head = shift == 0 ? 0 : (Q16 - shift < count ? Q16 - shift : count);
-                        const int body = (count - head) / Q16 * Q16;
-                        const int tail = count - head - body;
-                        if (lane < head) gdst[lane] = img[lane];
-                        if (lane >= 8 && lane - 8 < tail) gdst[head + body + lane - 8] = img[head + body + lane - 8];
-                        if (lane == 0 && body > 0)
-                            bulk_store_smem_to_global(gdst + head, img + head, unsigned(body) * unsigned(sizeof(T)));
-                    };
-                    copy_out(gsph, image0, shift0, nvalid * ny);
-                    if constexpr (LEVEL >= 1) copy_out(gd, image1, shift1, nvalid * 3 * ny);
-                    if constexpr (LEVEL >= 2) copy_out(gdd, image2, shift2, nvalid * 9 * ny);
-                    if (lane == 0) bulk_commit();
-                } else {
-                    __syncwarp();  // image complete
-                    if (cols == ny) {
-                        for (int e = lane; e < nvalid * ny; e += 32) gsph[e] = image0[e];
-                        if constexpr (LEVEL >= 1)
-                            for (int e = lane; e < nvalid * 3 * ny; e += 32) gd[e] = image1[e];
-                        if constexpr (LEVEL >= 2)
-                            for (int e = lane; e < nvalid * 9 * ny; e += 32) gdd[e] = image2[e];
-                    } else {
-                        // one band of columns: a fragment of `cols` elements per (point, component)
-                        for (int r = 0; r < nvalid; ++r)
-                            for (int e = lane; e < cols; e += 32) gsph[size_t(r) * ny + kb + e] = image0[r * cols + e];
-                        if constexpr (LEVEL >= 1)
-                            for (int r = 0; r < nvalid * 3; ++r)
-                                for (int e = lane; e < cols; e += 32) gd[size_t(r) * ny + kb + e] = image1[r * cols + e];
-                        if constexpr (LEVEL >= 2)
-                            for (int r = 0; r < nvalid * 9; ++r)
-                                for (int e = lane; e < cols; e += 32) gdd[size_t(r) * ny + kb + e] = image2[r * cols + e];
-                    }
-                    __syncwarp();  // image free for the next band
-                }
+        // ---- phase B: pairs (l, m) dealt round-robin to the group's lanes, two in flight per lane
+        int l = 0, m = g - G;
+        advance(l, m);
+        if (!valid) l = L + 1;
+        while (l <= L) {
+            const PairInputs<T, LEVEL> in0 = band_load_pair<T, LEVEL>(l, m, RS, sF, sQ, sc, ss);
+            advance(l, m);
+            if (l <= L) {
+                const PairInputs<T, LEVEL> in1 = band_load_pair<T, LEVEL>(l, m, RS, sF, sQ, sc, ss);
+                advance(l, m);
+                finish_pair(in0);
+                finish_pair(in1);
+            } else {
+                finish_pair(in0);
+            }
+        }
+
+        if constexpr (!VJP) {
+            if (bulk) {
+                // each image is one span of the output. Elements before the first and after the last
+                // 16-byte boundary go out with plain stores, the body through TMA.
+                fence_proxy_async_smem();
+                __syncwarp();
+                constexpr int Q16 = 16 / int(sizeof(T));
+                auto copy_out = [&](T* gdst, const T* img, int shift, int count) {
+                    const int head = shift == 0 ? 0 : (Q16 - shift < count ? Q16 - shift : count);
+                    const int body = (count - head) / Q16 * Q16;
+                    const int tail = count - head - body;
+                    if (lane < head) gdst[lane] = img[lane];
+                    if (lane >= 8 && lane - 8 < tail) gdst[head + body + lane - 8] = img[head + body + lane - 8];
+                    if (lane == 0 && body > 0)
+                        bulk_store_smem_to_global(gdst + head, img + head, unsigned(body) * unsigned(sizeof(T)));
+                };
+                copy_out(gsph, image0, shift0, nvalid * ny);
+                if constexpr (LEVEL >= 1) copy_out(gd, image1, shift1, nvalid * 3 * ny);
+                if constexpr (LEVEL >= 2) copy_out(gdd, image2, shift2, nvalid * 9 * ny);
+                if (lane == 0) bulk_commit();
+            } else if (!direct) {
+                __syncwarp();  // image complete
+                for (int e = lane; e < nvalid * ny; e += 32) gsph[e] = image0[e];
+                if constexpr (LEVEL >= 1)
+                    for (int e = lane; e < nvalid * 3 * ny; e += 32) gd[e] = image1[e];
+                if constexpr (LEVEL >= 2)
+                    for (int e = lane; e < nvalid * 9 * ny; e += 32) gdd[e] = image2[e];
             }
         }
 
@@ -392,7 +413,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         }
     }
     // shared memory must outlive the engine's reads
-    if (!VJP && a.use_bulk && lane == 0) bulk_wait_read_all();
+    if (bulk && lane == 0) bulk_wait_read_all();
 }
 
 }  // namespace sph_b200

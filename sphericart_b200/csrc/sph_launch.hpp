@@ -29,9 +29,8 @@ template <typename T, int LMAX> struct TileLaunch {
                            const T* host_tables, int warps, int device, cudaStream_t stream);
 };
 
-// Band kernels, run-time l_max. G lanes per point.
-constexpr int BAND_MAX_BANDS = 32;
-
+// Band kernels, run-time l_max. G lanes per point. mode: 0 = image in shared memory copied out by
+// TMA bulk stores, 1 = image copied out by plain stores, 2 = direct global stores (G = 32 only).
 template <typename T> struct BandLaunchArgs {
     const T* xyz;
     long long n;
@@ -42,10 +41,7 @@ template <typename T> struct BandLaunchArgs {
     T* xyz_grad;
     const T* d_tables;
     int l_max;
-    int nbands;
-    int max_cols;
-    bool use_bulk;
-    short band_lo[BAND_MAX_BANDS + 1];
+    int mode;
     int warps;
     size_t smem;
 };

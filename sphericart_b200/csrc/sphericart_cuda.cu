@@ -38,6 +38,7 @@ struct Knobs {
     int tile_warps;     // force warps per CTA of the tile kernels (1..8)
     int force_band;     // route l_max <= 8 through the band kernel too
     int no_bulk;        // copy tiles out with plain stores instead of TMA bulk stores
+    int band_direct;    // 1: force direct global stores in the band kernel, -1: forbid them
 };
 
 int env_int(const char* name, int fallback) {
@@ -49,7 +50,8 @@ int env_int(const char* name, int fallback) {
 const Knobs& knobs() {
     static const Knobs k = {env_int("SPH_B200_BAND_IMAGE_KB", 64), env_int("SPH_B200_BAND_LANES", 0),
                             env_int("SPH_B200_BAND_WARPS", 0),     env_int("SPH_B200_TILE_WARPS", 0),
-                            env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0)};
+                            env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0),
+                            env_int("SPH_B200_BAND_DIRECT", 0)};
     return k;
 }
 
@@ -118,15 +120,12 @@ template <typename T> void build_tables(int l_max, T* out) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Band-kernel plan: lanes per point, warps per CTA, bands of degrees, shared-memory size.
+// Band-kernel plan: lanes per point, warps per CTA, copy-out mode, shared-memory size.
 struct BandPlan {
-    int lanes = 1;      // G
-    int warps = 1;      // warps per CTA
-    int nbands = 1;
-    int max_cols = 0;   // widest band, columns
-    bool single_band = true;
-    short band_lo[BAND_MAX_BANDS + 1] = {};
-    size_t smem = 0;    // dynamic shared memory per CTA
+    int lanes = 1;    // G
+    int warps = 1;    // warps per CTA
+    int mode = 0;     // 0 image + TMA bulk stores, 1 image + plain stores, 2 direct global stores
+    size_t smem = 0;  // dynamic shared memory per CTA
     bool feasible = true;
 };
 
@@ -137,7 +136,7 @@ size_t band_align16(size_t elems, size_t elem) {
 }
 int band_row_stride_host(int l_max) { return (l_max + 5) + ((l_max + 5) & 1); }
 size_t band_point_state_host(int l_max) {
-    return 2 * size_t(l_max + 3) + size_t(l_max + 1) + size_t(l_max + 1) * band_row_stride_host(l_max);
+    return 2 * size_t(l_max + 3) + size_t(l_max + 1) + size_t(l_max + 3) * band_row_stride_host(l_max);
 }
 
 // kind: 0..2 = forward level, 3 = VJP.
@@ -146,80 +145,69 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
     const size_t ny = size_t(n_columns(L));
     const size_t nq = size_t(n_table(L));
     const bool vjp = kind == 3;
-    const size_t ncomp = vjp ? 1 : size_t(level_components(kind));
-    const size_t table_elems = band_align16(2 * nq, elem);
+    const size_t table_bytes = band_align16(2 * nq, elem) * elem;
     const size_t slack = 16 / elem;
 
-    auto per_warp_elems = [&](int P, size_t cols) {
+    auto per_warp_bytes = [&](int P, bool with_image) {
         size_t e = band_align16(size_t(P) * band_point_state_host(L), elem);
-        if (vjp) return e + band_align16(size_t(P) * ny, elem);
-        e += band_align16(size_t(P) * cols, elem) + slack;
-        if (kind >= 1) e += band_align16(size_t(P) * 3 * cols, elem) + slack;
-        if (kind >= 2) e += band_align16(size_t(P) * 9 * cols, elem) + slack;
-        return e;
+        if (vjp) return (e + band_align16(size_t(P) * ny, elem)) * elem;
+        if (with_image) {
+            e += band_align16(size_t(P) * ny, elem) + slack;
+            if (kind >= 1) e += band_align16(size_t(P) * 3 * ny, elem) + slack;
+            if (kind >= 2) e += band_align16(size_t(P) * 9 * ny, elem) + slack;
+        }
+        return e * elem;
+    };
+    // warps per SM that fit when CTAs of w warps share the tables
+    auto warps_per_sm = [&](size_t per_warp, int w) {
+        const size_t cta = table_bytes + w * per_warp;
+        if (cta > smem_limit) return size_t(0);
+        const size_t n_cta = std::min<size_t>(32, (smem_limit + 1024) / (cta + 1024));
+        return std::min<size_t>(64, n_cta * w);
     };
 
+    BandPlan plan;
     // Lanes per point. The pair loop is balanced for any G, so G is chosen for occupancy and for
     // amortising the per-group prologue: about four pairs per lane at least, and a warp's images
     // within the budget.
     const size_t budget = size_t(knobs().band_image_kb) * 1024;
-    const int pairs = n_table(L) - 3;
+    const int pairs = n_table(L);
     int G = 32;
     while (G > 1 && pairs / G < 4) G /= 2;
-    while (G < 32 && per_warp_elems(32 / G, ny) * elem > budget) G *= 2;
+    while (G < 32 && per_warp_bytes(32 / G, true) > budget) G *= 2;
     const int forced = knobs().band_lanes;
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16 || forced == 32) G = forced;
-    const int P = 32 / G;
 
-    BandPlan plan;
-    plan.lanes = G;
-    const size_t usable = smem_limit > table_elems * elem + 1024 ? smem_limit - table_elems * elem - 1024 : 0;
-    if (vjp || per_warp_elems(P, ny) * elem <= usable) {
-        plan.nbands = 1;
-        plan.band_lo[0] = 0;
-        plan.band_lo[1] = short(L + 1);
-        plan.max_cols = int(ny);
-    } else {
-        // consecutive degrees per band, each band's image within ~half of shared memory
-        const size_t band_budget = std::min(usable, size_t(112) * 1024);
-        int nb = 0, lo = 0, max_cols = 0;
-        while (lo <= L) {
-            int hi = lo;
-            auto cols_of = [&](int h) { return size_t((h + 1) * (h + 1) - lo * lo); };
-            if (per_warp_elems(P, cols_of(hi)) * elem > usable) { plan.feasible = false; break; }
-            while (hi + 1 <= L && per_warp_elems(P, cols_of(hi + 1)) * elem <= band_budget) ++hi;
-            if (nb >= BAND_MAX_BANDS) { plan.feasible = false; break; }
-            plan.band_lo[nb++] = short(lo);
-            max_cols = std::max(max_cols, int(cols_of(hi)));
-            lo = hi + 1;
-        }
-        plan.band_lo[nb] = short(L + 1);
-        plan.nbands = nb;
-        plan.max_cols = max_cols;
-        plan.single_band = false;
+    // Copy-out mode. With a whole warp per point, rows so long that their image leaves room for
+    // fewer than eight warps per SM are stored straight to global memory instead, provided a
+    // degree's run of columns is long enough to fill store sectors (>= 128 bytes at l_max).
+    plan.mode = knobs().no_bulk != 0 ? 1 : 0;
+    if (!vjp && G == 32) {
+        const bool long_runs = size_t(L + 1) * elem >= 128;
+        const bool image_fits = warps_per_sm(per_warp_bytes(1, true), 1) >= 1;
+        const bool crowded = warps_per_sm(per_warp_bytes(1, true), 4) < 8 && warps_per_sm(per_warp_bytes(1, true), 1) < 8;
+        if (!image_fits || (crowded && long_runs)) plan.mode = 2;
+        if (knobs().band_direct == 1) plan.mode = 2;
+        if (knobs().band_direct == -1 && image_fits) plan.mode = knobs().no_bulk != 0 ? 1 : 0;
     }
+    plan.lanes = G;
+    const int P = 32 / G;
+    const size_t per_warp = per_warp_bytes(P, plan.mode != 2);
 
     // warps per CTA: up to 4; pick the count that packs the most warps into an SM
-    const size_t per_warp = per_warp_elems(P, size_t(plan.max_cols)) * elem;
-    const size_t table_bytes = table_elems * elem;
-    int warps = 4;
+    int warps = 1;
     const int forced_warps = knobs().band_warps;
     if (forced_warps >= 1 && forced_warps <= 4) {
         warps = forced_warps;
     } else {
-        int best = 1;
-        size_t best_per_sm = 0;
+        size_t best = 0;
         for (int w = 4; w >= 1; --w) {
-            const size_t cta = table_bytes + w * per_warp;
-            if (cta > smem_limit) continue;
-            const size_t n_cta = std::min<size_t>(32, (smem_limit + 1024) / (cta + 1024));
-            const size_t per_sm = std::min<size_t>(64, n_cta * w);
-            if (per_sm > best_per_sm) {
-                best_per_sm = per_sm;
-                best = w;
+            const size_t per_sm = warps_per_sm(per_warp, w);
+            if (per_sm > best) {
+                best = per_sm;
+                warps = w;
             }
         }
-        warps = best;
     }
     plan.warps = warps;
     plan.smem = table_bytes + warps * per_warp;
@@ -253,8 +241,8 @@ void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int
 }
 
 template <typename T>
-BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, bool vjp, const T* d_tables, const T* xyz,
-                                   long long n, T* sph, T* dsph, T* ddsph, const T* sph_grad, T* xyz_grad) {
+BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, const T* d_tables, const T* xyz, long long n,
+                                   T* sph, T* dsph, T* ddsph, const T* sph_grad, T* xyz_grad) {
     BandLaunchArgs<T> a{};
     a.xyz = xyz;
     a.n = n;
@@ -265,10 +253,7 @@ BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, bool vjp, co
     a.xyz_grad = xyz_grad;
     a.d_tables = d_tables;
     a.l_max = l_max;
-    a.nbands = plan.nbands;
-    a.max_cols = plan.max_cols;
-    a.use_bulk = !vjp && plan.single_band && knobs().no_bulk == 0;
-    for (int b = 0; b <= BAND_MAX_BANDS; ++b) a.band_lo[b] = plan.band_lo[b];
+    a.mode = plan.mode;
     a.warps = plan.warps;
     a.smem = plan.smem;
     return a;
@@ -383,7 +368,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         throw std::runtime_error("sphericart::cuda: l_max is too large for this device's shared memory");
     }
     const BandLaunchArgs<T> a =
-        band_launch_args<T>(*plan, l_max, vjp, d_tables, xyz, n, sph, dsph, ddsph, sph_grad, xyz_grad);
+        band_launch_args<T>(*plan, l_max, d_tables, xyz, n, sph, dsph, ddsph, sph_grad, xyz_grad);
     check(band_dispatch<T>(plan->lanes, vjp ? 1 : kind, vjp, normalized, a, scope.device, stream), "band kernel launch");
 }
 
@@ -692,7 +677,7 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
         dev.resident_l_max = l_max;
     }
     const BandLaunchArgs<double> a =
-        band_launch_args<double>(plan, l_max, false, reinterpret_cast<const double*>(dev.scratch), xyz,
+        band_launch_args<double>(plan, l_max, reinterpret_cast<const double*>(dev.scratch), xyz,
                                  (long long)n_samples, sph, dsph, nullptr, nullptr, nullptr);
     check(band_dispatch<double>(plan.lanes, 1, false, normalized, a, scope.device, stream),
           "band kernel launch (allocation-free)");
