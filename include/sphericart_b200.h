@@ -136,6 +136,11 @@ SPHERICART_EXPORT void sphericart_cuda_solid_harmonics_compute_array_with_hessia
  * *_new (empty string if none). The pointer stays valid until the thread's next failing call. */
 SPHERICART_EXPORT const char* sphericart_cuda_last_error(void);
 
+/* The kernels' only waits are on their own asynchronous copies and are bounded; a wait that ever
+ * gave up records it on the device. Returns 1 if that happened on the current device since the
+ * library was loaded, 0 if not, -1 if the flags could not be read. Synchronises the device. */
+SPHERICART_EXPORT int sphericart_cuda_device_wait_errors(void);
+
 /* Fused backward of the values: xyz_grad[i][a] = sum_k sph_grad[i][k] * dsph[i][a][k], dsph never
  * materialised. Fuses what sphericart-torch/python/sphericart/torch/register.py:90-108 does with a
  * gradients launch plus a product and a reduction. Aborts on failure like the reference's compute calls. */

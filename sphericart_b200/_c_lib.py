@@ -18,7 +18,8 @@ _SUFFIXES = ("", "_f")
 
 def exported_names():
     """Every function the C header declares, in declaration-family order."""
-    names = ["sphericart_cuda_last_error", "sphericart_cuda_harmonics_with_gradients_no_alloc"]
+    names = ["sphericart_cuda_last_error", "sphericart_cuda_device_wait_errors",
+             "sphericart_cuda_harmonics_with_gradients_no_alloc"]
     for kind in _KINDS:
         for sfx in _SUFFIXES:
             base = f"sphericart_cuda_{kind}_harmonics"
@@ -41,6 +42,8 @@ def get_library():
     vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
     lib.sphericart_cuda_last_error.restype = ctypes.c_char_p
     lib.sphericart_cuda_last_error.argtypes = []
+    lib.sphericart_cuda_device_wait_errors.restype = ci
+    lib.sphericart_cuda_device_wait_errors.argtypes = []
     lib.sphericart_cuda_harmonics_with_gradients_no_alloc.restype = ci
     lib.sphericart_cuda_harmonics_with_gradients_no_alloc.argtypes = [ci, sz, vp, sz, vp, vp, vp]
     for kind in _KINDS:

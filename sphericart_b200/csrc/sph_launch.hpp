@@ -26,7 +26,10 @@ template <typename T, int LMAX> struct TileLaunch {
     static cudaError_t forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
                                const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream);
     static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* host_tables, int warps, int device, cudaStream_t stream);
+                           const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream);
+    // 1 if a bounded wait inside one of this instantiation's kernels ever gave up on the current
+    // device, 0 if not, -1 if the flag could not be read. Synchronises the device.
+    static int device_error_flag();
 };
 
 // Band kernels, run-time l_max. G lanes per point. mode: 0 = image in shared memory copied out by

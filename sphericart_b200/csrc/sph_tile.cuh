@@ -150,23 +150,96 @@ template <typename T, int NY> struct VjpSink {
     }
 };
 
-template <typename T, int LMAX> constexpr size_t vjp_tile_smem_bytes() {
-    return size_t(TILE_POINTS) * n_columns(LMAX) * sizeof(T);
+// ---- mbarrier + TMA 1-D bulk load (global -> the issuing CTA's own shared memory) ----------
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
 }
 
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void bulk_load_global_to_smem(void* sdst, const void* gsrc, unsigned bytes,
+                                                         unsigned long long* bar) {
+    const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(sdst));
+    const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(d),
+                 "l"(gsrc), "r"(bytes), "r"(b)
+                 : "memory");
+}
+
+// Waits for the phase with the given parity, giving up after a bounded number of polls (each
+// poll already blocks for a hardware-defined interval). Returns false on give-up.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    for (int tries = 0; tries < (1 << 22); ++tries) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Set when a bounded wait gave up (it never does unless the device is misbehaving); one flag per
+// translation unit, read by TileLaunch::device_error_flag().
+static __device__ int g_tile_wait_gave_up = 0;
+
+// Per warp: two images of the tile's sph_grad rows (double buffer) followed by two mbarriers.
+template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_smem_bytes() {
+    return 2 * size_t(TILE_POINTS) * n_columns(LMAX) * sizeof(T) + 16;
+}
+
+// use_bulk != 0: the rows of sph_grad are fetched by the TMA engine (1-D bulk load, completion on
+// an mbarrier), one tile ahead of the arithmetic, so the warp neither spends issue slots on the
+// staging copy nor waits for it. Requires a 16-byte aligned sph_grad; otherwise, and for the
+// ragged last tile, the warp stages the rows itself with coalesced loads.
 template <typename T, int LMAX, bool NORM>
 __global__ void __launch_bounds__(256)
 sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, long long n,
-                    T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab) {
+                    T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
+    constexpr unsigned TILE_BYTES = unsigned(TILE_POINTS * NY * sizeof(T));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    T* img_g = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * NY;
+    unsigned char* mine = smem_raw + size_t(warp) * vjp_tile_smem_bytes<T, LMAX>();
+    T* img[2] = {reinterpret_cast<T*>(mine), reinterpret_cast<T*>(mine) + TILE_POINTS * NY};
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(mine + 2 * size_t(TILE_BYTES));
 
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long stride = (long long)gridDim.x * nwarps;
-    for (long long tile = (long long)blockIdx.x * nwarps + warp; tile < ntiles; tile += stride) {
+    const long long tile0 = (long long)blockIdx.x * nwarps + warp;
+
+    // a tile can come through the engine when it is full (its byte count is then a multiple of 16)
+    auto engine_tile = [&](long long tile) { return use_bulk && (tile + 1) * TILE_POINTS <= n; };
+    auto issue = [&](long long tile, int buf) {
+        if (lane == 0 && tile < ntiles && engine_tile(tile)) {
+            mbar_expect_tx(&bar[buf], TILE_BYTES);
+            bulk_load_global_to_smem(img[buf], sph_grad + tile * TILE_POINTS * NY, TILE_BYTES, &bar[buf]);
+        }
+    };
+
+    if (use_bulk) {
+        if (lane == 0) {
+            mbar_init(&bar[0], 1);
+            mbar_init(&bar[1], 1);
+            mbar_init_fence();
+        }
+        __syncwarp();
+        issue(tile0, 0);
+    }
+
+    unsigned phase[2] = {0u, 0u};
+    int cur = 0;
+    for (long long tile = tile0; tile < ntiles; tile += stride, cur ^= 1) {
         const long long first = tile * TILE_POINTS;
         const long long i = first + lane;
         const int npts = (n - first) < TILE_POINTS ? int(n - first) : TILE_POINTS;
@@ -176,18 +249,32 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             y = xyz[3 * i + 1];
             z = xyz[3 * i + 2];
         }
-        __syncwarp();  // previous tile's reads of the image are complete
-        const T* gsrc = sph_grad + first * NY;
-        for (int e = lane; e < TILE_POINTS * NY; e += 32) img_g[e] = (e < npts * NY) ? gsrc[e] : T(0);
-        __syncwarp();
+        // every lane finished reading the other buffer in the previous iteration (barrier at its
+        // end), so the next tile may stream into it while this one is being processed
+        issue(tile + stride, cur ^ 1);
 
-        VjpSink<T, NY> sink{img_g + lane * NY, T(0), T(0), T(0)};
+        if (engine_tile(tile)) {
+            if (!mbar_wait_bounded(&bar[cur], phase[cur])) {
+                g_tile_wait_gave_up = 1;
+                // do not leave with a copy in flight towards this CTA's shared memory
+                if (tile + stride < ntiles && engine_tile(tile + stride)) mbar_wait_bounded(&bar[cur ^ 1], phase[cur ^ 1]);
+                return;
+            }
+            phase[cur] ^= 1u;
+        } else {
+            const T* gsrc = sph_grad + first * NY;
+            for (int e = lane; e < TILE_POINTS * NY; e += 32) img[cur][e] = (e < npts * NY) ? gsrc[e] : T(0);
+            __syncwarp();
+        }
+
+        VjpSink<T, NY> sink{img[cur] + lane * NY, T(0), T(0), T(0)};
         eval_point<T, LMAX, 1, NORM>(x, y, z, tab, sink);
         if (i < n) {
             xyz_grad[3 * i + 0] = sink.ax;
             xyz_grad[3 * i + 1] = sink.ay;
             xyz_grad[3 * i + 2] = sink.az;
         }
+        __syncwarp();  // all lanes are done with img[cur]
     }
 }
 

@@ -298,13 +298,22 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* tables, int warps, int device, cudaStream_t stream) {
+                           const T* tables, int warps, bool use_bulk, int device, cudaStream_t stream) {
         if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, device, stream);
+            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, device,
+                                            stream);
         if constexpr (LMAX > 0)
-            return TileDispatch<T, LMAX - 1>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, warps, device,
-                                                  stream);
+            return TileDispatch<T, LMAX - 1>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk,
+                                                  device, stream);
         return cudaErrorInvalidValue;
+    }
+    static int error_flags() {
+        int flag = TileLaunch<T, LMAX>::device_error_flag();
+        if constexpr (LMAX > 0) {
+            const int rest = TileDispatch<T, LMAX - 1>::error_flags();
+            flag = (flag < 0 || rest < 0) ? -1 : (flag | rest);
+        }
+        return flag;
     }
 };
 
@@ -343,11 +352,12 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
     const bool force_band = knobs().force_band != 0;
 
     if (l_max <= TILE_LMAX && !force_band) {
-        const size_t per_warp = vjp ? size_t(32) * n_columns(l_max) * sizeof(T)
+        const size_t per_warp = vjp ? 2 * size_t(32) * n_columns(l_max) * sizeof(T) + 16
                                     : TileDispatch<T>::smem_per_warp(l_max, kind);
         if (vjp) {
+            const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
             check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, tile_warps(per_warp),
-                                       scope.device, stream),
+                                       use_bulk, scope.device, stream),
                   "tile VJP kernel launch");
             return;
         }
@@ -549,6 +559,12 @@ void vjp_call(Calculator* c, const T* xyz, size_t n, const T* sph_grad, T* xyz_g
 }  // namespace
 
 extern "C" const char* sphericart_cuda_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int sphericart_cuda_device_wait_errors(void) {
+    const int f = sph_b200::TileDispatch<float>::error_flags();
+    const int d = sph_b200::TileDispatch<double>::error_flags();
+    return (f < 0 || d < 0) ? -1 : (f | d);
+}
 
 #define SPH_CAPI_FAMILY(KIND, SFX, T)                                                                               \
     extern "C" sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* sphericart_cuda_##KIND##_harmonics_new##SFX( \

@@ -58,7 +58,7 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
 
 template <typename T, int LMAX, bool NORM>
 cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, int warps,
-                       int device, cudaStream_t stream) {
+                       bool use_bulk, int device, cudaStream_t stream) {
     static GridCache cache{};
     auto kernel = sph_vjp_tile_kernel<T, LMAX, NORM>;
     const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>();
@@ -67,7 +67,8 @@ cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long want = (ntiles + warps - 1) / warps;
     const int grid = int(want < max_blocks ? want : max_blocks);
-    kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables));
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables),
+                                               use_bulk ? 1 : 0);
     return cudaGetLastError();
 }
 
@@ -105,9 +106,19 @@ cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xy
 
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                     const T* host_tables, int warps, int device, cudaStream_t stream) {
-    return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, device, stream)
-                      : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, device, stream);
+                                     const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream) {
+    return normalized
+               ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, device, stream)
+               : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, device, stream);
+}
+
+template <typename T, int LMAX> int TileLaunch<T, LMAX>::device_error_flag() {
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_tile_wait_gave_up, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return flag;
 }
 
 template struct TileLaunch<SPH_T, SPH_LMAX>;
