@@ -80,39 +80,80 @@ template <typename T> struct BandArgs {
     int mode;           // BAND_IMAGE_BULK or BAND_IMAGE_PLAIN (ignored by the VJP and by DIRECT kernels)
 };
 
+// ---- explicit shared-memory access with 32-bit addresses and constant offsets -----------------
+template <typename T, int OFF_ELEMS> __device__ __forceinline__ T lds_at(unsigned addr) {
+    T v;
+    if constexpr (sizeof(T) == 4) {
+        asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(OFF_ELEMS * 4));
+    } else {
+        asm volatile("ld.shared.f64 %0, [%1+%2];" : "=d"(v) : "r"(addr), "n"(OFF_ELEMS * 8));
+    }
+    return v;
+}
+
+template <typename T> __device__ __forceinline__ void sts_to(unsigned addr, T v) {
+    if constexpr (sizeof(T) == 4) {
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+    } else {
+        asm volatile("st.shared.f64 [%0], %1;" ::"r"(addr), "d"(v) : "memory");
+    }
+}
+
+// Per-pair constants, the same for every point, built once per CTA: where the pair's inputs sit
+// in the per-point state and in F, which column it produces, and the integer factors of the
+// derivative formulas as floating-point numbers.
+struct PairDesc {
+    int q_off;  // byte offset of Q_{l-2}^{m} in the point's Q table (rows l-1, l at +row stride)
+    int f_off;  // byte offset of F[l][m]
+    int kp;     // column l*l + l + m  (the -m column is kp - 2m)
+    int m;
+};
+__host__ __device__ constexpr int band_pair_factors(int level) { return level == 0 ? 0 : (level == 1 ? 2 : 4); }
+
 // Everything phase B reads for one (l, m) pair.
 template <typename T, int LEVEL> struct PairInputs {
-    int l, m;
+    int kp, m;
     T f, q, cm, sm;
-    T q1a, q1b, cm1, sm1;      // Q_{l-1}^{m+1}, Q_{l-1}^{m}, c_{m-1}, s_{m-1}
-    T q2a, q2b, q2c, cm2, sm2; // Q_{l-2}^{m+2}, Q_{l-2}^{m+1}, Q_{l-2}^{m}, c_{m-2}, s_{m-2}
+    T q1a, q1b, cm1, sm1;       // Q_{l-1}^{m+1}, Q_{l-1}^{m}, c_{m-1}, s_{m-1}
+    T q2a, q2b, q2c, cm2, sm2;  // Q_{l-2}^{m+2}, Q_{l-2}^{m+1}, Q_{l-2}^{m}, c_{m-2}, s_{m-2}
+    T fm, flm, fmm, fz;         // m, l+m, m(m-1), (l+m)(l+m-1)
 };
 
+// sQ_addr: shared address of the point's row -2; sc_addr, ss_addr: of c_{-2}, s_{-2};
+// row_b: Q row stride in bytes.
 template <typename T, int LEVEL>
-__device__ __forceinline__ PairInputs<T, LEVEL> band_load_pair(int l, int m, int RS, const T* sF, const T* sQ,
-                                                               const T* sc, const T* ss) {
+__device__ __forceinline__ PairInputs<T, LEVEL> band_load_pair(const PairDesc d, unsigned sF_addr, unsigned sQ_addr,
+                                                               unsigned sc_addr, unsigned ss_addr, unsigned row_b,
+                                                               unsigned fac_addr) {
     PairInputs<T, LEVEL> in;
-    in.l = l;
-    in.m = m;
-    const T* Ql = sQ + l * RS;
-    in.f = sF[tri(l, m)];
-    in.q = Ql[m];
-    in.cm = sc[m];
-    in.sm = ss[m];
+    in.kp = d.kp;
+    in.m = d.m;
+    const unsigned m_b = unsigned(d.m) * unsigned(sizeof(T));
+    const unsigned a2 = sQ_addr + unsigned(d.q_off);  // row l-2, column m
+    const unsigned a1 = a2 + row_b;                   // row l-1
+    const unsigned a0 = a1 + row_b;                   // row l
+    const unsigned ac = sc_addr + m_b;                // c_{m-2}
+    const unsigned as = ss_addr + m_b;                // s_{m-2}
+    in.f = lds_at<T, 0>(sF_addr + unsigned(d.f_off));
+    in.q = lds_at<T, 0>(a0);
+    in.cm = lds_at<T, 2>(ac);
+    in.sm = lds_at<T, 2>(as);
     if constexpr (LEVEL >= 1) {
-        const T* Ql1 = Ql - RS;
-        in.q1a = Ql1[m + 1];
-        in.q1b = Ql1[m];
-        in.cm1 = sc[m - 1];
-        in.sm1 = ss[m - 1];
+        in.q1a = lds_at<T, 1>(a1);
+        in.q1b = lds_at<T, 0>(a1);
+        in.cm1 = lds_at<T, 1>(ac);
+        in.sm1 = lds_at<T, 1>(as);
+        in.fm = lds_at<T, 0>(fac_addr);
+        in.flm = lds_at<T, 1>(fac_addr);
     }
     if constexpr (LEVEL >= 2) {
-        const T* Ql2 = Ql - 2 * RS;
-        in.q2a = Ql2[m + 2];
-        in.q2b = Ql2[m + 1];
-        in.q2c = Ql2[m];
-        in.cm2 = sc[m - 2];
-        in.sm2 = ss[m - 2];
+        in.q2a = lds_at<T, 2>(a2);
+        in.q2b = lds_at<T, 1>(a2);
+        in.q2c = lds_at<T, 0>(a2);
+        in.cm2 = lds_at<T, 0>(ac);
+        in.sm2 = lds_at<T, 0>(as);
+        in.fmm = lds_at<T, 2>(fac_addr);
+        in.fz = lds_at<T, 3>(fac_addr);
     }
     return in;
 }
@@ -129,7 +170,7 @@ __device__ __forceinline__ void band_eval_pair(const PairInputs<T, LEVEL>& in, T
     vm.y = pq * sm;
     if constexpr (LEVEL >= 1) {
         const T cm1 = in.cm1, sm1 = in.sm1;
-        const T fm = T(in.m);
+        const T fm = in.fm;
         const T pqm = pq * fm;
         const T pqs = pqm * sm1, pqc = pqm * cm1;
         const T pdq = f * in.q1a;
@@ -138,21 +179,21 @@ __device__ __forceinline__ void band_eval_pair(const PairInputs<T, LEVEL>& in, T
         vp.gx = pdqx * cm + pqc;
         vm.gy = pdqy * sm + pqc;
         vp.gy = pdqy * cm - pqs;
-        const T flm = T(in.l + in.m);
+        const T flm = in.flm;
         const T pdz = f * flm * in.q1b;
         vm.gz = pdz * sm;
         vp.gz = pdz * cm;
         if constexpr (LEVEL >= 2) {
             const T A = f * in.q1a, D = f * in.q1b;
             const T B = f * in.q2a, E = f * in.q2b, C = f * in.q2c;
-            const T fmm = T(in.m * (in.m - 1));
+            const T fmm = in.fmm;
             const T Pc = fmm * pq * in.cm2, Ps = fmm * pq * in.sm2;
-            const T f2m = T(2 * in.m);
+            const T f2m = fm + fm;
             vp.hxx = A * cm + x2 * B * cm + f2m * x * A * cm1 + Pc;
             vm.hxx = A * sm + x2 * B * sm + f2m * x * A * sm1 + Ps;
             vp.hyy = A * cm + y2 * B * cm - f2m * y * A * sm1 - Pc;
             vm.hyy = A * sm + y2 * B * sm + f2m * y * A * cm1 - Ps;
-            const T fz = T((in.l + in.m) * (in.l + in.m - 1));
+            const T fz = in.fz;
             vp.hzz = fz * C * cm;
             vm.hzz = fz * C * sm;
             vp.hxy = xy * B * cm + y * A * fm * cm1 - x * A * fm * sm1 - Ps;
@@ -181,14 +222,19 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
     static_assert(!(VJP && DIRECT), "the VJP has no output image");
     const bool bulk = !VJP && !DIRECT && a.mode == BAND_IMAGE_BULK;
 
-    // shared memory carve-up: F | K | per warp: P point states, then the image regions
+    // shared memory carve-up: F | K | pair factors | pair descriptors | per warp: P point states,
+    // then the image regions
+    constexpr int NF = band_pair_factors(LEVEL);
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
+    T* sFac = sF + align16_elems<T>(2 * nq);
+    PairDesc* sDesc = reinterpret_cast<PairDesc*>(sFac + align16_elems<T>(nq * NF));
+    T* warps_base = reinterpret_cast<T*>(sDesc + nq);
     const int state_elems = align16_elems<T>(P * band_point_state(L));
     const int reg0 = VJP ? align16_elems<T>(P * ny) : (direct ? 0 : band_region<T>(P, 1, ny));
     const int reg1 = (!VJP && !direct && LEVEL >= 1) ? band_region<T>(P, 3, ny) : 0;
     const int reg2 = (!VJP && !direct && LEVEL >= 2) ? band_region<T>(P, 9, ny) : 0;
-    T* warp_base = sF + align16_elems<T>(2 * nq) + size_t(warp) * (state_elems + reg0 + reg1 + reg2);
+    T* warp_base = warps_base + size_t(warp) * (state_elems + reg0 + reg1 + reg2);
     T* state = warp_base + pt * band_point_state(L);
     T* sc = state + 2;             // sc[-2], sc[-1] are zeros
     T* ss = sc + (L + 1) + 2;      // ss[-2], ss[-1] are zeros
@@ -199,6 +245,27 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
     T* region2 = region1 + reg1;
 
     for (int e = threadIdx.x; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
+    // pair t of the flattened (l, m) list: l = largest integer with l(l+1)/2 <= t
+    for (int t = threadIdx.x; t < nq; t += blockDim.x) {
+        int l = int((sqrtf(8.0f * float(t) + 1.0f) - 1.0f) * 0.5f);
+        while (tri(l + 1, 0) <= t) ++l;
+        while (tri(l, 0) > t) --l;
+        const int m = t - tri(l, 0);
+        PairDesc d;
+        d.q_off = (l * RS + m) * int(sizeof(T));  // relative to row -2, i.e. row l-2 of the table
+        d.f_off = t * int(sizeof(T));
+        d.kp = l * l + l + m;
+        d.m = m;
+        sDesc[t] = d;
+        if constexpr (NF >= 2) {
+            sFac[t * NF + 0] = T(m);
+            sFac[t * NF + 1] = T(l + m);
+        }
+        if constexpr (NF >= 4) {
+            sFac[t * NF + 2] = T(m * (m - 1));
+            sFac[t * NF + 3] = T((l + m) * (l + m - 1));
+        }
+    }
     // the zero rows and the zeros before c_0, s_0 never change
     for (int e = g; e < BAND_ZERO_ROWS * RS; e += G) sQ[e - BAND_ZERO_ROWS * RS] = T(0);
     if (g == 0) sc[-2] = sc[-1] = ss[-2] = ss[-1] = T(0);
@@ -338,34 +405,30 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         auto finish_pair = [&](const PairInputs<T, LEVEL>& in) {
             Column<T> vp{}, vm{};
             band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
-            const int mid = in.l * in.l + in.l;
-            put(mid + in.m, vp);
-            if (in.m > 0) put(mid - in.m, vm);
-        };
-        auto advance = [&](int& l, int& m) {
-            m += G;
-            while (l <= L && m > l) {
-                m -= l + 1;
-                ++l;
-            }
+            put(in.kp, vp);
+            if (in.m > 0) put(in.kp - 2 * in.m, vm);
         };
 
-        // ---- phase B: pairs (l, m) dealt round-robin to the group's lanes, two in flight per lane
-        int l = 0, m = g - G;
-        advance(l, m);
-        if (!valid) l = L + 1;
-        while (l <= L) {
-            const PairInputs<T, LEVEL> in0 = band_load_pair<T, LEVEL>(l, m, RS, sF, sQ, sc, ss);
-            advance(l, m);
-            if (l <= L) {
-                const PairInputs<T, LEVEL> in1 = band_load_pair<T, LEVEL>(l, m, RS, sF, sQ, sc, ss);
-                advance(l, m);
-                finish_pair(in0);
-                finish_pair(in1);
-            } else {
-                finish_pair(in0);
-            }
+        // ---- phase B: pairs t = g, g + G, ... of the flattened (l, m) list, two in flight per lane
+        const unsigned sF_addr = static_cast<unsigned>(__cvta_generic_to_shared(sF));
+        const unsigned sQ_addr = static_cast<unsigned>(__cvta_generic_to_shared(sQ - BAND_ZERO_ROWS * RS));
+        const unsigned sc_addr = static_cast<unsigned>(__cvta_generic_to_shared(sc - 2));
+        const unsigned ss_addr = static_cast<unsigned>(__cvta_generic_to_shared(ss - 2));
+        const unsigned fac_addr = static_cast<unsigned>(__cvta_generic_to_shared(sFac));
+        const unsigned row_b = unsigned(RS) * unsigned(sizeof(T));
+        constexpr unsigned FAC_B = unsigned(NF) * unsigned(sizeof(T));
+        auto load = [&](int t) {
+            return band_load_pair<T, LEVEL>(sDesc[t], sF_addr, sQ_addr, sc_addr, ss_addr, row_b,
+                                            fac_addr + unsigned(t) * FAC_B);
+        };
+        int t = valid ? g : nq;
+        for (; t + G < nq; t += 2 * G) {
+            const PairInputs<T, LEVEL> in0 = load(t);
+            const PairInputs<T, LEVEL> in1 = load(t + G);
+            finish_pair(in0);
+            finish_pair(in1);
         }
+        if (t < nq) finish_pair(load(t));
 
         if constexpr (!VJP) {
             if (bulk) {

@@ -145,7 +145,11 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
     const size_t ny = size_t(n_columns(L));
     const size_t nq = size_t(n_table(L));
     const bool vjp = kind == 3;
-    const size_t table_bytes = band_align16(2 * nq, elem) * elem;
+    // per CTA: F and K, the per-pair factors (2 per pair with gradients, 4 with Hessians) and the
+    // 16-byte pair descriptors
+    const size_t pair_factors = (vjp || kind == 1) ? 2 : (kind == 2 ? 4 : 0);
+    const size_t table_bytes =
+        (band_align16(2 * nq, elem) + band_align16(nq * pair_factors, elem)) * elem + nq * 16;
     const size_t slack = 16 / elem;
 
     auto per_warp_bytes = [&](int P, bool with_image) {
