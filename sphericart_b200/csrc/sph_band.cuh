@@ -298,9 +298,31 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
 
         __syncwarp();  // the previous group's phase B has finished reading the state
 
-        // ---- phase A1: c_m, s_m, 2(m+1)z. Every lane of the group runs the (serial) recurrence,
-        // lane g keeps the entries m = g mod G.
-        {
+        // ---- phase A1: c_m + i s_m = (x + i y)^m and 2(m+1)z.
+        if constexpr (sizeof(T) == 8) {
+            // float64: lane g builds the powers m = g, g + G, ... from the repeated squares of
+            // x + i y (a dozen dependent operations instead of 2 l_max). The rounding differs from
+            // the serial recurrence by a few ulp, far inside the 1e-12 bar.
+            for (int m = g; m <= L; m += G) {
+                T pr = T(1), pi = T(0);  // running product
+                T wr = x, wi = y;        // (x + i y)^(2^b)
+                for (int bits = m; bits != 0; bits >>= 1) {
+                    if (bits & 1) {
+                        const T nr = pr * wr - pi * wi;
+                        pi = pr * wi + pi * wr;
+                        pr = nr;
+                    }
+                    const T sr = wr * wr - wi * wi;
+                    wi = (wr + wr) * wi;
+                    wr = sr;
+                }
+                sc[m] = pr;
+                ss[m] = pi;
+                stz[m] = T(2 * (m + 1)) * z;
+            }
+        } else {
+            // float32: every lane of the group runs the reference's serial recurrence (so the
+            // rounding follows the reference), lane g keeps the entries m = g mod G.
             T cc = T(1), cs = T(0);
             const T twoz = z + z;
             T ctz = twoz;
@@ -375,30 +397,70 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         }
         __syncwarp();  // table, c/s and (VJP) gradient rows visible; images free
 
+        // shared-memory addresses of this lane's image rows (image modes) or gradient row (VJP)
+        const unsigned ny_b = unsigned(ny) * unsigned(sizeof(T));
+        [[maybe_unused]] const unsigned img0_addr = static_cast<unsigned>(__cvta_generic_to_shared(VJP ? grow : out_sph));
+        [[maybe_unused]] const unsigned img1_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_d));
+        [[maybe_unused]] const unsigned img2_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_dd));
+
         auto put = [&](int k, Column<T> v) {
             if constexpr (NORM && LEVEL >= 1) to_cartesian<T, LEVEL>(v, us);
             if constexpr (VJP) {
-                const T gk = grow[k];
+                const T gk = lds_at<T, 0>(img0_addr + unsigned(k) * unsigned(sizeof(T)));
                 ax += gk * v.gx;
                 ay += gk * v.gy;
                 az += gk * v.gz;
-            } else {
-                out_sph[k] = v.y;
+            } else if constexpr (DIRECT) {
+                // streaming stores: the data is written once and never read back by this kernel
+                __stcs(out_sph + k, v.y);
                 if constexpr (LEVEL >= 1) {
-                    out_d[k] = v.gx;
-                    out_d[ny + k] = v.gy;
-                    out_d[2 * ny + k] = v.gz;
+                    T* d = out_d + k;
+                    __stcs(d, v.gx);
+                    __stcs(d + ny, v.gy);
+                    __stcs(d + 2 * ny, v.gz);
                 }
                 if constexpr (LEVEL >= 2) {
-                    out_dd[0 * ny + k] = v.hxx;
-                    out_dd[1 * ny + k] = v.hxy;
-                    out_dd[2 * ny + k] = v.hxz;
-                    out_dd[3 * ny + k] = v.hxy;
-                    out_dd[4 * ny + k] = v.hyy;
-                    out_dd[5 * ny + k] = v.hyz;
-                    out_dd[6 * ny + k] = v.hxz;
-                    out_dd[7 * ny + k] = v.hyz;
-                    out_dd[8 * ny + k] = v.hzz;
+                    T* h = out_dd + k;
+                    __stcs(h, v.hxx);
+                    __stcs(h + ny, v.hxy);
+                    __stcs(h + 2 * ny, v.hxz);
+                    __stcs(h + 3 * ny, v.hxy);
+                    __stcs(h + 4 * ny, v.hyy);
+                    __stcs(h + 5 * ny, v.hyz);
+                    __stcs(h + 6 * ny, v.hxz);
+                    __stcs(h + 7 * ny, v.hyz);
+                    __stcs(h + 8 * ny, v.hzz);
+                }
+            } else {
+                const unsigned k_b = unsigned(k) * unsigned(sizeof(T));
+                sts_to<T>(img0_addr + k_b, v.y);
+                if constexpr (LEVEL >= 1) {
+                    unsigned ad = img1_addr + k_b;
+                    sts_to<T>(ad, v.gx);
+                    ad += ny_b;
+                    sts_to<T>(ad, v.gy);
+                    ad += ny_b;
+                    sts_to<T>(ad, v.gz);
+                }
+                if constexpr (LEVEL >= 2) {
+                    unsigned ah = img2_addr + k_b;
+                    sts_to<T>(ah, v.hxx);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hxy);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hxz);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hxy);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hyy);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hyz);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hxz);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hyz);
+                    ah += ny_b;
+                    sts_to<T>(ah, v.hzz);
                 }
             }
         };
@@ -417,9 +479,13 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         const unsigned fac_addr = static_cast<unsigned>(__cvta_generic_to_shared(sFac));
         const unsigned row_b = unsigned(RS) * unsigned(sizeof(T));
         constexpr unsigned FAC_B = unsigned(NF) * unsigned(sizeof(T));
+        const unsigned desc_addr = static_cast<unsigned>(__cvta_generic_to_shared(sDesc));
         auto load = [&](int t) {
-            return band_load_pair<T, LEVEL>(sDesc[t], sF_addr, sQ_addr, sc_addr, ss_addr, row_b,
-                                            fac_addr + unsigned(t) * FAC_B);
+            PairDesc d;
+            asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(d.q_off), "=r"(d.f_off), "=r"(d.kp), "=r"(d.m)
+                         : "r"(desc_addr + unsigned(t) * 16u));
+            return band_load_pair<T, LEVEL>(d, sF_addr, sQ_addr, sc_addr, ss_addr, row_b, fac_addr + unsigned(t) * FAC_B);
         };
         int t = valid ? g : nq;
         for (; t + G < nq; t += 2 * G) {

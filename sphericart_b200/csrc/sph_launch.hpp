@@ -47,6 +47,7 @@ template <typename T> struct BandLaunchArgs {
     int mode;
     int warps;
     size_t smem;
+    int grid_cap;  // upper bound on the number of CTAs (0 = none)
 };
 
 template <typename T, int G> struct BandLaunch {

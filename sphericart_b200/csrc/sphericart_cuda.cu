@@ -39,6 +39,7 @@ struct Knobs {
     int force_band;     // route l_max <= 8 through the band kernel too
     int no_bulk;        // copy tiles out with plain stores instead of TMA bulk stores
     int band_direct;    // 1: force direct global stores in the band kernel, -1: forbid them
+    int band_max_ctas;  // cap on resident CTAs per SM of the band kernel (0 = no cap)
 };
 
 int env_int(const char* name, int fallback) {
@@ -51,7 +52,7 @@ const Knobs& knobs() {
     static const Knobs k = {env_int("SPH_B200_BAND_IMAGE_KB", 64), env_int("SPH_B200_BAND_LANES", 0),
                             env_int("SPH_B200_BAND_WARPS", 0),     env_int("SPH_B200_TILE_WARPS", 0),
                             env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0),
-                            env_int("SPH_B200_BAND_DIRECT", 0)};
+                            env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0)};
     return k;
 }
 
@@ -126,6 +127,7 @@ struct BandPlan {
     int warps = 1;    // warps per CTA
     int mode = 0;     // 0 image + TMA bulk stores, 1 image + plain stores, 2 direct global stores
     size_t smem = 0;  // dynamic shared memory per CTA
+    int grid_cap = 0; // upper bound on CTAs (0 = none)
     bool feasible = true;
 };
 
@@ -140,7 +142,7 @@ size_t band_point_state_host(int l_max) {
 }
 
 // kind: 0..2 = forward level, 3 = VJP.
-BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
+BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int sm_count) {
     const int L = l_max;
     const size_t ny = size_t(n_columns(L));
     const size_t nq = size_t(n_table(L));
@@ -214,6 +216,16 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit) {
         }
     }
     plan.warps = warps;
+    plan.grid_cap = 0;
+    if (plan.mode == 2 && forced_warps == 0) {
+        // Direct stores: every warp keeps several write streams open in L2 / DRAM, and measured
+        // throughput peaks at eight warps per SM (12 warps: 12 % slower, 4 warps: 28 % slower on a
+        // B200 at l_max = 32, float64). Two CTAs of four warps.
+        plan.warps = warps = 4;
+        if (table_bytes + 4 * per_warp > smem_limit) plan.warps = warps = 1;
+        plan.grid_cap = (warps == 4 ? 2 : 8) * sm_count;
+    }
+    if (knobs().band_max_ctas > 0) plan.grid_cap = knobs().band_max_ctas * sm_count;
     plan.smem = table_bytes + warps * per_warp;
     if (plan.smem > smem_limit) plan.feasible = false;
     return plan;
@@ -229,10 +241,10 @@ template <typename T> struct CalculatorState {
 
 template <typename T>
 void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int kind, int device, size_t smem_limit,
-                    const BandPlan*& plan, const T*& d_tables) {
+                    int sm_count, const BandPlan*& plan, const T*& d_tables) {
     std::lock_guard<std::mutex> lock(st.mutex);
     if (!st.plan_ready[kind]) {
-        st.plans[kind] = make_band_plan(l_max, kind, sizeof(T), smem_limit);
+        st.plans[kind] = make_band_plan(l_max, kind, sizeof(T), smem_limit, sm_count);
         st.plan_ready[kind] = true;
     }
     if (st.tables[device] == nullptr) {
@@ -260,6 +272,7 @@ BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, const T* d_t
     a.mode = plan.mode;
     a.warps = plan.warps;
     a.smem = plan.smem;
+    a.grid_cap = plan.grid_cap;
     return a;
 }
 
@@ -335,12 +348,27 @@ cudaError_t band_dispatch(int lanes, int level, bool vjp, bool normalized, const
     }
 }
 
-// Warps per CTA for a tile kernel: keep a CTA's images within ~48 KB so several CTAs share an SM.
-int tile_warps(size_t smem_per_warp) {
+// Tile images in flight per CTA. What matters most is the number of images an SM can hold (each
+// one is a tile being drained while others are computed); among the choices that reach the
+// maximum, the largest CTA of at most five warps spreads the warps over the SM's schedulers.
+int tile_warps(size_t smem_per_warp, size_t smem_limit) {
+    if (smem_per_warp == 0) return 4;
     const int forced = knobs().tile_warps;
-    if (forced >= 1 && forced <= 8) return forced;
-    const size_t w = smem_per_warp == 0 ? 8 : (48 * 1024) / smem_per_warp;
-    return int(std::min<size_t>(8, std::max<size_t>(1, w)));
+    int best = 1;
+    size_t best_slots = 0;
+    for (int w = 1; w <= 8; ++w) {
+        const size_t cta = w * smem_per_warp;
+        if (cta > smem_limit) break;
+        size_t n_cta = (smem_limit + 1024) / (cta + 1024);
+        n_cta = std::min<size_t>(n_cta, 32);
+        const size_t slots = std::min<size_t>(64, n_cta * w);
+        if (forced == w) return w;
+        if (slots > best_slots || (slots == best_slots && w <= 5)) {
+            best_slots = slots;
+            best = w;
+        }
+    }
+    return best;
 }
 
 // kind 0..2: forward level; 3: VJP (sph = sph_grad in, dsph = xyz_grad out).
@@ -360,7 +388,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
                                     : TileDispatch<T>::smem_per_warp(l_max, kind);
         if (vjp) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
-            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, tile_warps(per_warp),
+            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, tile_warps(per_warp, props.smem_optin),
                                        use_bulk, scope.device, stream),
                   "tile VJP kernel launch");
             return;
@@ -369,7 +397,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
             if (knobs().no_bulk != 0) use_bulk = false;
             check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables,
-                                           tile_warps(per_warp), use_bulk, scope.device, stream),
+                                           tile_warps(per_warp, props.smem_optin), use_bulk, scope.device, stream),
                   "tile kernel launch");
             return;
         }
@@ -377,7 +405,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
 
     const BandPlan* plan = nullptr;
     const T* d_tables = nullptr;
-    band_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, plan, d_tables);
+    band_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, props.sm_count, plan, d_tables);
     if (!plan->feasible) {
         throw std::runtime_error("sphericart::cuda: l_max is too large for this device's shared memory");
     }
@@ -677,7 +705,7 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
     // host-side tables and launch plan (host heap only)
     std::vector<double> tables(2 * size_t(n_table(l_max)));
     build_tables<double>(l_max, tables.data());
-    const BandPlan plan = make_band_plan(l_max, /*kind=*/1, sizeof(double), props.smem_optin);
+    const BandPlan plan = make_band_plan(l_max, /*kind=*/1, sizeof(double), props.smem_optin, props.sm_count);
     const size_t table_bytes = tables.size() * sizeof(double);
     if (table_bytes > NO_ALLOC_SCRATCH_BYTES || !plan.feasible) {
         throw std::runtime_error("sphericart::cuda: internal tables do not fit the allocation-free array");
