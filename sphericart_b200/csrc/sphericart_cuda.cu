@@ -183,6 +183,8 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
     while (G < 32 && per_warp_bytes(32 / G, true) > budget) G *= 2;
     const int forced = knobs().band_lanes;
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8 || forced == 16 || forced == 32) G = forced;
+    // whatever was asked for, one warp's state and images must fit next to the tables
+    while (G < 32 && table_bytes + per_warp_bytes(32 / G, !vjp) > smem_limit) G *= 2;
 
     // Copy-out mode. With a whole warp per point, rows so long that their image leaves room for
     // fewer than eight warps per SM are stored straight to global memory instead, provided a
@@ -226,6 +228,8 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
         plan.grid_cap = (warps == 4 ? 2 : 8) * sm_count;
     }
     if (knobs().band_max_ctas > 0) plan.grid_cap = knobs().band_max_ctas * sm_count;
+    while (warps > 1 && table_bytes + warps * per_warp > smem_limit) --warps;  // a forced count may not fit
+    plan.warps = warps;
     plan.smem = table_bytes + warps * per_warp;
     if (plan.smem > smem_limit) plan.feasible = false;
     return plan;
