@@ -33,7 +33,7 @@ def test_port_matches_golden_vectors(oracle_mod, golden):
     assert n_cases >= 60
 
 
-def test_golden_corner_cases_are_what_the_survey_observed(golden):
+def test_golden_corner_cases_follow_the_origin_convention(golden):
     """Origin: Y_00 finite and everything else NaN for the normalised harmonics; finite for solid."""
     sph = golden["spherical_f64_l8_lv1_sph_A"]
     dsph = golden["spherical_f64_l8_lv1_dsph_A"]
