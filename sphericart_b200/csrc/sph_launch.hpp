@@ -23,8 +23,10 @@ int persistent_grid(const void* kernel, int block, size_t smem, int device);
 // Tile kernels, l_max = LMAX known at compile time. host_tables = F then K (n_table each).
 template <typename T, int LMAX> struct TileLaunch {
     static size_t smem_per_warp(int level);
+    // warps: images in flight per CTA; span_tiles (1..8): consecutive 32-point tiles per image
     static cudaError_t forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
-                               const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream);
+                               const T* host_tables, int warps, int span_tiles, bool use_bulk, int device,
+                               cudaStream_t stream);
     static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
                            const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream);
     // 1 if a bounded wait inside one of this instantiation's kernels ever gave up on the current

@@ -68,52 +68,70 @@ template <typename T, int LMAX, int LEVEL> constexpr size_t tile_smem_bytes() {
     return size_t(TILE_POINTS) * n_columns(LMAX) * level_components(LEVEL) * sizeof(T);
 }
 
-// blockDim.x = 32 * warps; dynamic shared memory = warps * tile_smem_bytes. Tiles are dealt
+// blockDim.x = 32 * warps; dynamic shared memory = warps * span_tiles * tile_smem_bytes. A warp's
+// unit of work is a span of `span_tiles` consecutive tiles (span_tiles * 32 points): it evaluates
+// them one after the other into one image and hands the whole span to the TMA engine at once, so
+// that small tiles (low l_max, values only) still leave as stores of several KB. Spans are dealt
 // round-robin over all warps of the (persistent) grid.
 template <typename T, int LMAX, int LEVEL, bool NORM>
 __global__ void __launch_bounds__(256)
 sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* __restrict__ dsph,
-                T* __restrict__ ddsph, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk) {
+                T* __restrict__ ddsph, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk, int span_tiles) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
     constexpr int ROW = NY * level_components(LEVEL);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
+    const int span_points = span_tiles * TILE_POINTS;
 
-    T* img_sph = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * ROW;
-    T* img_d = img_sph + TILE_POINTS * NY;
-    T* img_dd = img_sph + TILE_POINTS * NY * 4;
+    // image of one span: [span_points][NY], then [span_points][3][NY], then [span_points][9][NY]
+    T* img_sph = reinterpret_cast<T*>(smem_raw) + size_t(warp) * span_points * ROW;
+    T* img_d = img_sph + span_points * NY;
+    T* img_dd = img_sph + span_points * NY * 4;
 
-    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const long long nspans = (n + span_points - 1) / span_points;
     const long long stride = (long long)gridDim.x * nwarps;
-    for (long long tile = (long long)blockIdx.x * nwarps + warp; tile < ntiles; tile += stride) {
-        const long long first = tile * TILE_POINTS;
-        const long long i = first + lane;
+    for (long long span = (long long)blockIdx.x * nwarps + warp; span < nspans; span += stride) {
+        const long long first = span * span_points;
         // lanes past the end evaluate a harmless point; their rows are never copied out
         T x = T(1), y = T(0), z = T(0);
-        if (i < n) {
-            x = xyz[3 * i + 0];
-            y = xyz[3 * i + 1];
-            z = xyz[3 * i + 2];
+        if (first + lane < n) {
+            x = xyz[3 * (first + lane) + 0];
+            y = xyz[3 * (first + lane) + 1];
+            z = xyz[3 * (first + lane) + 2];
         }
 
-        // the previous tile's bulk stores must be done reading this slice
+        // the previous span's bulk stores must be done reading this slice
         if (use_bulk && lane == 0) bulk_wait_read_all();
         __syncwarp();
 
-        TileSink<T, NY, LEVEL> sink{img_sph + lane * NY, img_d + lane * 3 * NY, img_dd + lane * 9 * NY};
-        eval_point<T, LMAX, LEVEL, NORM>(x, y, z, tab, sink);
+        for (int t = 0; t < span_tiles; ++t) {
+            // fetch the next tile's point while this one is evaluated
+            T nx = T(1), ny_ = T(0), nz = T(0);
+            const long long inext = first + (t + 1) * TILE_POINTS + lane;
+            if (t + 1 < span_tiles && inext < n) {
+                nx = xyz[3 * inext + 0];
+                ny_ = xyz[3 * inext + 1];
+                nz = xyz[3 * inext + 2];
+            }
+            const int row = t * TILE_POINTS + lane;
+            TileSink<T, NY, LEVEL> sink{img_sph + row * NY, img_d + row * 3 * NY, img_dd + row * 9 * NY};
+            eval_point<T, LMAX, LEVEL, NORM>(x, y, z, tab, sink);
+            x = nx;
+            y = ny_;
+            z = nz;
+        }
 
-        const int npts = (n - first) < TILE_POINTS ? int(n - first) : TILE_POINTS;
-        if (use_bulk && npts == TILE_POINTS) {
+        const int npts = (n - first) < span_points ? int(n - first) : span_points;
+        if (use_bulk && npts == span_points) {
             fence_proxy_async_smem();  // make this lane's image writes visible to the TMA engine
             __syncwarp();
             if (lane == 0) {
-                bulk_store_smem_to_global(sph + first * NY, img_sph, unsigned(TILE_POINTS * NY * sizeof(T)));
+                bulk_store_smem_to_global(sph + first * NY, img_sph, unsigned(span_points * NY * sizeof(T)));
                 if constexpr (LEVEL >= 1)
-                    bulk_store_smem_to_global(dsph + first * 3 * NY, img_d, unsigned(TILE_POINTS * 3 * NY * sizeof(T)));
+                    bulk_store_smem_to_global(dsph + first * 3 * NY, img_d, unsigned(span_points * 3 * NY * sizeof(T)));
                 if constexpr (LEVEL >= 2)
-                    bulk_store_smem_to_global(ddsph + first * 9 * NY, img_dd, unsigned(TILE_POINTS * 9 * NY * sizeof(T)));
+                    bulk_store_smem_to_global(ddsph + first * 9 * NY, img_dd, unsigned(span_points * 9 * NY * sizeof(T)));
                 bulk_commit();
             }
         } else {

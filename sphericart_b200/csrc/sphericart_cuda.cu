@@ -40,6 +40,7 @@ struct Knobs {
     int no_bulk;        // copy tiles out with plain stores instead of TMA bulk stores
     int band_direct;    // 1: force direct global stores in the band kernel, -1: forbid them
     int band_max_ctas;  // cap on resident CTAs per SM of the band kernel (0 = no cap)
+    int tile_span;      // force the number of 32-point tiles per image of the tile kernels (1..8)
 };
 
 int env_int(const char* name, int fallback) {
@@ -52,7 +53,8 @@ const Knobs& knobs() {
     static const Knobs k = {env_int("SPH_B200_BAND_IMAGE_KB", 64), env_int("SPH_B200_BAND_LANES", 0),
                             env_int("SPH_B200_BAND_WARPS", 0),     env_int("SPH_B200_TILE_WARPS", 0),
                             env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0),
-                            env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0)};
+                            env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0),
+                            env_int("SPH_B200_TILE_SPAN", 0)};
     return k;
 }
 
@@ -309,13 +311,14 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return 0;
     }
     static cudaError_t forward(int l_max, int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
-                               T* ddsph, const T* tables, int warps, bool use_bulk, int device, cudaStream_t stream) {
+                               T* ddsph, const T* tables, int warps, int span_tiles, bool use_bulk, int device,
+                               cudaStream_t stream) {
         if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::forward(level, normalized, xyz, n, sph, dsph, ddsph, tables, warps, use_bulk,
-                                                device, stream);
+            return TileLaunch<T, LMAX>::forward(level, normalized, xyz, n, sph, dsph, ddsph, tables, warps, span_tiles,
+                                                use_bulk, device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::forward(l_max, level, normalized, xyz, n, sph, dsph, ddsph, tables, warps,
-                                                      use_bulk, device, stream);
+                                                      span_tiles, use_bulk, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
@@ -400,8 +403,15 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         if (per_warp <= TILE_SMEM_LIMIT) {
             bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
             if (knobs().no_bulk != 0) use_bulk = false;
+            // tiles per image: small tiles are grouped so that each bulk store moves about 12 KB or more
+            int span_tiles = knobs().tile_span;
+            if (span_tiles < 1 || span_tiles > 8) {
+                span_tiles = int(std::min<size_t>(8, std::max<size_t>(1, (12 * 1024 + per_warp - 1) / per_warp)));
+            }
+            while (span_tiles > 1 && span_tiles * per_warp > props.smem_optin) --span_tiles;
             check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables,
-                                           tile_warps(per_warp, props.smem_optin), use_bulk, scope.device, stream),
+                                           tile_warps(span_tiles * per_warp, props.smem_optin), span_tiles, use_bulk,
+                                           scope.device, stream),
                   "tile kernel launch");
             return;
         }

@@ -42,17 +42,19 @@ template <typename T, int LMAX> Tables<T, LMAX> make_tables(const T* host_tables
 
 template <typename T, int LMAX, int LEVEL, bool NORM>
 cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph, const T* host_tables, int warps,
-                           bool use_bulk, int device, cudaStream_t stream) {
-    static GridCache cache{};
+                           int span_tiles, bool use_bulk, int device, cudaStream_t stream) {
+    static GridCache cache[9] = {};
+    if (span_tiles < 1 || span_tiles > 8) return cudaErrorInvalidValue;
     auto kernel = sph_tile_kernel<T, LMAX, LEVEL, NORM>;
-    const size_t smem = size_t(warps) * tile_smem_bytes<T, LMAX, LEVEL>();
-    const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
+    const size_t smem = size_t(warps) * span_tiles * tile_smem_bytes<T, LMAX, LEVEL>();
+    const int max_blocks = cached_grid(cache[span_tiles], kernel, warps, smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
-    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
-    const long long want = (ntiles + warps - 1) / warps;
+    const long long span_points = (long long)span_tiles * TILE_POINTS;
+    const long long nspans = (n + span_points - 1) / span_points;
+    const long long want = (nspans + warps - 1) / warps;
     const int grid = int(want < max_blocks ? want : max_blocks);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, n, sph, dsph, ddsph, make_tables<T, LMAX>(host_tables),
-                                               use_bulk ? 1 : 0);
+                                               use_bulk ? 1 : 0, span_tiles);
     return cudaGetLastError();
 }
 
@@ -84,14 +86,14 @@ template <typename T, int LMAX> size_t TileLaunch<T, LMAX>::smem_per_warp(int le
 
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
-                                         T* ddsph, const T* host_tables, int warps, bool use_bulk, int device,
-                                         cudaStream_t stream) {
+                                         T* ddsph, const T* host_tables, int warps, int span_tiles, bool use_bulk,
+                                         int device, cudaStream_t stream) {
 #define SPH_CASE(LEVEL)                                                                                            \
     if constexpr (tile_fits<T, LMAX, LEVEL>()) {                                                                   \
         return normalized ? launch_forward<T, LMAX, LEVEL, true>(xyz, n, sph, dsph, ddsph, host_tables, warps,     \
-                                                                 use_bulk, device, stream)                        \
+                                                                 span_tiles, use_bulk, device, stream)            \
                           : launch_forward<T, LMAX, LEVEL, false>(xyz, n, sph, dsph, ddsph, host_tables, warps,    \
-                                                                  use_bulk, device, stream);                       \
+                                                                  span_tiles, use_bulk, device, stream);           \
     } else {                                                                                                       \
         return cudaErrorInvalidConfiguration;                                                                      \
     }
