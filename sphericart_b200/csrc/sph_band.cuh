@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         [[maybe_unused]] const unsigned img2_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_dd));
 
         auto put = [&](int k, Column<T> v) {
-            if constexpr (NORM && LEVEL >= 1) to_cartesian<T, LEVEL>(v, us);
+            if constexpr (NORM && LEVEL >= 1 && !VJP) to_cartesian<T, LEVEL>(v, us);
             if constexpr (VJP) {
                 const T gk = lds_at<T, 0>(img0_addr + unsigned(k) * unsigned(sizeof(T)));
                 ax += gk * v.gx;
@@ -533,6 +533,13 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                 ax += __shfl_xor_sync(0xffffffffu, ax, off);
                 ay += __shfl_xor_sync(0xffffffffu, ay, off);
                 az += __shfl_xor_sync(0xffffffffu, az, off);
+            }
+            if constexpr (NORM) {
+                // linear chain rule, applied once to the sum of raw gradients
+                const T t = ax * us.x + ay * us.y + az * us.z;
+                ax = (ax - us.x * t) * us.ir;
+                ay = (ay - us.y * t) * us.ir;
+                az = (az - us.z * t) * us.ir;
             }
             if (g == 0 && valid) {
                 a.xyz_grad[3 * i + 0] = ax;

@@ -97,7 +97,9 @@ __device__ __forceinline__ void to_cartesian(Column<T>& v, const UnitSphere<T>& 
 
 // Evaluates all (l_max+1)^2 columns for one point and hands each to sink.put<column>(Column).
 // LEVEL 0: values; 1: + gradient; 2: + Hessian. NORM: evaluate at r/|r| and chain-rule back.
-template <typename T, int LMAX, int LEVEL, bool NORM, typename Sink>
+// RAW: hand over the derivatives with respect to the unit vector instead (a caller that only
+// needs a linear combination of the columns applies the linear chain rule once, to the sum).
+template <typename T, int LMAX, int LEVEL, bool NORM, typename Sink, bool RAW = false>
 __device__ __forceinline__ void eval_point(T x, T y, T z, const Tables<T, LMAX>& tab, Sink& sink) {
     UnitSphere<T> us{x, y, z, T(0), T(0)};
     if constexpr (NORM) {
@@ -114,7 +116,7 @@ __device__ __forceinline__ void eval_point(T x, T y, T z, const Tables<T, LMAX>&
 
     auto emit = [&](auto kc, Column<T> v) {
         constexpr int k = decltype(kc)::value;
-        if constexpr (NORM && LEVEL >= 1) to_cartesian<T, LEVEL>(v, us);
+        if constexpr (NORM && LEVEL >= 1 && !RAW) to_cartesian<T, LEVEL>(v, us);
         sink.template put<k>(v);
     };
 

@@ -285,8 +285,18 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             __syncwarp();
         }
 
+        // The chain rule through r -> r/|r| is linear in the gradient, so it is applied once to the
+        // accumulated sum of raw gradients instead of to each of the (l_max+1)^2 columns.
         VjpSink<T, NY> sink{img[cur] + lane * NY, T(0), T(0), T(0)};
-        eval_point<T, LMAX, 1, NORM>(x, y, z, tab, sink);
+        eval_point<T, LMAX, 1, NORM, VjpSink<T, NY>, true>(x, y, z, tab, sink);
+        if constexpr (NORM) {
+            const T ir = T(1) / sqrt(x * x + y * y + z * z);
+            const T ux = x * ir, uy = y * ir, uz = z * ir;
+            const T t = sink.ax * ux + sink.ay * uy + sink.az * uz;
+            sink.ax = (sink.ax - ux * t) * ir;
+            sink.ay = (sink.ay - uy * t) * ir;
+            sink.az = (sink.az - uz * t) * ir;
+        }
         if (i < n) {
             xyz_grad[3 * i + 0] = sink.ax;
             xyz_grad[3 * i + 1] = sink.ay;
