@@ -36,7 +36,8 @@
 #include <cstdint>
 
 #include "sph_core.cuh"
-#include "sph_tile.cuh"  // bulk-store helpers
+#include "sph_packed.cuh"  // float32: both columns of a pair with packed two-wide instructions
+#include "sph_tile.cuh"    // bulk-store helpers
 
 namespace sph_b200 {
 
@@ -403,8 +404,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         [[maybe_unused]] const unsigned img1_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_d));
         [[maybe_unused]] const unsigned img2_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_dd));
 
-        auto put = [&](int k, Column<T> v) {
-            if constexpr (NORM && LEVEL >= 1 && !VJP) to_cartesian<T, LEVEL>(v, us);
+        auto store_column = [&](int k, const Column<T>& v) {
             if constexpr (VJP) {
                 const T gk = lds_at<T, 0>(img0_addr + unsigned(k) * unsigned(sizeof(T)));
                 ax += gk * v.gx;
@@ -464,11 +464,60 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                 }
             }
         };
+        // float32 with derivatives: the pair's two columns go through the packed two-wide path
+        constexpr bool PACKED = sizeof(T) == 4 && LEVEL >= 1;
+        [[maybe_unused]] UnitSphere2 us2{};
+        if constexpr (PACKED && NORM && !VJP) {
+            UnitSphere<float> usf{float(us.x), float(us.y), float(us.z), float(us.ir), float(us.irsq)};
+            us2 = make_unit_sphere2<LEVEL>(usf);
+        }
         auto finish_pair = [&](const PairInputs<T, LEVEL>& in) {
-            Column<T> vp{}, vm{};
-            band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
-            put(in.kp, vp);
-            if (in.m > 0) put(in.kp - 2 * in.m, vm);
+            if constexpr (PACKED) {
+                PairScalars ps{};
+                ps.f = float(in.f);
+                ps.q = float(in.q);
+                ps.q1a = float(in.q1a);
+                ps.q1b = float(in.q1b);
+                ps.fm = float(in.fm);
+                ps.flm = float(in.flm);
+                F2 cs2 = bc(0.0f);
+                if constexpr (LEVEL >= 2) {
+                    ps.q2a = float(in.q2a);
+                    ps.q2b = float(in.q2b);
+                    ps.q2c = float(in.q2c);
+                    ps.fmm = float(in.fmm);
+                    ps.fz = float(in.fz);
+                    cs2 = f2(float(in.cm2), float(in.sm2));
+                }
+                Column2 v{};
+                eval_pair2<LEVEL>(ps, f2(float(in.cm), float(in.sm)), f2(float(in.cm1), float(in.sm1)), cs2, float(x),
+                                  float(y), float(x2), float(y2), float(xy), v);
+                if constexpr (NORM && !VJP) to_cartesian2<LEVEL>(v, us2);
+                Column<T> vp{}, vm{};
+                vp.y = T(v.y.v.x);    vm.y = T(v.y.v.y);
+                vp.gx = T(v.gx.v.x);  vm.gx = T(v.gx.v.y);
+                vp.gy = T(v.gy.v.x);  vm.gy = T(v.gy.v.y);
+                vp.gz = T(v.gz.v.x);  vm.gz = T(v.gz.v.y);
+                if constexpr (LEVEL >= 2) {
+                    vp.hxx = T(v.hxx.v.x);  vm.hxx = T(v.hxx.v.y);
+                    vp.hxy = T(v.hxy.v.x);  vm.hxy = T(v.hxy.v.y);
+                    vp.hxz = T(v.hxz.v.x);  vm.hxz = T(v.hxz.v.y);
+                    vp.hyy = T(v.hyy.v.x);  vm.hyy = T(v.hyy.v.y);
+                    vp.hyz = T(v.hyz.v.x);  vm.hyz = T(v.hyz.v.y);
+                    vp.hzz = T(v.hzz.v.x);  vm.hzz = T(v.hzz.v.y);
+                }
+                store_column(in.kp, vp);
+                if (in.m > 0) store_column(in.kp - 2 * in.m, vm);
+            } else {
+                Column<T> vp{}, vm{};
+                band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
+                if constexpr (NORM && LEVEL >= 1 && !VJP) {
+                    to_cartesian<T, LEVEL>(vp, us);
+                    to_cartesian<T, LEVEL>(vm, us);
+                }
+                store_column(in.kp, vp);
+                if (in.m > 0) store_column(in.kp - 2 * in.m, vm);
+            }
         };
 
         // ---- phase B: pairs t = g, g + G, ... of the flattened (l, m) list, two in flight per lane
