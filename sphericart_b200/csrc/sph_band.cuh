@@ -50,9 +50,9 @@ __host__ __device__ constexpr int band_row_stride(int l_max) {
     return (l_max + 1 + BAND_ROW_PAD) + ((l_max + 1 + BAND_ROW_PAD) & 1);
 }
 
-// Elements of per-point state: 2 + (l_max+1) for c, the same for s, l_max+1 for 2(m+1)z, the Q table.
+// Elements of per-point state: 2 + (l_max+1) for c, the same for s, then the Q table.
 __host__ __device__ constexpr int band_point_state(int l_max) {
-    return 2 * (l_max + 3) + (l_max + 1) + (l_max + 1 + BAND_ZERO_ROWS) * band_row_stride(l_max);
+    return 2 * (l_max + 3) + (l_max + 1 + BAND_ZERO_ROWS) * band_row_stride(l_max);
 }
 
 // Round an element count up so that the next region starts 16-byte aligned.
@@ -239,8 +239,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
     T* state = warp_base + pt * band_point_state(L);
     T* sc = state + 2;             // sc[-2], sc[-1] are zeros
     T* ss = sc + (L + 1) + 2;      // ss[-2], ss[-1] are zeros
-    T* stz = ss + (L + 1);
-    T* sQ = stz + (L + 1) + BAND_ZERO_ROWS * RS;  // sQ[l * RS + m], rows -2 and -1 are zeros
+    T* sQ = ss + (L + 1) + BAND_ZERO_ROWS * RS;  // sQ[l * RS + m], rows -2 and -1 are zeros
     T* region0 = warp_base + state_elems;
     T* region1 = region0 + reg0;
     T* region2 = region1 + reg1;
@@ -295,72 +294,52 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
             us = UnitSphere<T>{x, y, z, ir, ir * ir};
         }
         const T x2 = x * x, y2 = y * y, xy = x * y;
-        const T rho = x2 + y2;
 
         __syncwarp();  // the previous group's phase B has finished reading the state
 
-        // ---- phase A1: c_m + i s_m = (x + i y)^m and 2(m+1)z.
-        if constexpr (sizeof(T) == 8) {
-            // float64: lane g builds the powers m = g, g + G, ... from the repeated squares of
-            // x + i y (a dozen dependent operations instead of 2 l_max). The rounding differs from
-            // the serial recurrence by a few ulp, far inside the 1e-12 bar.
-            for (int m = g; m <= L; m += G) {
-                T pr = T(1), pi = T(0);  // running product
-                T wr = x, wi = y;        // (x + i y)^(2^b)
-                for (int bits = m; bits != 0; bits >>= 1) {
-                    if (bits & 1) {
-                        const T nr = pr * wr - pi * wi;
-                        pi = pr * wi + pi * wr;
-                        pr = nr;
-                    }
-                    const T sr = wr * wr - wi * wi;
-                    wi = (wr + wr) * wi;
-                    wr = sr;
-                }
-                sc[m] = pr;
-                ss[m] = pi;
-                stz[m] = T(2 * (m + 1)) * z;
-            }
-        } else {
-            // float32: every lane of the group runs the reference's serial recurrence (so the
-            // rounding follows the reference), lane g keeps the entries m = g mod G.
-            T cc = T(1), cs = T(0);
-            const T twoz = z + z;
-            T ctz = twoz;
-            if (g == 0) {
-                sc[0] = cc;
-                ss[0] = cs;
-                stz[0] = ctz;
-            }
-            for (int m = 1; m <= L; ++m) {
-                const T nc = cc * x - cs * y;
-                const T ns = cc * y + cs * x;
-                cc = nc;
-                cs = ns;
-                ctz += twoz;
-                if (m % G == g) {
-                    sc[m] = cc;
-                    ss[m] = cs;
-                    stz[m] = ctz;
-                }
-            }
-        }
-        __syncwarp();
+        // ---- phase A, in float64 for both element types. The recurrences below are where rounding
+        // accumulates (an error growing with l_max in the element type); carried in float64 and rounded
+        // once on storing, they make the float32 results essentially exact up to this point, so that
+        // what separates them from the reference's float32 output is the reference's own rounding
+        // only. The float64 pipe is otherwise idle in the float32 kernels. The inputs are the
+        // element-type coordinates (normalised in the element type, as the reference does).
+        const double xd = double(x), yd = double(y), zd = double(z);
+        const double rhod = xd * xd + yd * yd;
 
-        // ---- phase A2: the Q table, one degree per lane, downward in m
+        // A1: c_m + i s_m = (x + i y)^m. Lane g builds the powers m = g, g + G, ... from the repeated
+        // squares of x + i y: a dozen dependent operations instead of a serial chain of 2 l_max.
+        for (int m = g; m <= L; m += G) {
+            double pr = 1.0, pi = 0.0;  // running product
+            double wr = xd, wi = yd;    // (x + i y)^(2^b)
+            for (int bits = m; bits != 0; bits >>= 1) {
+                if (bits & 1) {
+                    const double nr = pr * wr - pi * wi;
+                    pi = pr * wi + pi * wr;
+                    pr = nr;
+                }
+                const double sr = wr * wr - wi * wi;
+                wi = (wr + wr) * wi;
+                wr = sr;
+            }
+            sc[m] = T(pr);
+            ss[m] = T(pi);
+        }
+
+        // A2: the Q table, one degree per lane, downward in m (the reference's recurrence,
+        // sphericart/include/templates_core.hpp:123,155,202, with 2(m+1)z formed directly)
         for (int l = g; l <= L; l += G) {
             T* row = sQ + l * RS;
             const T* Kl = sK + tri(l, 0);
-            T q2 = Kl[l];  // Q_l^l is tabulated
-            row[l] = q2;
+            double q2 = double(Kl[l]);  // Q_l^l is tabulated
+            row[l] = T(q2);
 #pragma unroll
             for (int j = 1; j <= BAND_ROW_PAD; ++j) row[l + j] = T(0);
             if (l >= 1) {
-                T q1 = -z * q2;  // Q_l^{l-1}
-                row[l - 1] = q1;
+                double q1 = -zd * q2;  // Q_l^{l-1}
+                row[l - 1] = T(q1);
                 for (int m = l - 2; m >= 0; --m) {
-                    const T q0 = Kl[m] * (stz[m] * q1 + rho * q2);
-                    row[m] = q0;
+                    const double q0 = double(Kl[m]) * (double(2 * (m + 1)) * zd * q1 + rhod * q2);
+                    row[m] = T(q0);
                     q2 = q1;
                     q1 = q0;
                 }

@@ -140,7 +140,7 @@ size_t band_align16(size_t elems, size_t elem) {
 }
 int band_row_stride_host(int l_max) { return (l_max + 5) + ((l_max + 5) & 1); }
 size_t band_point_state_host(int l_max) {
-    return 2 * size_t(l_max + 3) + size_t(l_max + 1) + size_t(l_max + 3) * band_row_stride_host(l_max);
+    return 2 * size_t(l_max + 3) + size_t(l_max + 3) * band_row_stride_host(l_max);
 }
 
 // kind: 0..2 = forward level, 3 = VJP.
