@@ -205,6 +205,62 @@ SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_f(
 SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_f(
     sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, float* xyz_grad, void* cuda_stream);
 
+/* Fused second-order backward (no counterpart in the reference's C API): the VJP of the
+ * values-and-gradients map, xyz_grad[i][b] = sum_k sph_grad[i][k] dsph[i][b][k]
+ * + sum_(a,k) dsph_grad[i][a][k] ddsph[i][a][b][k], without materialising dsph or ddsph. Fuses what
+ * sphericart-torch/python/sphericart/torch/register.py:117-145 does with a Hessians launch plus products and
+ * reductions. sph_grad may be NULL. Aborts on failure like the reference's compute calls. */
+SPHERICART_EXPORT void sphericart_cuda_spherical_harmonics_compute_vjp_with_gradients(
+    sphericart_cuda_spherical_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const double* sph_grad, const double* dsph_grad, double* xyz_grad,
+    void* cuda_stream);
+
+/* Status-returning form of compute_vjp_with_gradients. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_spherical_harmonics_try_compute_vjp_with_gradients(
+    sphericart_cuda_spherical_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const double* sph_grad, const double* dsph_grad, double* xyz_grad,
+    void* cuda_stream);
+
+/* Fused second-order backward (no counterpart in the reference's C API): the VJP of the
+ * values-and-gradients map, xyz_grad[i][b] = sum_k sph_grad[i][k] dsph[i][b][k]
+ * + sum_(a,k) dsph_grad[i][a][k] ddsph[i][a][b][k], without materialising dsph or ddsph. Fuses what
+ * sphericart-torch/python/sphericart/torch/register.py:117-145 does with a Hessians launch plus products and
+ * reductions. sph_grad may be NULL. Aborts on failure like the reference's compute calls. */
+SPHERICART_EXPORT void sphericart_cuda_spherical_harmonics_compute_vjp_with_gradients_f(
+    sphericart_cuda_spherical_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, const float* dsph_grad, float* xyz_grad,
+    void* cuda_stream);
+
+/* Status-returning form of compute_vjp_with_gradients. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_spherical_harmonics_try_compute_vjp_with_gradients_f(
+    sphericart_cuda_spherical_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, const float* dsph_grad, float* xyz_grad,
+    void* cuda_stream);
+
+/* Fused second-order backward (no counterpart in the reference's C API): the VJP of the
+ * values-and-gradients map, xyz_grad[i][b] = sum_k sph_grad[i][k] dsph[i][b][k]
+ * + sum_(a,k) dsph_grad[i][a][k] ddsph[i][a][b][k], without materialising dsph or ddsph. Fuses what
+ * sphericart-torch/python/sphericart/torch/register.py:117-145 does with a Hessians launch plus products and
+ * reductions. sph_grad may be NULL. Aborts on failure like the reference's compute calls. */
+SPHERICART_EXPORT void sphericart_cuda_solid_harmonics_compute_vjp_with_gradients(
+    sphericart_cuda_solid_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const double* sph_grad, const double* dsph_grad, double* xyz_grad,
+    void* cuda_stream);
+
+/* Status-returning form of compute_vjp_with_gradients. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_with_gradients(
+    sphericart_cuda_solid_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const double* sph_grad, const double* dsph_grad, double* xyz_grad,
+    void* cuda_stream);
+
+/* Fused second-order backward (no counterpart in the reference's C API): the VJP of the
+ * values-and-gradients map, xyz_grad[i][b] = sum_k sph_grad[i][k] dsph[i][b][k]
+ * + sum_(a,k) dsph_grad[i][a][k] ddsph[i][a][b][k], without materialising dsph or ddsph. Fuses what
+ * sphericart-torch/python/sphericart/torch/register.py:117-145 does with a Hessians launch plus products and
+ * reductions. sph_grad may be NULL. Aborts on failure like the reference's compute calls. */
+SPHERICART_EXPORT void sphericart_cuda_solid_harmonics_compute_vjp_with_gradients_f(
+    sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, const float* dsph_grad, float* xyz_grad,
+    void* cuda_stream);
+
+/* Status-returning form of compute_vjp_with_gradients. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_with_gradients_f(
+    sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, const float* dsph_grad, float* xyz_grad,
+    void* cuda_stream);
+
 /* No counterpart in the reference. Values and gradients (float64, level 1) for hosts that do not
  * let a plugin allocate device memory of its own - a runtime that reserved the whole device arena
  * at start-up, or a latency-bound service loop where cudaMalloc's device-wide synchronisation is

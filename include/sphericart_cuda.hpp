@@ -5,7 +5,8 @@
 // compute_with_hessians signatures, and the same object size and member offsets (the
 // reference's bindings allocate these objects themselves: sphericart-torch/src/torch.cpp:340-349,
 // sphericart-jax/src/sphericart_jax_cuda.cpp:25-40), so code compiled against either header links
-// against this library. One method is added, compute_vjp, which nothing in the reference calls.
+// against this library. Two methods are added, compute_vjp and compute_vjp_with_gradients, which
+// nothing in the reference calls.
 //
 // Contract of every compute call (reference: sphericart/src/sphericart_cuda.cpp:74-160):
 //  * xyz, sph, dsph, ddsph are DEVICE pointers to caller-owned contiguous buffers of
@@ -48,6 +49,16 @@ template <typename T> class SphericalHarmonics {
     /// xyz_grad[i][a] = sum_k sph_grad[i][k] * dsph[i][a][k], with dsph never written to memory.
     /// sph_grad is n_samples x (l_max+1)^2, xyz_grad is n_samples x 3, both device pointers.
     void compute_vjp(const T* xyz, const size_t n_samples, const T* sph_grad, T* xyz_grad, void* cuda_stream = nullptr);
+
+    /// Fused second-order backward (no counterpart in the reference's C++ classes): the
+    /// vector-Jacobian product of the values-and-gradients map,
+    /// xyz_grad[i][b] = sum_k sph_grad[i][k] dsph[i][b][k] + sum_{a,k} dsph_grad[i][a][k] ddsph[i][a][b][k],
+    /// with neither dsph nor ddsph written to memory. sph_grad (n_samples x (l_max+1)^2) may be null,
+    /// dsph_grad is n_samples x 3 x (l_max+1)^2, xyz_grad is n_samples x 3; device pointers.
+    void compute_vjp_with_gradients(
+        const T* xyz, const size_t n_samples, const T* sph_grad, const T* dsph_grad, T* xyz_grad,
+        void* cuda_stream = nullptr
+    );
 
     template <typename U> friend class SolidHarmonics;
 

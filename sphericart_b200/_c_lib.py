@@ -24,7 +24,8 @@ def exported_names():
         for sfx in _SUFFIXES:
             base = f"sphericart_cuda_{kind}_harmonics"
             for fn in ("new", "delete", "compute_array", "compute_array_with_gradients",
-                       "compute_array_with_hessians", "compute_vjp", "try_compute", "try_compute_vjp"):
+                       "compute_array_with_hessians", "compute_vjp", "try_compute", "try_compute_vjp",
+                       "compute_vjp_with_gradients", "try_compute_vjp_with_gradients"):
                 names.append(f"{base}_{fn}{sfx}")
     return names
 
@@ -63,6 +64,8 @@ def get_library():
             bind("compute_vjp", None, [vp, vp, sz, vp, vp, vp])
             bind("try_compute", ci, [vp, ci, vp, sz, vp, vp, vp, vp])
             bind("try_compute_vjp", ci, [vp, vp, sz, vp, vp, vp])
+            bind("compute_vjp_with_gradients", None, [vp, vp, sz, vp, vp, vp, vp])
+            bind("try_compute_vjp_with_gradients", ci, [vp, vp, sz, vp, vp, vp, vp])
     _lib = lib
     return lib
 

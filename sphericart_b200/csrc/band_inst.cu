@@ -35,6 +35,7 @@ cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t str
     k.dsph = a.dsph;
     k.ddsph = a.ddsph;
     k.sph_grad = a.sph_grad;
+    k.dsph_grad = a.dsph_grad;
     k.xyz_grad = a.xyz_grad;
     k.tables = a.d_tables;
     k.l_max = a.l_max;
@@ -64,6 +65,10 @@ template <typename T, int G>
 cudaError_t BandLaunch<T, G>::run(int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
                                   cudaStream_t stream) {
     if (vjp) {
+        if (level >= 2) {
+            return normalized ? launch_band<T, 2, true, G, true, false>(a, device, stream)
+                              : launch_band<T, 2, false, G, true, false>(a, device, stream);
+        }
         return normalized ? launch_band<T, 1, true, G, true, false>(a, device, stream)
                           : launch_band<T, 1, false, G, true, false>(a, device, stream);
     }

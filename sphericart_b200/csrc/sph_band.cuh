@@ -74,8 +74,9 @@ template <typename T> struct BandArgs {
     T* sph;
     T* dsph;
     T* ddsph;
-    const T* sph_grad;  // VJP only
-    T* xyz_grad;        // VJP only
+    const T* sph_grad;   // VJP only (may be null in the second-order VJP)
+    const T* dsph_grad;  // second-order VJP only
+    T* xyz_grad;         // VJP only
     const T* tables;    // F then K, n_table(l_max) entries each
     int l_max;
     int mode;           // BAND_IMAGE_BULK or BAND_IMAGE_PLAIN (ignored by the VJP and by DIRECT kernels)
@@ -232,7 +233,9 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
     PairDesc* sDesc = reinterpret_cast<PairDesc*>(sFac + align16_elems<T>(nq * NF));
     T* warps_base = reinterpret_cast<T*>(sDesc + nq);
     const int state_elems = align16_elems<T>(P * band_point_state(L));
-    const int reg0 = VJP ? align16_elems<T>(P * ny) : (direct ? 0 : band_region<T>(P, 1, ny));
+    // VJP: the staged upstream gradients, [P][ny] of sph_grad (+ [P][3][ny] of dsph_grad at LEVEL 2)
+    constexpr int VJP_ROWS = LEVEL >= 2 ? 4 : 1;
+    const int reg0 = VJP ? align16_elems<T>(P * VJP_ROWS * ny) : (direct ? 0 : band_region<T>(P, 1, ny));
     const int reg1 = (!VJP && !direct && LEVEL >= 1) ? band_region<T>(P, 3, ny) : 0;
     const int reg2 = (!VJP && !direct && LEVEL >= 2) ? band_region<T>(P, 9, ny) : 0;
     T* warp_base = warps_base + size_t(warp) * (state_elems + reg0 + reg1 + reg2);
@@ -368,9 +371,18 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
 
         [[maybe_unused]] T ax = T(0), ay = T(0), az = T(0);  // VJP accumulators
         if constexpr (VJP) {
-            // the P rows of the upstream gradient are one contiguous span: coalesced load
-            const T* gsrc = a.sph_grad + first * ny;
-            for (int e = lane; e < nvalid * ny; e += 32) region0[e] = gsrc[e];
+            // the P rows of each upstream gradient are one contiguous span: coalesced loads
+            if (a.sph_grad != nullptr) {
+                const T* gsrc = a.sph_grad + first * ny;
+                for (int e = lane; e < nvalid * ny; e += 32) region0[e] = gsrc[e];
+            } else {
+                for (int e = lane; e < nvalid * ny; e += 32) region0[e] = T(0);
+            }
+            if constexpr (LEVEL >= 2) {
+                const T* dsrc = a.dsph_grad + first * 3 * ny;
+                T* ddst = region0 + P * ny;
+                for (int e = lane; e < nvalid * 3 * ny; e += 32) ddst[e] = dsrc[e];
+            }
         } else {
             // the engine must be done reading the images of the previous group
             if (bulk && lane == 0) bulk_wait_read_all();
@@ -380,15 +392,30 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         // shared-memory addresses of this lane's image rows (image modes) or gradient row (VJP)
         const unsigned ny_b = unsigned(ny) * unsigned(sizeof(T));
         [[maybe_unused]] const unsigned img0_addr = static_cast<unsigned>(__cvta_generic_to_shared(VJP ? grow : out_sph));
+        [[maybe_unused]] const unsigned vjp_d_addr =
+            static_cast<unsigned>(__cvta_generic_to_shared(region0 + P * ny + pt * 3 * ny));
         [[maybe_unused]] const unsigned img1_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_d));
         [[maybe_unused]] const unsigned img2_addr = direct ? 0u : static_cast<unsigned>(__cvta_generic_to_shared(out_dd));
 
         auto store_column = [&](int k, const Column<T>& v) {
             if constexpr (VJP) {
-                const T gk = lds_at<T, 0>(img0_addr + unsigned(k) * unsigned(sizeof(T)));
+                const unsigned k_b = unsigned(k) * unsigned(sizeof(T));
+                const T gk = lds_at<T, 0>(img0_addr + k_b);
                 ax += gk * v.gx;
                 ay += gk * v.gy;
                 az += gk * v.gz;
+                if constexpr (LEVEL >= 2) {
+                    // second-order backward: contract the Hessian column with the dsph_grad column
+                    unsigned ad = vjp_d_addr + k_b;
+                    const T wx = lds_at<T, 0>(ad);
+                    ad += ny_b;
+                    const T wy = lds_at<T, 0>(ad);
+                    ad += ny_b;
+                    const T wz = lds_at<T, 0>(ad);
+                    ax += wx * v.hxx + wy * v.hxy + wz * v.hxz;
+                    ay += wx * v.hxy + wy * v.hyy + wz * v.hyz;
+                    az += wx * v.hxz + wy * v.hyz + wz * v.hzz;
+                }
             } else if constexpr (DIRECT) {
                 // streaming stores: the data is written once and never read back by this kernel
                 __stcs(out_sph + k, v.y);
@@ -446,7 +473,9 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         // float32 with derivatives: the pair's two columns go through the packed two-wide path
         constexpr bool PACKED = sizeof(T) == 4 && LEVEL >= 1;
         [[maybe_unused]] UnitSphere2 us2{};
-        if constexpr (PACKED && NORM && !VJP) {
+        // (the first-order VJP applies the linear chain rule once to its sum; everything else per column)
+        constexpr bool CHAIN_PER_COLUMN = NORM && LEVEL >= 1 && !(VJP && LEVEL == 1);
+        if constexpr (PACKED && CHAIN_PER_COLUMN) {
             UnitSphere<float> usf{float(us.x), float(us.y), float(us.z), float(us.ir), float(us.irsq)};
             us2 = make_unit_sphere2<LEVEL>(usf);
         }
@@ -471,7 +500,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                 Column2 v{};
                 eval_pair2<LEVEL>(ps, f2(float(in.cm), float(in.sm)), f2(float(in.cm1), float(in.sm1)), cs2, float(x),
                                   float(y), float(x2), float(y2), float(xy), v);
-                if constexpr (NORM && !VJP) to_cartesian2<LEVEL>(v, us2);
+                if constexpr (CHAIN_PER_COLUMN) to_cartesian2<LEVEL>(v, us2);
                 Column<T> vp{}, vm{};
                 vp.y = T(v.y.v.x);    vm.y = T(v.y.v.y);
                 vp.gx = T(v.gx.v.x);  vm.gx = T(v.gx.v.y);
@@ -490,7 +519,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
             } else {
                 Column<T> vp{}, vm{};
                 band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
-                if constexpr (NORM && LEVEL >= 1 && !VJP) {
+                if constexpr (CHAIN_PER_COLUMN) {
                     to_cartesian<T, LEVEL>(vp, us);
                     to_cartesian<T, LEVEL>(vm, us);
                 }
@@ -562,7 +591,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                 ay += __shfl_xor_sync(0xffffffffu, ay, off);
                 az += __shfl_xor_sync(0xffffffffu, az, off);
             }
-            if constexpr (NORM) {
+            if constexpr (NORM && LEVEL == 1) {
                 // linear chain rule, applied once to the sum of raw gradients
                 const T t = ax * us.x + ay * us.y + az * us.z;
                 ax = (ax - us.x * t) * us.ir;

@@ -29,6 +29,9 @@ template <typename T, int LMAX> struct TileLaunch {
                                cudaStream_t stream);
     static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
                            const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream);
+    // second-order backward: VJP of (values, gradients); sph_grad may be null
+    static cudaError_t vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
+                            T* xyz_grad, const T* host_tables, int warps, int device, cudaStream_t stream);
     // 1 if a bounded wait inside one of this instantiation's kernels ever gave up on the current
     // device, 0 if not, -1 if the flag could not be read. Synchronises the device.
     static int device_error_flag();
@@ -43,6 +46,7 @@ template <typename T> struct BandLaunchArgs {
     T* dsph;
     T* ddsph;
     const T* sph_grad;
+    const T* dsph_grad;
     T* xyz_grad;
     const T* d_tables;
     int l_max;
@@ -53,7 +57,7 @@ template <typename T> struct BandLaunchArgs {
 };
 
 template <typename T, int G> struct BandLaunch {
-    // level 0..2 forward, or vjp
+    // level 0..2 forward; vjp with level 1: first-order VJP, with level 2: VJP of (values, gradients)
     static cudaError_t run(int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
                            cudaStream_t stream);
 };

@@ -307,3 +307,96 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
 }
 
 }  // namespace sph_b200
+
+namespace sph_b200 {
+
+// ---------------------------------------------------------------------------------------------
+// Fused second-order backward: the vector-Jacobian product of the values-and-gradients map,
+//   xyz_grad[i][b] = sum_k sph_grad[i][k] dY[i][b][k] + sum_{a,k} dsph_grad[i][a][k] ddY[i][a][b][k],
+// with neither dY nor ddY written to memory. sph_grad may be null (second term only).
+// Replaces the reference's backward of its with_gradients op, which materialises the whole
+// Hessian tensor and then multiplies and reduces it
+// (sphericart-torch/python/sphericart/torch/register.py:117-145, and :101-106, :165-167).
+template <typename T, int NY, bool HAS_VALUE_GRAD> struct Vjp2Sink {
+    const T* gs;  // this point's row of sph_grad (shared memory), unused without HAS_VALUE_GRAD
+    const T* gd;  // this point's [3][NY] rows of dsph_grad (shared memory)
+    T ax, ay, az;
+    template <int K> __device__ __forceinline__ void put(const Column<T>& v) {
+        const T wx = gd[K], wy = gd[NY + K], wz = gd[2 * NY + K];
+        ax += wx * v.hxx + wy * v.hxy + wz * v.hxz;
+        ay += wx * v.hxy + wy * v.hyy + wz * v.hyz;
+        az += wx * v.hxz + wy * v.hyz + wz * v.hzz;
+        if constexpr (HAS_VALUE_GRAD) {
+            const T gk = gs[K];
+            ax += gk * v.gx;
+            ay += gk * v.gy;
+            az += gk * v.gz;
+        }
+    }
+};
+
+// Per warp: the tile's 32 rows of sph_grad ([32][NY]) followed by its rows of dsph_grad ([32][3][NY]).
+template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp2_tile_smem_bytes() {
+    return size_t(TILE_POINTS) * 4 * n_columns(LMAX) * sizeof(T);
+}
+
+// The upstream gradients of a tile are contiguous spans of their arrays; the warp stages them with
+// coalesced loads (this kernel is bound by the Hessian arithmetic, not by these reads).
+template <typename T, int LMAX, bool NORM>
+__global__ void __launch_bounds__(256)
+sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, const T* __restrict__ dsph_grad,
+                     long long n, T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int NY = n_columns(LMAX);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    T* img_s = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * 4 * NY;
+    T* img_d = img_s + TILE_POINTS * NY;
+    const bool has_value_grad = sph_grad != nullptr;
+
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const long long stride = (long long)gridDim.x * nwarps;
+    for (long long tile = (long long)blockIdx.x * nwarps + warp; tile < ntiles; tile += stride) {
+        const long long first = tile * TILE_POINTS;
+        const long long i = first + lane;
+        const int npts = (n - first) < TILE_POINTS ? int(n - first) : TILE_POINTS;
+        T x = T(1), y = T(0), z = T(0);
+        if (i < n) {
+            x = xyz[3 * i + 0];
+            y = xyz[3 * i + 1];
+            z = xyz[3 * i + 2];
+        }
+        __syncwarp();  // previous tile's reads of the images are complete
+        if (has_value_grad) {
+            const T* src = sph_grad + first * NY;
+            for (int e = lane; e < TILE_POINTS * NY; e += 32) img_s[e] = (e < npts * NY) ? src[e] : T(0);
+        }
+        {
+            const T* src = dsph_grad + first * 3 * NY;
+            for (int e = lane; e < TILE_POINTS * 3 * NY; e += 32) img_d[e] = (e < npts * 3 * NY) ? src[e] : T(0);
+        }
+        __syncwarp();
+
+        T ax, ay, az;
+        if (has_value_grad) {
+            Vjp2Sink<T, NY, true> sink{img_s + lane * NY, img_d + lane * 3 * NY, T(0), T(0), T(0)};
+            eval_point<T, LMAX, 2, NORM>(x, y, z, tab, sink);
+            ax = sink.ax;
+            ay = sink.ay;
+            az = sink.az;
+        } else {
+            Vjp2Sink<T, NY, false> sink{img_s, img_d + lane * 3 * NY, T(0), T(0), T(0)};
+            eval_point<T, LMAX, 2, NORM>(x, y, z, tab, sink);
+            ax = sink.ax;
+            ay = sink.ay;
+            az = sink.az;
+        }
+        if (i < n) {
+            xyz_grad[3 * i + 0] = ax;
+            xyz_grad[3 * i + 1] = ay;
+            xyz_grad[3 * i + 2] = az;
+        }
+    }
+}
+
+}  // namespace sph_b200

@@ -143,22 +143,23 @@ size_t band_point_state_host(int l_max) {
     return 2 * size_t(l_max + 3) + size_t(l_max + 3) * band_row_stride_host(l_max);
 }
 
-// kind: 0..2 = forward level, 3 = VJP.
+// kind: 0..2 = forward level, 3 = VJP of the values, 4 = VJP of (values, gradients).
 BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int sm_count) {
     const int L = l_max;
     const size_t ny = size_t(n_columns(L));
     const size_t nq = size_t(n_table(L));
-    const bool vjp = kind == 3;
+    const bool vjp = kind >= 3;
+    const size_t vjp_rows = kind == 4 ? 4 : 1;  // staged upstream-gradient rows per point, in units of ny
     // per CTA: F and K, the per-pair factors (2 per pair with gradients, 4 with Hessians) and the
     // 16-byte pair descriptors
-    const size_t pair_factors = (vjp || kind == 1) ? 2 : (kind == 2 ? 4 : 0);
+    const size_t pair_factors = (kind == 1 || kind == 3) ? 2 : ((kind == 2 || kind == 4) ? 4 : 0);
     const size_t table_bytes =
         (band_align16(2 * nq, elem) + band_align16(nq * pair_factors, elem)) * elem + nq * 16;
     const size_t slack = 16 / elem;
 
     auto per_warp_bytes = [&](int P, bool with_image) {
         size_t e = band_align16(size_t(P) * band_point_state_host(L), elem);
-        if (vjp) return (e + band_align16(size_t(P) * ny, elem)) * elem;
+        if (vjp) return (e + band_align16(size_t(P) * vjp_rows * ny, elem)) * elem;
         if (with_image) {
             e += band_align16(size_t(P) * ny, elem) + slack;
             if (kind >= 1) e += band_align16(size_t(P) * 3 * ny, elem) + slack;
@@ -240,8 +241,8 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
 // Library-owned state of one calculator, reached through the class's prefactors_cuda slot.
 template <typename T> struct CalculatorState {
     std::mutex mutex;
-    BandPlan plans[4];
-    bool plan_ready[4] = {false, false, false, false};
+    BandPlan plans[5];
+    bool plan_ready[5] = {false, false, false, false, false};
     T* tables[MAX_DEVICES] = {};  // device copies of the F and K tables, made on first use per device
 };
 
@@ -264,7 +265,7 @@ void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int
 
 template <typename T>
 BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, const T* d_tables, const T* xyz, long long n,
-                                   T* sph, T* dsph, T* ddsph, const T* sph_grad, T* xyz_grad) {
+                                   T* sph, T* dsph, T* ddsph, const T* sph_grad, const T* dsph_grad, T* xyz_grad) {
     BandLaunchArgs<T> a{};
     a.xyz = xyz;
     a.n = n;
@@ -272,6 +273,7 @@ BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, const T* d_t
     a.dsph = dsph;
     a.ddsph = ddsph;
     a.sph_grad = sph_grad;
+    a.dsph_grad = dsph_grad;
     a.xyz_grad = xyz_grad;
     a.d_tables = d_tables;
     a.l_max = l_max;
@@ -331,6 +333,16 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
                                                   device, stream);
         return cudaErrorInvalidValue;
     }
+    static cudaError_t vjp2(int l_max, bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
+                            T* xyz_grad, const T* tables, int warps, int device, cudaStream_t stream) {
+        if (l_max == LMAX)
+            return TileLaunch<T, LMAX>::vjp2(normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps, device,
+                                             stream);
+        if constexpr (LMAX > 0)
+            return TileDispatch<T, LMAX - 1>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps,
+                                                   device, stream);
+        return cudaErrorInvalidValue;
+    }
     static int error_flags() {
         int flag = TileLaunch<T, LMAX>::device_error_flag();
         if constexpr (LMAX > 0) {
@@ -378,29 +390,39 @@ int tile_warps(size_t smem_per_warp, size_t smem_limit) {
     return best;
 }
 
-// kind 0..2: forward level; 3: VJP (sph = sph_grad in, dsph = xyz_grad out).
+// kind 0..2: forward level; 3: VJP of the values; 4: VJP of (values, gradients).
 template <typename T>
 void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T>& st, int kind, const T* xyz,
-         size_t n_samples, T* sph, T* dsph, T* ddsph, const T* sph_grad, T* xyz_grad, void* cuda_stream) {
+         size_t n_samples, T* sph, T* dsph, T* ddsph, const T* sph_grad, const T* dsph_grad, T* xyz_grad,
+         void* cuda_stream) {
     const int l_max = int(l_max_);
     const long long n = (long long)n_samples;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
     DeviceScope scope(xyz);
     const DeviceProps& props = device_props(scope.device);
-    const bool vjp = kind == 3;
+    const bool vjp = kind >= 3;
     const bool force_band = knobs().force_band != 0;
 
     if (l_max <= TILE_LMAX && !force_band) {
-        const size_t per_warp = vjp ? 2 * size_t(32) * n_columns(l_max) * sizeof(T) + 16
-                                    : TileDispatch<T>::smem_per_warp(l_max, kind);
-        if (vjp) {
+        if (kind == 4) {
+            const size_t vjp2_per_warp = size_t(32) * 4 * n_columns(l_max) * sizeof(T);
+            if (vjp2_per_warp <= TILE_SMEM_LIMIT) {
+                check(TileDispatch<T>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables,
+                                            tile_warps(vjp2_per_warp, props.smem_optin), scope.device, stream),
+                      "tile second-order VJP kernel launch");
+                return;
+            }
+        }
+        const size_t per_warp = kind == 3 ? 2 * size_t(32) * n_columns(l_max) * sizeof(T) + 16
+                                          : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
+        if (kind == 3) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
             check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, tile_warps(per_warp, props.smem_optin),
                                        use_bulk, scope.device, stream),
                   "tile VJP kernel launch");
             return;
         }
-        if (per_warp <= TILE_SMEM_LIMIT) {
+        if (kind < 3 && per_warp <= TILE_SMEM_LIMIT) {
             bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
             if (knobs().no_bulk != 0) use_bulk = false;
             // tiles per image: small tiles are grouped so that each bulk store moves about 12 KB or more
@@ -424,8 +446,9 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         throw std::runtime_error("sphericart::cuda: l_max is too large for this device's shared memory");
     }
     const BandLaunchArgs<T> a =
-        band_launch_args<T>(*plan, l_max, d_tables, xyz, n, sph, dsph, ddsph, sph_grad, xyz_grad);
-    check(band_dispatch<T>(plan->lanes, vjp ? 1 : kind, vjp, normalized, a, scope.device, stream), "band kernel launch");
+        band_launch_args<T>(*plan, l_max, d_tables, xyz, n, sph, dsph, ddsph, sph_grad, dsph_grad, xyz_grad);
+    check(band_dispatch<T>(plan->lanes, kind == 3 ? 1 : (kind == 4 ? 2 : kind), vjp, normalized, a, scope.device, stream),
+          "band kernel launch");
 }
 
 }  // namespace sph_b200
@@ -487,7 +510,7 @@ void SphericalHarmonics<T>::compute_internal(
         throw std::runtime_error("sphericart::cuda: Hessians were requested but ddsph is a null pointer");
     const int level = compute_with_hessian ? 2 : (compute_with_gradients ? 1 : 0);
     sph_b200::run<T>(this->l_max, this->normalized, this->prefactors_cpu, *state_of<T>(this->prefactors_cuda), level, xyz,
-                     n_samples, sph, dsph, ddsph, nullptr, nullptr, cuda_stream);
+                     n_samples, sph, dsph, ddsph, nullptr, nullptr, nullptr, cuda_stream);
 }
 
 template <typename T>
@@ -516,7 +539,19 @@ void SphericalHarmonics<T>::compute_vjp(
     if (sph_grad == nullptr) throw std::runtime_error("sphericart::cuda: sph_grad is a null pointer");
     if (xyz_grad == nullptr) throw std::runtime_error("sphericart::cuda: xyz_grad is a null pointer");
     sph_b200::run<T>(this->l_max, this->normalized, this->prefactors_cpu, *state_of<T>(this->prefactors_cuda), 3, xyz,
-                     n_samples, nullptr, nullptr, nullptr, sph_grad, xyz_grad, cuda_stream);
+                     n_samples, nullptr, nullptr, nullptr, sph_grad, nullptr, xyz_grad, cuda_stream);
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute_vjp_with_gradients(
+    const T* xyz, const size_t n_samples, const T* sph_grad, const T* dsph_grad, T* xyz_grad, void* cuda_stream
+) {
+    if (n_samples == 0) return;
+    if (xyz == nullptr) throw std::runtime_error("sphericart::cuda: xyz is a null pointer");
+    if (dsph_grad == nullptr) throw std::runtime_error("sphericart::cuda: dsph_grad is a null pointer");
+    if (xyz_grad == nullptr) throw std::runtime_error("sphericart::cuda: xyz_grad is a null pointer");
+    sph_b200::run<T>(this->l_max, this->normalized, this->prefactors_cpu, *state_of<T>(this->prefactors_cuda), 4, xyz,
+                     n_samples, nullptr, nullptr, nullptr, sph_grad, dsph_grad, xyz_grad, cuda_stream);
 }
 
 template <typename T> SolidHarmonics<T>::SolidHarmonics(size_t l_max) : SphericalHarmonics<T>(l_max) {
@@ -597,6 +632,12 @@ void level_call(Calculator* c, int level, const T* xyz, size_t n, T* sph, T* dsp
 }
 
 template <typename Calculator, typename T>
+void vjp2_call(Calculator* c, const T* xyz, size_t n, const T* sph_grad, const T* dsph_grad, T* xyz_grad, void* stream) {
+    if (c == nullptr) throw std::runtime_error("sphericart::cuda: calculator is a null pointer");
+    c->compute_vjp_with_gradients(xyz, n, sph_grad, dsph_grad, xyz_grad, stream);
+}
+
+template <typename Calculator, typename T>
 void vjp_call(Calculator* c, const T* xyz, size_t n, const T* sph_grad, T* xyz_grad, void* stream) {
     if (c == nullptr) throw std::runtime_error("sphericart::cuda: calculator is a null pointer");
     c->compute_vjp(xyz, n, sph_grad, xyz_grad, stream);
@@ -652,12 +693,30 @@ extern "C" int sphericart_cuda_device_wait_errors(void) {
         return capi_try([&] { vjp_call(calculator, xyz, n_samples, sph_grad, xyz_grad, cuda_stream); });            \
     }
 
+#define SPH_CAPI_VJP2(KIND, SFX, T)                                                                                  \
+    extern "C" void sphericart_cuda_##KIND##_harmonics_compute_vjp_with_gradients##SFX(                             \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples,         \
+        const T* sph_grad, const T* dsph_grad, T* xyz_grad, void* cuda_stream) {                                    \
+        capi_or_abort([&] { vjp2_call(calculator, xyz, n_samples, sph_grad, dsph_grad, xyz_grad, cuda_stream); });   \
+    }                                                                                                               \
+    extern "C" int sphericart_cuda_##KIND##_harmonics_try_compute_vjp_with_gradients##SFX(                          \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples,         \
+        const T* sph_grad, const T* dsph_grad, T* xyz_grad, void* cuda_stream) {                                    \
+        return capi_try([&] { vjp2_call(calculator, xyz, n_samples, sph_grad, dsph_grad, xyz_grad, cuda_stream); }); \
+    }
+
 SPH_CAPI_FAMILY(spherical, , double)
 SPH_CAPI_FAMILY(spherical, _f, float)
 SPH_CAPI_FAMILY(solid, , double)
 SPH_CAPI_FAMILY(solid, _f, float)
 
+SPH_CAPI_VJP2(spherical, , double)
+SPH_CAPI_VJP2(spherical, _f, float)
+SPH_CAPI_VJP2(solid, , double)
+SPH_CAPI_VJP2(solid, _f, float)
+
 #undef SPH_CAPI_FAMILY
+#undef SPH_CAPI_VJP2
 
 // ---------------------------------------------------------------------------------------------
 // Allocation-free entry point (an addition; the reference has nothing like it).
@@ -740,7 +799,7 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
     }
     const BandLaunchArgs<double> a =
         band_launch_args<double>(plan, l_max, reinterpret_cast<const double*>(dev.scratch), xyz,
-                                 (long long)n_samples, sph, dsph, nullptr, nullptr, nullptr);
+                                 (long long)n_samples, sph, dsph, nullptr, nullptr, nullptr, nullptr);
     check(band_dispatch<double>(plan.lanes, 1, false, normalized, a, scope.device, stream),
           "band kernel launch (allocation-free)");
 }

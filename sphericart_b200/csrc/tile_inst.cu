@@ -74,6 +74,21 @@ cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad
     return cudaGetLastError();
 }
 
+template <typename T, int LMAX, bool NORM>
+cudaError_t launch_vjp2(const T* xyz, const T* sph_grad, const T* dsph_grad, long long n, T* xyz_grad,
+                        const T* host_tables, int warps, int device, cudaStream_t stream) {
+    static GridCache cache{};
+    auto kernel = sph_vjp2_tile_kernel<T, LMAX, NORM>;
+    const size_t smem = size_t(warps) * vjp2_tile_smem_bytes<T, LMAX>();
+    const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const long long want = (ntiles + warps - 1) / warps;
+    const int grid = int(want < max_blocks ? want : max_blocks);
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, dsph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables));
+    return cudaGetLastError();
+}
+
 template <typename T, int LMAX, int LEVEL> constexpr bool tile_fits() {
     return tile_smem_bytes<T, LMAX, LEVEL>() <= TILE_SMEM_LIMIT;
 }
@@ -112,6 +127,14 @@ cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph
     return normalized
                ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, device, stream)
                : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, device, stream);
+}
+
+template <typename T, int LMAX>
+cudaError_t TileLaunch<T, LMAX>::vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
+                                      T* xyz_grad, const T* host_tables, int warps, int device, cudaStream_t stream) {
+    return normalized
+               ? launch_vjp2<T, LMAX, true>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, device, stream)
+               : launch_vjp2<T, LMAX, false>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, device, stream);
 }
 
 template <typename T, int LMAX> int TileLaunch<T, LMAX>::device_error_flag() {

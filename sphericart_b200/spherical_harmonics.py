@@ -121,9 +121,37 @@ class _BaseHarmonics:
         self.compute_vjp_raw(xyz.dtype, _ptr(xyz), n, _ptr(sph_grad), _ptr(xyz_grad), stream)
         return xyz_grad
 
+    def compute_vjp_with_gradients(self, xyz, sph_grad, dsph_grad, out=None) -> torch.Tensor:
+        """Second-order backward in one kernel: ``xyz_grad[i, b] = sum_k sph_grad[i, k] dsph[i, b, k] +
+        sum_{a,k} dsph_grad[i, a, k] ddsph[i, a, b, k]`` with neither dsph nor ddsph in memory.
+        ``sph_grad`` may be ``None``."""
+        xyz = self._validate_xyz(xyz)
+        n = xyz.shape[0]
+        ny = (self._l_max + 1) ** 2
+        if dsph_grad.shape != (n, 3, ny) or dsph_grad.dtype != xyz.dtype or dsph_grad.device != xyz.device:
+            raise ValueError("dsph_grad must match xyz in dtype and device and have shape (n_samples, 3, (l_max+1)^2)")
+        if sph_grad is not None:
+            if sph_grad.shape != (n, ny) or sph_grad.dtype != xyz.dtype or sph_grad.device != xyz.device:
+                raise ValueError("sph_grad must match xyz in dtype and device and have shape (n_samples, (l_max+1)^2)")
+            sph_grad = sph_grad.detach().contiguous()
+        dsph_grad = dsph_grad.detach().contiguous()
+        xyz_grad = torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None else out
+        stream = torch.cuda.current_stream(xyz.device).cuda_stream
+        sfx = "" if xyz.dtype == torch.float64 else "_f"
+        status = getattr(self._lib, f"{self._prefix}_try_compute_vjp_with_gradients{sfx}")(
+            self._calculator(xyz.dtype), _ptr(xyz), n, _ptr(sph_grad), _ptr(dsph_grad), _ptr(xyz_grad), stream)
+        if status != 0:
+            raise RuntimeError(_c_lib.last_error())
+        return xyz_grad
+
     def forward(self, xyz) -> torch.Tensor:
         """Values with autograd support: the backward pass is the fused VJP kernel."""
         return _HarmonicsFunction.apply(xyz, self)
+
+    def forward_with_gradients(self, xyz) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Values and gradients with autograd support (as the reference's ``*_with_gradients`` op):
+        the backward pass is the fused second-order kernel, no Hessian tensor is materialised."""
+        return _HarmonicsWithGradientsFunction.apply(xyz, self)
 
     __call__ = forward
 
@@ -142,6 +170,24 @@ class _HarmonicsFunction(torch.autograd.Function):
         if not ctx.needs_input_grad[0]:
             return None, None
         return ctx.calculator.compute_vjp(xyz, grad_sph), None
+
+
+class _HarmonicsWithGradientsFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xyz, calculator):
+        ctx.calculator = calculator
+        ctx.save_for_backward(xyz)
+        return calculator.compute_with_gradients(xyz)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_sph, grad_dsph):
+        (xyz,) = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None
+        if grad_dsph is None:
+            return ctx.calculator.compute_vjp(xyz, grad_sph), None
+        return ctx.calculator.compute_vjp_with_gradients(xyz, grad_sph, grad_dsph), None
 
 
 class SphericalHarmonics(_BaseHarmonics):

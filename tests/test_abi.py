@@ -25,7 +25,7 @@ def test_library_exports_every_declared_function():
 
     lib = _c_lib.get_library()
     declared = _declared_functions()
-    assert len(declared) == 35, declared
+    assert len(declared) == 43, declared
     for name in declared:
         assert getattr(lib, name) is not None
     assert sorted(declared) == sorted(_c_lib.exported_names())

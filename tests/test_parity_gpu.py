@@ -271,3 +271,50 @@ def test_host_pipeline_round_trip(sb, oracle_mod):
     pipe.run(torch.from_numpy(xyz).pin_memory(), [sph, dsph])
     want = _reference(oracle_mod, xyz, l_max, True, 1)
     _assert_close(oracle_mod, [sph.numpy(), dsph.numpy()], want, l_max, np.float32, "host pipeline")
+
+
+def _vjp2_reference(oracle_mod, xyz, g_sph, g_dsph, l_max, normalized):
+    """float64 contraction of the checker's float64 gradients and Hessians."""
+    x64 = xyz.astype(np.float64)
+    _, dsph, ddsph = _reference(oracle_mod, x64, l_max, normalized, 2)
+    want = np.einsum("nak,nabk->nb", g_dsph.astype(np.float64), ddsph)
+    scale = np.einsum("nak,nabk->nb", np.abs(g_dsph.astype(np.float64)), np.abs(ddsph))
+    if g_sph is not None:
+        want = want + np.einsum("nbk,nk->nb", dsph, g_sph.astype(np.float64))
+        scale = scale + np.einsum("nbk,nk->nb", np.abs(dsph), np.abs(g_sph.astype(np.float64)))
+    return want, np.maximum(scale.max(axis=1, keepdims=True), 1e-300)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_fused_second_order_backward(sb, oracle_mod, dtype):
+    """VJP of (values, gradients) in one kernel against Hessian-then-contract
+    (sphericart-torch/python/sphericart/torch/register.py:117-145), scaled by sum |g| |ddY| per point."""
+    rng = np.random.default_rng(14)
+    dev = torch.device("cuda", 0)
+    tol = 1e-12 if dtype == np.float64 else 1e-5
+    for cls, normalized in _classes(sb):
+        for l_max in (0, 1, 2, 4, 7, 8, 9, 12, 16):
+            for n in (1, 33, 500):
+                ny = (l_max + 1) ** 2
+                xyz = (rng.standard_normal((n, 3)) * 1.4).astype(dtype)
+                g_sph = rng.standard_normal((n, ny)).astype(dtype)
+                g_dsph = rng.standard_normal((n, 3, ny)).astype(dtype)
+                calc = cls(l_max)
+                t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+                for with_values in (True, False):
+                    got = calc.compute_vjp_with_gradients(t(xyz), t(g_sph) if with_values else None, t(g_dsph))
+                    want, scale = _vjp2_reference(oracle_mod, xyz, g_sph if with_values else None, g_dsph, l_max,
+                                                  normalized)
+                    assert (np.abs(got.cpu().numpy() - want) / scale).max() <= tol, (cls.__name__, l_max, n, with_values)
+
+
+def test_autograd_of_values_and_gradients(sb):
+    """gradcheck of the (values, gradients) map, as the reference checks its with_gradients op
+    (sphericart-torch/python/tests/test_autograd.py:126-146)."""
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(1)
+    xyz = (2 * torch.randn(12, 3, dtype=torch.float64, device=dev)).requires_grad_(True)
+    for cls in (sb.SphericalHarmonics, sb.SolidHarmonics):
+        for l_max in (3, 10):
+            calc = cls(l_max)
+            assert torch.autograd.gradcheck(lambda t: calc.forward_with_gradients(t), (xyz,), fast_mode=True)
