@@ -545,6 +545,19 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
             return band_load_pair<T, LEVEL>(d, sF_addr, sQ_addr, sc_addr, ss_addr, row_b, fac_addr + unsigned(t) * FAC_B);
         };
         int t = valid ? g : nq;
+        if constexpr (sizeof(T) == 8) {
+            // float64 arithmetic has long dependent chains: four independent pairs per lane in flight
+            for (; t + 3 * G < nq; t += 4 * G) {
+                const PairInputs<T, LEVEL> in0 = load(t);
+                const PairInputs<T, LEVEL> in1 = load(t + G);
+                const PairInputs<T, LEVEL> in2 = load(t + 2 * G);
+                const PairInputs<T, LEVEL> in3 = load(t + 3 * G);
+                finish_pair(in0);
+                finish_pair(in1);
+                finish_pair(in2);
+                finish_pair(in3);
+            }
+        }
         for (; t + G < nq; t += 2 * G) {
             const PairInputs<T, LEVEL> in0 = load(t);
             const PairInputs<T, LEVEL> in1 = load(t + G);
