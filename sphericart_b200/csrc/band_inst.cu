@@ -26,8 +26,8 @@ cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t str
     constexpr int P = 32 / G;
     const long long ngroups = (a.n + P - 1) / P;
     const long long want = (ngroups + a.warps - 1) / a.warps;
-    int grid = int(want < max_blocks ? want : max_blocks);
-    if (a.grid_cap > 0 && grid > a.grid_cap) grid = a.grid_cap;
+    int grid = work_grid(want, max_blocks, a.iters);
+    if (a.iters <= 0 && a.grid_cap > 0 && grid > a.grid_cap) grid = a.grid_cap;
     BandArgs<T> k{};
     k.xyz = a.xyz;
     k.n = a.n;

@@ -41,6 +41,9 @@ struct Knobs {
     int band_direct;    // 1: force direct global stores in the band kernel, -1: forbid them
     int band_max_ctas;  // cap on resident CTAs per SM of the band kernel (0 = no cap)
     int tile_span;      // force the number of 32-point tiles per image of the tile kernels (1..8)
+    int tile_iters;     // work items per warp of the forward tile kernels (k > 0), -1: persistent launch
+    int vjp_iters;      // the same for the backward tile kernels
+    int band_iters;     // the same for the band kernels
 };
 
 int env_int(const char* name, int fallback) {
@@ -54,9 +57,13 @@ const Knobs& knobs() {
                             env_int("SPH_B200_BAND_WARPS", 0),     env_int("SPH_B200_TILE_WARPS", 0),
                             env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0),
                             env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0),
-                            env_int("SPH_B200_TILE_SPAN", 0)};
+                            env_int("SPH_B200_TILE_SPAN", 0),      env_int("SPH_B200_TILE_ITERS", 0),
+                            env_int("SPH_B200_VJP_ITERS", 0),      env_int("SPH_B200_BAND_ITERS", 0)};
     return k;
 }
+
+// A knob of the *_iters family against the built-in choice: the value handed to work_grid().
+int resolve_iters(int knob, int builtin) { return knob < 0 ? 0 : (knob > 0 ? knob : builtin); }
 
 struct DeviceProps {
     bool known = false;
@@ -129,7 +136,8 @@ struct BandPlan {
     int warps = 1;    // warps per CTA
     int mode = 0;     // 0 image + TMA bulk stores, 1 image + plain stores, 2 direct global stores
     size_t smem = 0;  // dynamic shared memory per CTA
-    int grid_cap = 0; // upper bound on CTAs (0 = none)
+    int grid_cap = 0; // upper bound on CTAs of a persistent launch (0 = none)
+    int iters = 0;    // groups of points per warp (see work_grid() in sph_launch.hpp)
     bool feasible = true;
 };
 
@@ -235,6 +243,11 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
     plan.warps = warps;
     plan.smem = table_bytes + warps * per_warp;
     if (plan.smem > smem_limit) plan.feasible = false;
+    // Short-lived CTAs (see work_grid()); each one rebuilds the tables in shared memory, which a few
+    // dozen groups per warp amortise. Measured on a B200: l_max = 16 float32 Hessians 0.78 -> 0.81 of
+    // the copy peak at 32 groups per warp; l_max = 32 float64 gradients (direct stores) 0.73 -> 0.76
+    // at 4.
+    plan.iters = resolve_iters(knobs().band_iters, plan.mode == 2 ? 4 : 32);
     return plan;
 }
 
@@ -281,6 +294,7 @@ BandLaunchArgs<T> band_launch_args(const BandPlan& plan, int l_max, const T* d_t
     a.warps = plan.warps;
     a.smem = plan.smem;
     a.grid_cap = plan.grid_cap;
+    a.iters = plan.iters;
     return a;
 }
 
@@ -313,34 +327,34 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return 0;
     }
     static cudaError_t forward(int l_max, int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
-                               T* ddsph, const T* tables, int warps, int span_tiles, bool use_bulk, int device,
-                               cudaStream_t stream) {
+                               T* ddsph, const T* tables, int warps, int span_tiles, bool use_bulk, int iters,
+                               int device, cudaStream_t stream) {
         if (l_max == LMAX)
             return TileLaunch<T, LMAX>::forward(level, normalized, xyz, n, sph, dsph, ddsph, tables, warps, span_tiles,
-                                                use_bulk, device, stream);
+                                                use_bulk, iters, device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::forward(l_max, level, normalized, xyz, n, sph, dsph, ddsph, tables, warps,
-                                                      span_tiles, use_bulk, device, stream);
+                                                      span_tiles, use_bulk, iters, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* tables, int warps, bool use_bulk, int device, cudaStream_t stream) {
+                           const T* tables, int warps, bool use_bulk, int iters, int device, cudaStream_t stream) {
         if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, device,
+            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, iters, device,
                                             stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk,
-                                                  device, stream);
+                                                  iters, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp2(int l_max, bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
-                            T* xyz_grad, const T* tables, int warps, int device, cudaStream_t stream) {
+                            T* xyz_grad, const T* tables, int warps, int iters, int device, cudaStream_t stream) {
         if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::vjp2(normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps, device,
-                                             stream);
+            return TileLaunch<T, LMAX>::vjp2(normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps, iters,
+                                             device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps,
-                                                   device, stream);
+                                                   iters, device, stream);
         return cudaErrorInvalidValue;
     }
     static int error_flags() {
@@ -367,9 +381,10 @@ cudaError_t band_dispatch(int lanes, int level, bool vjp, bool normalized, const
     }
 }
 
-// Tile images in flight per CTA. What matters most is the number of images an SM can hold (each
-// one is a tile being drained while others are computed); among the choices that reach the
-// maximum, the largest CTA of at most five warps spreads the warps over the SM's schedulers.
+// Tile images in flight per CTA of a persistent launch. What matters most is the number of images
+// an SM can hold (each one is a tile being drained while others are computed); among the choices
+// that reach the maximum, the largest CTA of at most five warps spreads the warps over the SM's
+// schedulers.
 int tile_warps(size_t smem_per_warp, size_t smem_limit) {
     if (smem_per_warp == 0) return 4;
     const int forced = knobs().tile_warps;
@@ -408,7 +423,8 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             const size_t vjp2_per_warp = size_t(32) * 4 * n_columns(l_max) * sizeof(T);
             if (vjp2_per_warp <= TILE_SMEM_LIMIT) {
                 check(TileDispatch<T>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables,
-                                            tile_warps(vjp2_per_warp, props.smem_optin), scope.device, stream),
+                                            tile_warps(vjp2_per_warp, props.smem_optin),
+                                            resolve_iters(knobs().vjp_iters, 4), scope.device, stream),
                       "tile second-order VJP kernel launch");
                 return;
             }
@@ -417,23 +433,34 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
                                           : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
         if (kind == 3) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
-            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, tile_warps(per_warp, props.smem_optin),
-                                       use_bulk, scope.device, stream),
+            // short-lived CTAs of four warps with four tiles each: measured best on a B200 (l_max = 4)
+            const int iters = resolve_iters(knobs().vjp_iters, 4);
+            int warps = tile_warps(per_warp, props.smem_optin);
+            if (iters > 0 && knobs().tile_warps == 0) warps = int(std::min<size_t>(4, std::max<size_t>(1, props.smem_optin / per_warp)));
+            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters,
+                                       scope.device, stream),
                   "tile VJP kernel launch");
             return;
         }
         if (kind < 3 && per_warp <= TILE_SMEM_LIMIT) {
             bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
             if (knobs().no_bulk != 0) use_bulk = false;
-            // tiles per image: small tiles are grouped so that each bulk store moves about 12 KB or more
+            // One warp and one image per short-lived CTA: a CTA's shared memory is released as soon
+            // as its own image has been read by the TMA engine, and the block scheduler keeps every
+            // SM as full as its shared memory allows (l_max = 8 float32 gradients: five images).
+            const int iters = resolve_iters(knobs().tile_iters, 1);
+            // tiles per image: small tiles are grouped so that each bulk store moves about 8 KB or more
+            // (12 KB for a persistent launch)
+            const size_t store_bytes = iters > 0 ? 8 * 1024 : 12 * 1024;
             int span_tiles = knobs().tile_span;
             if (span_tiles < 1 || span_tiles > 8) {
-                span_tiles = int(std::min<size_t>(8, std::max<size_t>(1, (12 * 1024 + per_warp - 1) / per_warp)));
+                span_tiles = int(std::min<size_t>(8, std::max<size_t>(1, (store_bytes + per_warp - 1) / per_warp)));
             }
             while (span_tiles > 1 && span_tiles * per_warp > props.smem_optin) --span_tiles;
-            check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables,
-                                           tile_warps(span_tiles * per_warp, props.smem_optin), span_tiles, use_bulk,
-                                           scope.device, stream),
+            int warps = tile_warps(span_tiles * per_warp, props.smem_optin);
+            if (iters > 0 && knobs().tile_warps == 0) warps = 1;
+            check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables, warps,
+                                           span_tiles, use_bulk, iters, scope.device, stream),
                   "tile kernel launch");
             return;
         }

@@ -42,7 +42,7 @@ template <typename T, int LMAX> Tables<T, LMAX> make_tables(const T* host_tables
 
 template <typename T, int LMAX, int LEVEL, bool NORM>
 cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph, const T* host_tables, int warps,
-                           int span_tiles, bool use_bulk, int device, cudaStream_t stream) {
+                           int span_tiles, bool use_bulk, int iters, int device, cudaStream_t stream) {
     static GridCache cache[9] = {};
     if (span_tiles < 1 || span_tiles > 8) return cudaErrorInvalidValue;
     auto kernel = sph_tile_kernel<T, LMAX, LEVEL, NORM>;
@@ -52,7 +52,7 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
     const long long span_points = (long long)span_tiles * TILE_POINTS;
     const long long nspans = (n + span_points - 1) / span_points;
     const long long want = (nspans + warps - 1) / warps;
-    const int grid = int(want < max_blocks ? want : max_blocks);
+    const int grid = work_grid(want, max_blocks, iters);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, n, sph, dsph, ddsph, make_tables<T, LMAX>(host_tables),
                                                use_bulk ? 1 : 0, span_tiles);
     return cudaGetLastError();
@@ -60,7 +60,7 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
 
 template <typename T, int LMAX, bool NORM>
 cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, int warps,
-                       bool use_bulk, int device, cudaStream_t stream) {
+                       bool use_bulk, int iters, int device, cudaStream_t stream) {
     static GridCache cache{};
     auto kernel = sph_vjp_tile_kernel<T, LMAX, NORM>;
     const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>();
@@ -68,7 +68,7 @@ cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long want = (ntiles + warps - 1) / warps;
-    const int grid = int(want < max_blocks ? want : max_blocks);
+    const int grid = work_grid(want, max_blocks, iters);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables),
                                                use_bulk ? 1 : 0);
     return cudaGetLastError();
@@ -76,7 +76,7 @@ cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad
 
 template <typename T, int LMAX, bool NORM>
 cudaError_t launch_vjp2(const T* xyz, const T* sph_grad, const T* dsph_grad, long long n, T* xyz_grad,
-                        const T* host_tables, int warps, int device, cudaStream_t stream) {
+                        const T* host_tables, int warps, int iters, int device, cudaStream_t stream) {
     static GridCache cache{};
     auto kernel = sph_vjp2_tile_kernel<T, LMAX, NORM>;
     const size_t smem = size_t(warps) * vjp2_tile_smem_bytes<T, LMAX>();
@@ -84,7 +84,7 @@ cudaError_t launch_vjp2(const T* xyz, const T* sph_grad, const T* dsph_grad, lon
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long want = (ntiles + warps - 1) / warps;
-    const int grid = int(want < max_blocks ? want : max_blocks);
+    const int grid = work_grid(want, max_blocks, iters);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, dsph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables));
     return cudaGetLastError();
 }
@@ -102,13 +102,13 @@ template <typename T, int LMAX> size_t TileLaunch<T, LMAX>::smem_per_warp(int le
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
                                          T* ddsph, const T* host_tables, int warps, int span_tiles, bool use_bulk,
-                                         int device, cudaStream_t stream) {
+                                         int iters, int device, cudaStream_t stream) {
 #define SPH_CASE(LEVEL)                                                                                            \
     if constexpr (tile_fits<T, LMAX, LEVEL>()) {                                                                   \
         return normalized ? launch_forward<T, LMAX, LEVEL, true>(xyz, n, sph, dsph, ddsph, host_tables, warps,     \
-                                                                 span_tiles, use_bulk, device, stream)            \
+                                                                 span_tiles, use_bulk, iters, device, stream)     \
                           : launch_forward<T, LMAX, LEVEL, false>(xyz, n, sph, dsph, ddsph, host_tables, warps,    \
-                                                                  span_tiles, use_bulk, device, stream);           \
+                                                                  span_tiles, use_bulk, iters, device, stream);    \
     } else {                                                                                                       \
         return cudaErrorInvalidConfiguration;                                                                      \
     }
@@ -123,18 +123,22 @@ cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xy
 
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                     const T* host_tables, int warps, bool use_bulk, int device, cudaStream_t stream) {
-    return normalized
-               ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, device, stream)
-               : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, device, stream);
+                                     const T* host_tables, int warps, bool use_bulk, int iters, int device,
+                                     cudaStream_t stream) {
+    return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters, device,
+                                                  stream)
+                      : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters, device,
+                                                   stream);
 }
 
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
-                                      T* xyz_grad, const T* host_tables, int warps, int device, cudaStream_t stream) {
-    return normalized
-               ? launch_vjp2<T, LMAX, true>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, device, stream)
-               : launch_vjp2<T, LMAX, false>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, device, stream);
+                                      T* xyz_grad, const T* host_tables, int warps, int iters, int device,
+                                      cudaStream_t stream) {
+    return normalized ? launch_vjp2<T, LMAX, true>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters, device,
+                                                   stream)
+                      : launch_vjp2<T, LMAX, false>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters,
+                                                    device, stream);
 }
 
 template <typename T, int LMAX> int TileLaunch<T, LMAX>::device_error_flag() {

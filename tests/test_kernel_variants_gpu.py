@@ -1,6 +1,6 @@
 """Parity of the kernel variants that the default dispatch does not reach on every input: the
 run-time-degree kernel for low degrees, its plain-store and direct-store copy-out modes, forced
-lane counts, and the tile kernels without TMA. The variants are selected by the library's
+lane counts, the tile kernels without TMA, and persistent launches against grids of short-lived CTAs. The variants are selected by the library's
 development environment variables, which are read once per process, so each runs in a child
 process that prints its worst scaled error against the CPU checker."""
 
@@ -59,6 +59,9 @@ VARIANTS = [
     {"SPH_B200_FORCE_BAND": "1", "SPH_B200_BAND_LANES": "4", "SPH_B200_BAND_WARPS": "3"},
     {"SPH_B200_BAND_DIRECT": "-1"},
     {"SPH_B200_TILE_WARPS": "3"},
+    # persistent launches instead of grids of short-lived CTAs, and a different split of the work
+    {"SPH_B200_TILE_ITERS": "-1", "SPH_B200_VJP_ITERS": "-1", "SPH_B200_BAND_ITERS": "-1"},
+    {"SPH_B200_TILE_ITERS": "3", "SPH_B200_VJP_ITERS": "1", "SPH_B200_BAND_ITERS": "2", "SPH_B200_TILE_WARPS": "2"},
 ]
 
 
