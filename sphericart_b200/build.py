@@ -3,7 +3,7 @@
 The kernels are instantiated per (type, l_max) and per (type, lanes-per-point) in separate
 objects so the compile parallelises; objects are rebuilt only when a source is newer.
 
-    python -m sphericart_b200.build            # build if out of date
+    python -m sphericart_b200.build            # build if out of date (CUDA library, then the torch operator library)
     python -m sphericart_b200.build --force
 """
 
@@ -86,6 +86,36 @@ def build(force=False, verbose=False, jobs=None):
     return LIB
 
 
+TORCH_OPS_SRC = os.path.join(HERE, "torch_csrc", "torch_ops.cpp")
+TORCH_OPS_LIB = os.path.join(HERE, "libsphericart_b200_torch.so")
+
+
+def build_torch_ops(force=False):
+    """Compile (if needed) the PyTorch operator library over ``libsphericart_b200.so`` with the host
+    compiler against the installed torch's headers; returns its path."""
+    import torch
+
+    build(force=False)
+    newest = max(os.path.getmtime(TORCH_OPS_SRC), os.path.getmtime(os.path.join(INCLUDE, "sphericart_cuda.hpp")))
+    if not force and os.path.exists(TORCH_OPS_LIB) and os.path.getmtime(TORCH_OPS_LIB) >= newest:
+        return TORCH_OPS_LIB
+    tdir = os.path.dirname(torch.__file__)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = [
+        "g++", "-std=c++17", "-O2", "-fPIC", "-shared",
+        f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+        f"-I{tdir}/include", f"-I{tdir}/include/torch/csrc/api/include", f"-I{cuda_home}/include", f"-I{INCLUDE}",
+        TORCH_OPS_SRC, f"-L{HERE}", "-lsphericart_b200", f"-L{tdir}/lib", "-ltorch", "-ltorch_cpu", "-ltorch_cuda",
+        "-lc10", "-lc10_cuda", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tdir}/lib", "-o", TORCH_OPS_LIB,
+    ]
+    out = subprocess.run(cmd, capture_output=True, text=True)
+    if out.returncode != 0:
+        raise RuntimeError(f"building the torch operator library failed:\n{out.stdout}\n{out.stderr}")
+    return TORCH_OPS_LIB
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    if "--no-torch-ops" not in sys.argv:
+        print(build_torch_ops(force="--force" in sys.argv))

@@ -107,6 +107,31 @@ def test_product_code_never_touches_the_oracle():
         if "_build" in dirpath:
             continue
         for name in files:
-            if name.endswith((".py", ".cu", ".cuh", ".hpp", ".h")):
+            if name.endswith((".py", ".cu", ".cuh", ".hpp", ".h", ".cpp")):
                 text = open(os.path.join(dirpath, name)).read()
                 assert "oracle" not in text.lower(), (dirpath, name)
+
+
+def test_torch_operator_library_loads_and_serves_cuda_tensors_only():
+    """The operator library registers the reference's six operator schemas (under its own
+    namespace) plus the fused backward operators; without a GPU nothing can be computed, and a CPU
+    tensor is refused by the dispatcher rather than served by some other path."""
+    import torch
+
+    import sphericart_b200.torch_ops as t
+
+    for prefix in ("spherical_harmonics", "solid_harmonics"):
+        assert str(getattr(t.ops, prefix).default._schema) == f"sphericart_b200::{prefix}(Tensor xyz, int l_max) -> Tensor"
+        assert str(getattr(t.ops, prefix + "_with_gradients").default._schema).endswith("-> (Tensor, Tensor)")
+        assert str(getattr(t.ops, prefix + "_with_hessians").default._schema).endswith("-> (Tensor, Tensor, Tensor)")
+        assert "Tensor? sph_grad" in str(getattr(t.ops, prefix + "_vjp_with_gradients").default._schema)
+    with pytest.raises(NotImplementedError):
+        t.ops.spherical_harmonics(torch.zeros(4, 3), 3)
+    # shape inference needs no device
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        x = torch.empty(10, 3, device="cuda")
+        shapes = [tuple(o.shape) for o in t.ops.solid_harmonics_with_hessians(x, 4)]
+        assert shapes == [(10, 25), (10, 3, 25), (10, 3, 3, 25)]
+        assert tuple(t.ops.spherical_harmonics_vjp(x, torch.empty(10, 25, device="cuda"), 4).shape) == (10, 3)

@@ -318,3 +318,43 @@ def test_autograd_of_values_and_gradients(sb):
         for l_max in (3, 10):
             calc = cls(l_max)
             assert torch.autograd.gradcheck(lambda t: calc.forward_with_gradients(t), (xyz,), fast_mode=True)
+
+
+def test_calls_can_be_recorded_in_a_cuda_graph(sb):
+    """After one ordinary call per calculator, kind of output and device (which builds the per-device
+    tables and kernel attributes), compute calls only enqueue kernels: recorded into a CUDA graph
+    and replayed on new input data they give the results of ordinary calls."""
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(5)
+    n = 5000
+    cases = [(sb.SphericalHarmonics(8), torch.float32, 1), (sb.SolidHarmonics(12), torch.float64, 1),
+             (sb.SphericalHarmonics(4), torch.float32, 0)]
+    for calc, tdtype, level in cases:
+        ny = (calc.l_max + 1) ** 2
+        xyz = torch.from_numpy(rng.standard_normal((n, 3))).to(dev, tdtype)
+        grad = torch.from_numpy(rng.standard_normal((n, ny))).to(dev, tdtype)
+        outs = [torch.zeros(s, dtype=tdtype, device=dev) for s in [(n, ny), (n, 3, ny)][: level + 1]]
+        xyz_grad = torch.zeros((n, 3), dtype=tdtype, device=dev)
+        ptrs = [o.data_ptr() for o in outs] + [None, None]
+
+        def enqueue(stream):
+            calc.compute_raw(tdtype, level, xyz.data_ptr(), n, ptrs[0], ptrs[1], None, stream.cuda_stream)
+            calc.compute_vjp_raw(tdtype, xyz.data_ptr(), n, grad.data_ptr(), xyz_grad.data_ptr(), stream.cuda_stream)
+
+        enqueue(torch.cuda.current_stream(dev))  # ordinary first call
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            enqueue(torch.cuda.current_stream(dev))
+        for _ in range(2):
+            xyz.copy_(torch.from_numpy(rng.standard_normal((n, 3))).to(dev, tdtype))
+            for o in outs:
+                o.zero_()
+            xyz_grad.zero_()
+            graph.replay()
+            torch.cuda.synchronize(dev)
+            replayed = [o.clone() for o in outs] + [xyz_grad.clone()]
+            enqueue(torch.cuda.current_stream(dev))
+            torch.cuda.synchronize(dev)
+            for a, b in zip(replayed, outs + [xyz_grad]):
+                assert torch.equal(a, b)

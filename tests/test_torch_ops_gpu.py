@@ -1,0 +1,209 @@
+"""The PyTorch operators ``torch.ops.sphericart_b200.*`` (C++ operator library over the CUDA
+library): parity with the CPU checker, autograd through the fused backward kernels up to second
+order, the registrations torch needs for tracing and vmap, CUDA-graph capture, and the host cost
+of one call. Modelled on the reference's operator tests
+(sphericart-torch/python/tests/test_autograd.py, test_cuda.py, test_script.py)."""
+
+import time
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import sphericart_b200.torch_ops as t
+
+    return t.ops
+
+
+def _reference(oracle_mod, xyz, l_max, normalized, level):
+    if oracle_mod.have_ref():
+        return oracle_mod.ref_compute(xyz, l_max, normalized, level)
+    return oracle_mod.port_compute(xyz, l_max, normalized, level)
+
+
+@pytest.mark.parametrize("normalized", [True, False])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_operators_match_the_cpu_reference(ops, oracle_mod, normalized, dtype):
+    rng = np.random.default_rng(21)
+    prefix = "spherical_harmonics" if normalized else "solid_harmonics"
+    tol = 1e-12 if dtype == np.float64 else 1e-5
+    for l_max, n in ((0, 7), (5, 1000), (8, 333), (13, 129)):
+        xyz = (rng.standard_normal((n, 3)) * 1.3).astype(dtype)
+        t = torch.from_numpy(xyz).cuda()
+        want = _reference(oracle_mod, xyz, l_max, normalized, 2)
+        results = ([getattr(ops, prefix)(t, l_max)], getattr(ops, prefix + "_with_gradients")(t, l_max),
+                   getattr(ops, prefix + "_with_hessians")(t, l_max))
+        for level, got in enumerate(results):
+            assert len(got) == level + 1
+            for a, b in zip(got, want):
+                assert tuple(a.shape) == b.shape
+                err, bad = oracle_mod.scaled_error(a.cpu().numpy(), b, l_max)
+                assert bad == 0 and err <= tol, (prefix, dtype, l_max, level, err)
+
+
+def test_non_contiguous_input_and_other_streams(ops, oracle_mod):
+    rng = np.random.default_rng(22)
+    wide = torch.from_numpy(rng.standard_normal((500, 6))).cuda()
+    xyz = wide[:, ::2]  # strided view
+    assert not xyz.is_contiguous()
+    want = _reference(oracle_mod, xyz.cpu().numpy().copy(), 6, True, 1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sph, dsph = ops.spherical_harmonics_with_gradients(xyz, 6)
+    side.synchronize()
+    for a, b in zip((sph, dsph), want):
+        err, bad = oracle_mod.scaled_error(a.cpu().numpy(), b, 6)
+        assert bad == 0 and err <= 1e-12
+    empty = ops.solid_harmonics(torch.empty((0, 3), device="cuda"), 4)
+    assert tuple(empty.shape) == (0, 25)
+
+
+def test_bad_arguments_raise(ops):
+    with pytest.raises(NotImplementedError):
+        ops.spherical_harmonics(torch.zeros(4, 3), 3)  # CPU tensor: no kernel for that backend
+    with pytest.raises(RuntimeError, match="shape"):
+        ops.spherical_harmonics(torch.zeros(4, 2, device="cuda"), 3)
+    with pytest.raises(RuntimeError, match="float64 and float32"):
+        ops.spherical_harmonics(torch.zeros(4, 3, device="cuda", dtype=torch.float16), 3)
+    with pytest.raises(RuntimeError, match="sph_grad"):
+        ops.spherical_harmonics_vjp(torch.zeros(4, 3, device="cuda"), torch.zeros(4, 15, device="cuda"), 3)
+    with pytest.raises(RuntimeError, match="l_max"):
+        ops.solid_harmonics(torch.zeros(4, 3, device="cuda"), -1)
+
+
+@pytest.mark.parametrize("prefix", ["spherical_harmonics", "solid_harmonics"])
+def test_first_and_second_order_autograd(ops, prefix):
+    torch.manual_seed(3)
+    xyz = (torch.randn(12, 3, dtype=torch.float64, device="cuda") * 1.2).requires_grad_(True)
+    values = getattr(ops, prefix)
+    gradients = getattr(ops, prefix + "_with_gradients")
+    hessians = getattr(ops, prefix + "_with_hessians")
+    assert torch.autograd.gradcheck(lambda x: values(x, 4), (xyz,), eps=1e-6, atol=1e-6, rtol=1e-6)
+    assert torch.autograd.gradgradcheck(lambda x: values(x, 4), (xyz,), eps=1e-6, atol=1e-5, rtol=1e-5)
+    assert torch.autograd.gradcheck(lambda x: gradients(x, 3), (xyz,), eps=1e-6, atol=1e-6, rtol=1e-6)
+    assert torch.autograd.gradcheck(lambda x: hessians(x, 3)[:2], (xyz,), eps=1e-6, atol=1e-6, rtol=1e-6)
+    # a loss on the Hessians would need third derivatives
+    with pytest.raises(RuntimeError, match="Third derivatives"):
+        hessians(xyz, 3)[2].sum().backward()
+
+
+def test_force_style_training_step_matches_the_materialising_formulation(ops):
+    """Energy = f(Y(xyz)); forces = -dE/dxyz; a loss on the forces back-propagates through the
+    second-order path (reference: sphericart-torch/python/tests/test_nn.py). Compared with the
+    same computation written with the explicit gradient and Hessian tensors."""
+    torch.manual_seed(4)
+    l_max = 5
+    ny = (l_max + 1) ** 2
+    xyz = torch.randn(64, 3, dtype=torch.float64, device="cuda").requires_grad_(True)
+    w = torch.randn(ny, dtype=torch.float64, device="cuda", requires_grad=True)
+    target = torch.randn(64, 3, dtype=torch.float64, device="cuda")
+
+    def loss_fused():
+        energy = (torch.tanh(ops.spherical_harmonics(xyz, l_max)) @ w).sum()
+        (forces,) = torch.autograd.grad(energy, xyz, create_graph=True)
+        return ((forces - target) ** 2).sum()
+
+    def loss_explicit():
+        sph, dsph, _ = ops.spherical_harmonics_with_hessians(xyz, l_max)
+        energy_grad = (1 - torch.tanh(sph) ** 2) * w  # dE/dY
+        forces = torch.einsum("nk,nak->na", energy_grad, dsph)
+        return ((forces - target) ** 2).sum()
+
+    g_fused = torch.autograd.grad(loss_fused(), (xyz, w))
+    g_explicit = torch.autograd.grad(loss_explicit(), (xyz, w))
+    for a, b in zip(g_fused, g_explicit):
+        assert torch.allclose(a, b, rtol=1e-9, atol=1e-9 * float(b.abs().max()))
+
+
+def test_tracing_vmap_and_opcheck(ops):
+    xyz = torch.randn(20, 3, device="cuda", dtype=torch.float64)
+    per_point = torch.vmap(lambda p: ops.spherical_harmonics_with_gradients(p, 3))(xyz)
+    whole = ops.spherical_harmonics_with_gradients(xyz, 3)
+    assert all(torch.equal(a, b) for a, b in zip(per_point, whole))
+    exported = torch.export.export(_Module(ops), (xyz,))
+    assert torch.equal(exported.module()(xyz), ops.solid_harmonics(xyz, 4))
+    sample = xyz.clone().requires_grad_(True)
+    torch.library.opcheck(ops.spherical_harmonics.default, (sample, 3),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+    torch.library.opcheck(ops.solid_harmonics_vjp.default, (sample, torch.randn(20, 16, device="cuda", dtype=torch.float64), 3),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+
+
+class _Module(torch.nn.Module):
+    def __init__(self, ops):
+        super().__init__()
+        self._ops = ops
+
+    def forward(self, xyz):
+        return self._ops.solid_harmonics(xyz, 4)
+
+
+def test_operators_record_into_a_cuda_graph(ops):
+    """Forward and backward of a small model recorded once and replayed on new data; the operators'
+    output allocations come from the graph's private pool."""
+    torch.manual_seed(6)
+    static_xyz = torch.randn(4096, 3, device="cuda")
+    w = torch.randn(81, device="cuda")
+
+    def step(xyz):
+        x = xyz.detach().requires_grad_(True)
+        energy = (ops.spherical_harmonics(x, 8) @ w).sum()
+        (force,) = torch.autograd.grad(energy, x)
+        return force
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step(static_xyz)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = step(static_xyz)
+    for _ in range(2):
+        static_xyz.copy_(torch.randn(4096, 3, device="cuda"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_out, step(static_xyz))
+
+
+def test_host_cost_of_one_call(ops, capsys):
+    """Not a timing bar: prints the host-side cost per call of the operator, of the Python front end
+    and (where it was built) of the reference's own operator layer over the same CUDA library, for a
+    problem so small (64 points, l_max = 8, float64) that the launch path, not the kernel, sets the
+    pace; checks only that the operator is not slower than the Python front end."""
+    import os
+
+    import sphericart_b200
+
+    xyz = torch.randn(64, 3, device="cuda", dtype=torch.float64)
+    calc = sphericart_b200.SphericalHarmonics(8)
+
+    def per_call(fn, reps=2000):
+        for _ in range(50):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps * 1e6
+
+    t_op = per_call(lambda: ops.spherical_harmonics_with_gradients(xyz, 8))
+    t_py = per_call(lambda: calc.compute_with_gradients(xyz))
+    line = f"operator {t_op:.1f} us, python front end {t_py:.1f} us"
+    binding = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                           "libsphericart_torch_binding.so")
+    if os.path.exists(binding):
+        torch.ops.load_library(binding)
+        ref_op = torch.ops.sphericart_torch.spherical_harmonics_with_gradients
+        line += f", reference operator layer over this library {per_call(lambda: ref_op(xyz, 8)):.1f} us"
+    with capsys.disabled():
+        print(f"\n[host cost per call, 64 points l_max=8 f64] {line}")
+    assert t_op <= 1.5 * t_py
