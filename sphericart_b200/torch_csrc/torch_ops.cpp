@@ -17,11 +17,21 @@
 //    set of four calculators (two of them CPU ones) per thread, l_max and device;
 //  * the current stream comes from c10 directly rather than from a helper library loaded at run
 //    time.
-// Autograd, shape inference for tracing and vmap rules are registered from Python
+//  * autograd is registered here, in C++, on the fused backward kernels (the reference registers
+//    Python backward functions that materialise dsph / ddsph and reduce them with tensor
+//    expressions: sphericart-torch/python/sphericart/torch/register.py:82-175):
+//      values                  -> *_vjp (gradients never written to memory); that operator is
+//                                 differentiable again, which gives the values' second-order path;
+//      values and gradients    -> *_vjp_with_gradients (neither gradients nor Hessians written);
+//      values, gradients and Hessians -> contraction of the saved outputs, third derivatives refused.
+// Shape inference for tracing and the vmap rules are registered from Python
 // (sphericart_b200/torch_ops.py), as the reference does for its own operators.
 #include <ATen/ATen.h>
+#include <ATen/core/dispatch/Dispatcher.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <torch/csrc/autograd/autograd_not_implemented_fallback.h>
+#include <torch/csrc/autograd/custom_function.h>
 #include <torch/library.h>
 
 #include <map>
@@ -134,6 +144,152 @@ at::Tensor vjp_with_gradients(const at::Tensor& xyz_in, const c10::optional<at::
     return out;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Autograd. Every operator called below goes back through the dispatcher, so what a backward
+// pass computes is recorded when a graph of it is asked for (create_graph).
+using torch::autograd::AutogradContext;
+using torch::autograd::variable_list;
+
+template <bool NORMALIZED> std::string op_name(const char* suffix) {
+    return std::string("sphericart_b200::") + (NORMALIZED ? "spherical" : "solid") + "_harmonics" + suffix;
+}
+
+template <bool NORMALIZED> at::Tensor call_values(const at::Tensor& xyz, int64_t l_max) {
+    static auto op = c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("").c_str(), "")
+                         .template typed<at::Tensor(const at::Tensor&, int64_t)>();
+    return op.call(xyz, l_max);
+}
+template <bool NORMALIZED> std::tuple<at::Tensor, at::Tensor> call_with_gradients(const at::Tensor& xyz, int64_t l_max) {
+    static auto op = c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("_with_gradients").c_str(), "")
+                         .template typed<std::tuple<at::Tensor, at::Tensor>(const at::Tensor&, int64_t)>();
+    return op.call(xyz, l_max);
+}
+template <bool NORMALIZED>
+std::tuple<at::Tensor, at::Tensor, at::Tensor> call_with_hessians(const at::Tensor& xyz, int64_t l_max) {
+    static auto op = c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("_with_hessians").c_str(), "")
+                         .template typed<std::tuple<at::Tensor, at::Tensor, at::Tensor>(const at::Tensor&, int64_t)>();
+    return op.call(xyz, l_max);
+}
+template <bool NORMALIZED> at::Tensor call_vjp(const at::Tensor& xyz, const at::Tensor& sph_grad, int64_t l_max) {
+    static auto op = c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("_vjp").c_str(), "")
+                         .template typed<at::Tensor(const at::Tensor&, const at::Tensor&, int64_t)>();
+    return op.call(xyz, sph_grad, l_max);
+}
+template <bool NORMALIZED>
+at::Tensor call_vjp_with_gradients(const at::Tensor& xyz, const c10::optional<at::Tensor>& sph_grad,
+                                   const at::Tensor& dsph_grad, int64_t l_max) {
+    static auto op =
+        c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("_vjp_with_gradients").c_str(), "")
+            .template typed<at::Tensor(const at::Tensor&, const c10::optional<at::Tensor>&, const at::Tensor&, int64_t)>();
+    return op.call(xyz, sph_grad, dsph_grad, l_max);
+}
+
+template <bool NORMALIZED> struct ValuesFunction : torch::autograd::Function<ValuesFunction<NORMALIZED>> {
+    static at::Tensor forward(AutogradContext* ctx, const at::Tensor& xyz, int64_t l_max) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        ctx->save_for_backward({xyz});
+        ctx->saved_data["l_max"] = l_max;
+        ctx->set_materialize_grads(false);
+        return call_values<NORMALIZED>(xyz, l_max);
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads) {
+        if (!grads[0].defined()) return {at::Tensor(), at::Tensor()};
+        const auto saved = ctx->get_saved_variables();
+        return {call_vjp<NORMALIZED>(saved[0], grads[0].contiguous(), ctx->saved_data["l_max"].toInt()), at::Tensor()};
+    }
+};
+
+// out[i][a] = sum_k g[i][k] dY[i][a][k]
+template <bool NORMALIZED> struct VjpFunction : torch::autograd::Function<VjpFunction<NORMALIZED>> {
+    static at::Tensor forward(AutogradContext* ctx, const at::Tensor& xyz, const at::Tensor& sph_grad, int64_t l_max) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        ctx->save_for_backward({xyz, sph_grad});
+        ctx->saved_data["l_max"] = l_max;
+        ctx->set_materialize_grads(false);
+        return call_vjp<NORMALIZED>(xyz, sph_grad, l_max);
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads) {
+        if (!grads[0].defined()) return {at::Tensor(), at::Tensor(), at::Tensor()};
+        const auto saved = ctx->get_saved_variables();
+        const at::Tensor& xyz = saved[0];
+        const at::Tensor& g = saved[1];
+        const int64_t l_max = ctx->saved_data["l_max"].toInt();
+        const at::Tensor v = grads[0].contiguous();
+        at::Tensor xyz_grad, g_grad;
+        if (ctx->needs_input_grad(0)) {
+            // d/dxyz[b] = sum_{a,k} v[a] g[k] ddY[a][b][k]: the second-order kernel with dsph_grad = v (x) g
+            xyz_grad = call_vjp_with_gradients<NORMALIZED>(xyz, c10::nullopt, (v.unsqueeze(2) * g.unsqueeze(1)).contiguous(),
+                                                           l_max);
+        }
+        if (ctx->needs_input_grad(1)) {
+            const at::Tensor dsph = std::get<1>(call_with_gradients<NORMALIZED>(xyz, l_max));
+            g_grad = at::einsum("na,nak->nk", {v, dsph});
+        }
+        return {xyz_grad, g_grad, at::Tensor()};
+    }
+};
+
+template <bool NORMALIZED> struct GradientsFunction : torch::autograd::Function<GradientsFunction<NORMALIZED>> {
+    static variable_list forward(AutogradContext* ctx, const at::Tensor& xyz, int64_t l_max) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        ctx->save_for_backward({xyz});
+        ctx->saved_data["l_max"] = l_max;
+        ctx->set_materialize_grads(false);  // an unused output arrives undefined, not as zeros
+        auto r = call_with_gradients<NORMALIZED>(xyz, l_max);
+        return {std::get<0>(r), std::get<1>(r)};
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads) {
+        const auto saved = ctx->get_saved_variables();
+        const int64_t l_max = ctx->saved_data["l_max"].toInt();
+        if (!grads[1].defined()) {
+            if (!grads[0].defined()) return {at::Tensor(), at::Tensor()};
+            return {call_vjp<NORMALIZED>(saved[0], grads[0].contiguous(), l_max), at::Tensor()};
+        }
+        c10::optional<at::Tensor> g0;
+        if (grads[0].defined()) g0 = grads[0].contiguous();
+        return {call_vjp_with_gradients<NORMALIZED>(saved[0], g0, grads[1].contiguous(), l_max), at::Tensor()};
+    }
+};
+
+template <bool NORMALIZED> struct HessiansFunction : torch::autograd::Function<HessiansFunction<NORMALIZED>> {
+    static variable_list forward(AutogradContext* ctx, const at::Tensor& xyz, int64_t l_max) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        auto r = call_with_hessians<NORMALIZED>(xyz, l_max);
+        ctx->save_for_backward({std::get<1>(r), std::get<2>(r)});
+        ctx->set_materialize_grads(false);
+        return {std::get<0>(r), std::get<1>(r), std::get<2>(r)};
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads) {
+        TORCH_CHECK(!grads[2].defined(),
+                    "Third derivatives of the spherical harmonics with respect to the Cartesian coordinates are not "
+                    "supported.");
+        const auto saved = ctx->get_saved_variables();
+        at::Tensor xyz_grad;
+        if (grads[0].defined()) xyz_grad = at::einsum("nk,nak->na", {grads[0], saved[0]});
+        if (grads[1].defined()) {
+            const at::Tensor extra = at::einsum("nak,nabk->nb", {grads[1], saved[1]});
+            xyz_grad = xyz_grad.defined() ? xyz_grad + extra : extra;
+        }
+        return {xyz_grad, at::Tensor()};
+    }
+};
+
+template <bool NORMALIZED> at::Tensor values_autograd(const at::Tensor& xyz, int64_t l_max) {
+    return ValuesFunction<NORMALIZED>::apply(xyz, l_max);
+}
+template <bool NORMALIZED> at::Tensor vjp_autograd(const at::Tensor& xyz, const at::Tensor& sph_grad, int64_t l_max) {
+    return VjpFunction<NORMALIZED>::apply(xyz, sph_grad, l_max);
+}
+template <bool NORMALIZED> std::tuple<at::Tensor, at::Tensor> with_gradients_autograd(const at::Tensor& xyz, int64_t l_max) {
+    auto r = GradientsFunction<NORMALIZED>::apply(xyz, l_max);
+    return {r[0], r[1]};
+}
+template <bool NORMALIZED>
+std::tuple<at::Tensor, at::Tensor, at::Tensor> with_hessians_autograd(const at::Tensor& xyz, int64_t l_max) {
+    auto r = HessiansFunction<NORMALIZED>::apply(xyz, l_max);
+    return {r[0], r[1], r[2]};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(sphericart_b200, m) {
@@ -158,4 +314,17 @@ TORCH_LIBRARY_IMPL(sphericart_b200, CUDA, m) {
     m.impl("solid_harmonics_with_hessians", &with_hessians<false>);
     m.impl("solid_harmonics_vjp", &vjp<false>);
     m.impl("solid_harmonics_vjp_with_gradients", &vjp_with_gradients<false>);
+}
+
+TORCH_LIBRARY_IMPL(sphericart_b200, Autograd, m) {
+    m.impl("spherical_harmonics", &values_autograd<true>);
+    m.impl("spherical_harmonics_with_gradients", &with_gradients_autograd<true>);
+    m.impl("spherical_harmonics_with_hessians", &with_hessians_autograd<true>);
+    m.impl("spherical_harmonics_vjp", &vjp_autograd<true>);
+    m.impl("spherical_harmonics_vjp_with_gradients", torch::autograd::autogradNotImplementedFallback());
+    m.impl("solid_harmonics", &values_autograd<false>);
+    m.impl("solid_harmonics_with_gradients", &with_gradients_autograd<false>);
+    m.impl("solid_harmonics_with_hessians", &with_hessians_autograd<false>);
+    m.impl("solid_harmonics_vjp", &vjp_autograd<false>);
+    m.impl("solid_harmonics_vjp_with_gradients", torch::autograd::autogradNotImplementedFallback());
 }
