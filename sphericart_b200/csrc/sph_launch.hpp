@@ -19,6 +19,7 @@ constexpr size_t TILE_SMEM_LIMIT = 100 * 1024;
 // the given block size and dynamic shared memory (also raises the kernel's dynamic shared
 // memory limit). Results are cached by the callers.
 int persistent_grid(const void* kernel, int block, size_t smem, int device);
+int device_sm_count(int device);
 
 // Every kernel walks its work items (spans of tiles, groups of points) with a grid-stride loop, so
 // the grid size alone decides how the work is divided:
@@ -41,10 +42,11 @@ inline int work_grid(long long ctas_wanted, int resident, int iters) {
 template <typename T, int LMAX> struct TileLaunch {
     static size_t smem_per_warp(int level);
     // warps: images in flight per CTA; span_tiles (1..8): consecutive 32-point tiles per image;
-    // iters: see work_grid()
+    // iters: see work_grid(); tile_points: 32, 16 or 8 points per tile, 0 = the widest tile with which
+    // the call fits in one wave of resident CTAs (32 when none does)
     static cudaError_t forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
-                               const T* host_tables, int warps, int span_tiles, bool use_bulk, int iters, int device,
-                               cudaStream_t stream);
+                               const T* host_tables, int warps, int span_tiles, bool use_bulk, int iters,
+                               int tile_points, int device, cudaStream_t stream);
     static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
                            const T* host_tables, int warps, bool use_bulk, int iters, int device, cudaStream_t stream);
     // second-order backward: VJP of (values, gradients); sph_grad may be null

@@ -40,9 +40,9 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 
 // Writes one point's columns into the tile image held in shared memory.
 template <typename T, int NY, int LEVEL> struct TileSink {
-    T* sph;    // this point's row of the [32][NY] image
-    T* dsph;   // this point's row of the [32][3][NY] image
-    T* ddsph;  // this point's row of the [32][9][NY] image
+    T* sph;    // this point's row of the [points][NY] image
+    T* dsph;   // this point's row of the [points][3][NY] image
+    T* ddsph;  // this point's row of the [points][9][NY] image
     template <int K> __device__ __forceinline__ void put(const Column<T>& v) {
         sph[K] = v.y;
         if constexpr (LEVEL >= 1) {
@@ -68,21 +68,27 @@ template <typename T, int LMAX, int LEVEL> constexpr size_t tile_smem_bytes() {
     return size_t(TILE_POINTS) * n_columns(LMAX) * level_components(LEVEL) * sizeof(T);
 }
 
-// blockDim.x = 32 * warps; dynamic shared memory = warps * span_tiles * tile_smem_bytes. A warp's
-// unit of work is a span of `span_tiles` consecutive tiles (span_tiles * 32 points): it evaluates
-// them one after the other into one image and hands the whole span to the TMA engine at once, so
-// that small tiles (low l_max, values only) still leave as stores of several KB. Spans are dealt
-// round-robin over all warps of the (persistent) grid.
+// blockDim.x = 32 * warps; dynamic shared memory = warps * span_tiles * tile_smem_bytes * tile_points / 32.
+// A warp's unit of work is a span of `span_tiles` consecutive tiles (span_tiles * tile_points
+// points): it evaluates them one after the other into one image and hands the whole span to the
+// TMA engine at once, so that small tiles (low l_max, values only) still leave as stores of several
+// KB. Spans are dealt round-robin over all warps of the grid.
+// tile_points is 32, or 16 or 8 where whole-warp tiles would leave SMs without work (small calls)
+// or with too few images in flight (large rows). The lanes beyond tile_points repeat the work of
+// lane (lane mod tile_points) and store the same values to the same places, so the evaluation
+// code carries no predicate.
 template <typename T, int LMAX, int LEVEL, bool NORM>
 __global__ void __launch_bounds__(256)
 sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* __restrict__ dsph,
-                T* __restrict__ ddsph, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk, int span_tiles) {
+                T* __restrict__ ddsph, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk, int span_tiles,
+                int tile_points) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
     constexpr int ROW = NY * level_components(LEVEL);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    const int span_points = span_tiles * TILE_POINTS;
+    const int span_points = span_tiles * tile_points;
+    const int pt = lane & (tile_points - 1);  // this lane's point within a tile
 
     // image of one span: [span_points][NY], then [span_points][3][NY], then [span_points][9][NY]
     T* img_sph = reinterpret_cast<T*>(smem_raw) + size_t(warp) * span_points * ROW;
@@ -95,10 +101,10 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
         const long long first = span * span_points;
         // lanes past the end evaluate a harmless point; their rows are never copied out
         T x = T(1), y = T(0), z = T(0);
-        if (first + lane < n) {
-            x = xyz[3 * (first + lane) + 0];
-            y = xyz[3 * (first + lane) + 1];
-            z = xyz[3 * (first + lane) + 2];
+        if (first + pt < n) {
+            x = xyz[3 * (first + pt) + 0];
+            y = xyz[3 * (first + pt) + 1];
+            z = xyz[3 * (first + pt) + 2];
         }
 
         // the previous span's bulk stores must be done reading this slice
@@ -108,13 +114,13 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
         for (int t = 0; t < span_tiles; ++t) {
             // fetch the next tile's point while this one is evaluated
             T nx = T(1), ny_ = T(0), nz = T(0);
-            const long long inext = first + (t + 1) * TILE_POINTS + lane;
+            const long long inext = first + (t + 1) * tile_points + pt;
             if (t + 1 < span_tiles && inext < n) {
                 nx = xyz[3 * inext + 0];
                 ny_ = xyz[3 * inext + 1];
                 nz = xyz[3 * inext + 2];
             }
-            const int row = t * TILE_POINTS + lane;
+            const int row = t * tile_points + pt;
             TileSink<T, NY, LEVEL> sink{img_sph + row * NY, img_d + row * 3 * NY, img_dd + row * 9 * NY};
             eval_point<T, LMAX, LEVEL, NORM>(x, y, z, tab, sink);
             x = nx;

@@ -44,6 +44,7 @@ struct Knobs {
     int tile_iters;     // work items per warp of the forward tile kernels (k > 0), -1: persistent launch
     int vjp_iters;      // the same for the backward tile kernels
     int band_iters;     // the same for the band kernels
+    int tile_points;    // force the points per tile of the forward tile kernels (8, 16 or 32)
 };
 
 int env_int(const char* name, int fallback) {
@@ -58,7 +59,8 @@ const Knobs& knobs() {
                             env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0),
                             env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0),
                             env_int("SPH_B200_TILE_SPAN", 0),      env_int("SPH_B200_TILE_ITERS", 0),
-                            env_int("SPH_B200_VJP_ITERS", 0),      env_int("SPH_B200_BAND_ITERS", 0)};
+                            env_int("SPH_B200_VJP_ITERS", 0),      env_int("SPH_B200_BAND_ITERS", 0),
+                            env_int("SPH_B200_TILE_POINTS", 0)};
     return k;
 }
 
@@ -89,10 +91,19 @@ const DeviceProps& device_props(int device) {
 
 }  // namespace
 
+int device_sm_count(int device) { return device_props(device).sm_count; }
+
 int persistent_grid(const void* kernel, int block, size_t smem, int device) {
     const DeviceProps& props = device_props(device);
     if (smem > props.smem_optin) return 0;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+    // the limit is only ever raised: one kernel may be launched with several image sizes
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (size_t(attr.maxDynamicSharedSizeBytes) < smem &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -328,13 +339,13 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
     }
     static cudaError_t forward(int l_max, int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
                                T* ddsph, const T* tables, int warps, int span_tiles, bool use_bulk, int iters,
-                               int device, cudaStream_t stream) {
+                               int tile_points, int device, cudaStream_t stream) {
         if (l_max == LMAX)
             return TileLaunch<T, LMAX>::forward(level, normalized, xyz, n, sph, dsph, ddsph, tables, warps, span_tiles,
-                                                use_bulk, iters, device, stream);
+                                                use_bulk, iters, tile_points, device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::forward(l_max, level, normalized, xyz, n, sph, dsph, ddsph, tables, warps,
-                                                      span_tiles, use_bulk, iters, device, stream);
+                                                      span_tiles, use_bulk, iters, tile_points, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
@@ -459,8 +470,10 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             while (span_tiles > 1 && span_tiles * per_warp > props.smem_optin) --span_tiles;
             int warps = tile_warps(span_tiles * per_warp, props.smem_optin);
             if (iters > 0 && knobs().tile_warps == 0) warps = 1;
+            int tile_points = knobs().tile_points;
+            if (tile_points != 8 && tile_points != 16 && tile_points != 32) tile_points = 0;
             check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables, warps,
-                                           span_tiles, use_bulk, iters, scope.device, stream),
+                                           span_tiles, use_bulk, iters, tile_points, scope.device, stream),
                   "tile kernel launch");
             return;
         }

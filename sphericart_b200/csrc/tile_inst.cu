@@ -42,19 +42,53 @@ template <typename T, int LMAX> Tables<T, LMAX> make_tables(const T* host_tables
 
 template <typename T, int LMAX, int LEVEL, bool NORM>
 cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph, const T* host_tables, int warps,
-                           int span_tiles, bool use_bulk, int iters, int device, cudaStream_t stream) {
-    static GridCache cache[9] = {};
+                           int span_tiles, bool use_bulk, int iters, int tile_points, int device, cudaStream_t stream) {
+    static GridCache cache[3][9] = {};
     if (span_tiles < 1 || span_tiles > 8) return cudaErrorInvalidValue;
     auto kernel = sph_tile_kernel<T, LMAX, LEVEL, NORM>;
-    const size_t smem = size_t(warps) * span_tiles * tile_smem_bytes<T, LMAX, LEVEL>();
-    const int max_blocks = cached_grid(cache[span_tiles], kernel, warps, smem, device);
-    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
-    const long long span_points = (long long)span_tiles * TILE_POINTS;
+    // Points per tile. For throughput: the widest tile of which an SM holds at least four images
+    // (measured on a B200, l_max = 8 gradients, 10^6 points: float64 32 / 16 / 8 points -> 0.70 / 0.96 /
+    // 0.84 of the copy peak with 2 / 4 / 10 images per SM; float32 32 / 16 -> 1.03 / 0.98 with 5 / 10).
+    // For calls that fit in one wave of resident CTAs a tile's latency is what counts: narrower
+    // tiles still, as long as the call keeps fitting in one wave.
+    const int candidates[3] = {32, 16, 8};
+    const int sms = device_sm_count(device);
+    int chosen = -1, max_blocks = 0;
+    size_t smem = 0;
+    auto query = [&](int c) {
+        smem = size_t(warps) * span_tiles * tile_smem_bytes<T, LMAX, LEVEL>() * candidates[c] / TILE_POINTS;
+        max_blocks = cached_grid(cache[c][span_tiles], kernel, warps, smem, device);
+    };
+    auto ctas_needed = [&](int c) {
+        const long long span_points = (long long)span_tiles * candidates[c];
+        return ((n + span_points - 1) / span_points + warps - 1) / warps;
+    };
+    for (int c = 0; c < 3 && chosen < 0; ++c) {
+        if (tile_points != 0 && tile_points != candidates[c]) continue;
+        query(c);
+        if (max_blocks <= 0) {
+            if (tile_points != 0) return cudaErrorLaunchOutOfResources;
+            continue;
+        }
+        if (tile_points != 0 || c == 2 || max_blocks * warps >= 4 * sms) chosen = c;
+    }
+    if (chosen < 0) return tile_points != 0 ? cudaErrorInvalidValue : cudaErrorLaunchOutOfResources;
+    if (tile_points == 0 && ctas_needed(chosen) <= max_blocks) {
+        // one wave: narrow the tile while the call still fits in one wave
+        while (chosen < 2) {
+            query(chosen + 1);
+            if (max_blocks <= 0 || ctas_needed(chosen + 1) > max_blocks) break;
+            ++chosen;
+        }
+    }
+    query(chosen);
+    const int tp = candidates[chosen];
+    const long long span_points = (long long)span_tiles * tp;
     const long long nspans = (n + span_points - 1) / span_points;
     const long long want = (nspans + warps - 1) / warps;
     const int grid = work_grid(want, max_blocks, iters);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, n, sph, dsph, ddsph, make_tables<T, LMAX>(host_tables),
-                                               use_bulk ? 1 : 0, span_tiles);
+                                               use_bulk ? 1 : 0, span_tiles, tp);
     return cudaGetLastError();
 }
 
@@ -102,13 +136,15 @@ template <typename T, int LMAX> size_t TileLaunch<T, LMAX>::smem_per_warp(int le
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph,
                                          T* ddsph, const T* host_tables, int warps, int span_tiles, bool use_bulk,
-                                         int iters, int device, cudaStream_t stream) {
+                                         int iters, int tile_points, int device, cudaStream_t stream) {
 #define SPH_CASE(LEVEL)                                                                                            \
     if constexpr (tile_fits<T, LMAX, LEVEL>()) {                                                                   \
         return normalized ? launch_forward<T, LMAX, LEVEL, true>(xyz, n, sph, dsph, ddsph, host_tables, warps,     \
-                                                                 span_tiles, use_bulk, iters, device, stream)     \
+                                                                 span_tiles, use_bulk, iters, tile_points, device,\
+                                                                 stream)                                           \
                           : launch_forward<T, LMAX, LEVEL, false>(xyz, n, sph, dsph, ddsph, host_tables, warps,    \
-                                                                  span_tiles, use_bulk, iters, device, stream);    \
+                                                                  span_tiles, use_bulk, iters, tile_points,       \
+                                                                  device, stream);                                 \
     } else {                                                                                                       \
         return cudaErrorInvalidConfiguration;                                                                      \
     }

@@ -62,6 +62,10 @@ VARIANTS = [
     # persistent launches instead of grids of short-lived CTAs, and a different split of the work
     {"SPH_B200_TILE_ITERS": "-1", "SPH_B200_VJP_ITERS": "-1", "SPH_B200_BAND_ITERS": "-1"},
     {"SPH_B200_TILE_ITERS": "3", "SPH_B200_VJP_ITERS": "1", "SPH_B200_BAND_ITERS": "2", "SPH_B200_TILE_WARPS": "2"},
+    # tiles narrower than a warp (chosen by the library for small calls and large rows)
+    {"SPH_B200_TILE_POINTS": "8"},
+    {"SPH_B200_TILE_POINTS": "16", "SPH_B200_TILE_ITERS": "-1"},
+    {"SPH_B200_TILE_POINTS": "32"},
 ]
 
 
