@@ -33,6 +33,8 @@ __device__ __forceinline__ void bulk_store_smem_to_global(void* gdst, const void
                  : "memory");
 }
 
+__device__ __forceinline__ int lane_of_warp() { return int(threadIdx.x & 31); }
+
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 // Waits until every committed bulk store of this thread has finished reading shared memory.
@@ -65,7 +67,7 @@ template <typename T, int NY, int LEVEL> struct TileSink {
 };
 
 template <typename T, int LMAX, int LEVEL> constexpr size_t tile_smem_bytes() {
-    return size_t(TILE_POINTS) * n_columns(LMAX) * level_components(LEVEL) * sizeof(T);
+    return size_t(TILE_POINTS) * tile_point_elems(n_columns(LMAX), LEVEL, int(sizeof(T))) * sizeof(T);
 }
 
 // blockDim.x = 32 * warps; dynamic shared memory = warps * span_tiles * tile_smem_bytes * tile_points / 32.
@@ -84,7 +86,14 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
                 int tile_points) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
-    constexpr int ROW = NY * level_components(LEVEL);
+    // padded rows (see tile_row_pad) are not an image of global memory: they leave row by row
+    constexpr int PAD = tile_row_pad(NY, int(sizeof(T)));
+    constexpr int S0 = NY + PAD, S1 = 3 * NY + PAD, S2 = 9 * NY + PAD;
+    constexpr int ROW = tile_point_elems(NY, LEVEL, int(sizeof(T)));
+    // (measured: worthwhile from 256-byte rows on; shorter padded rows are copied out by the warp)
+    if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
+    // bulk-store groups are per thread: with padded rows every lane issues and waits for its own
+    const bool bulk_lane = use_bulk && (PAD != 0 || lane_of_warp() == 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     const int span_points = span_tiles * tile_points;
@@ -92,8 +101,8 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
 
     // image of one span: [span_points][NY], then [span_points][3][NY], then [span_points][9][NY]
     T* img_sph = reinterpret_cast<T*>(smem_raw) + size_t(warp) * span_points * ROW;
-    T* img_d = img_sph + span_points * NY;
-    T* img_dd = img_sph + span_points * NY * 4;
+    T* img_d = img_sph + span_points * S0;
+    T* img_dd = img_d + span_points * S1;
 
     const long long nspans = (n + span_points - 1) / span_points;
     const long long stride = (long long)gridDim.x * nwarps;
@@ -108,7 +117,7 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
         }
 
         // the previous span's bulk stores must be done reading this slice
-        if (use_bulk && lane == 0) bulk_wait_read_all();
+        if (bulk_lane) bulk_wait_read_all();
         __syncwarp();
 
         for (int t = 0; t < span_tiles; ++t) {
@@ -121,7 +130,7 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
                 nz = xyz[3 * inext + 2];
             }
             const int row = t * tile_points + pt;
-            TileSink<T, NY, LEVEL> sink{img_sph + row * NY, img_d + row * 3 * NY, img_dd + row * 9 * NY};
+            TileSink<T, NY, LEVEL> sink{img_sph + row * S0, img_d + row * S1, img_dd + row * S2};
             eval_point<T, LMAX, LEVEL, NORM>(x, y, z, tab, sink);
             x = nx;
             y = ny_;
@@ -132,26 +141,42 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
         if (use_bulk && npts == span_points) {
             fence_proxy_async_smem();  // make this lane's image writes visible to the TMA engine
             __syncwarp();
-            if (lane == 0) {
-                bulk_store_smem_to_global(sph + first * NY, img_sph, unsigned(span_points * NY * sizeof(T)));
-                if constexpr (LEVEL >= 1)
-                    bulk_store_smem_to_global(dsph + first * 3 * NY, img_d, unsigned(span_points * 3 * NY * sizeof(T)));
-                if constexpr (LEVEL >= 2)
-                    bulk_store_smem_to_global(ddsph + first * 9 * NY, img_dd, unsigned(span_points * 9 * NY * sizeof(T)));
+            if constexpr (PAD == 0) {
+                if (lane == 0) {
+                    bulk_store_smem_to_global(sph + first * NY, img_sph, unsigned(span_points * NY * sizeof(T)));
+                    if constexpr (LEVEL >= 1)
+                        bulk_store_smem_to_global(dsph + first * 3 * NY, img_d, unsigned(span_points * 3 * NY * sizeof(T)));
+                    if constexpr (LEVEL >= 2)
+                        bulk_store_smem_to_global(ddsph + first * 9 * NY, img_dd,
+                                                  unsigned(span_points * 9 * NY * sizeof(T)));
+                    bulk_commit();
+                }
+            } else {
+                // one store per point and array, issued by the lanes side by side
+                for (int r = lane; r < span_points; r += 32) {
+                    bulk_store_smem_to_global(sph + (first + r) * NY, img_sph + r * S0, unsigned(NY * sizeof(T)));
+                    if constexpr (LEVEL >= 1)
+                        bulk_store_smem_to_global(dsph + (first + r) * 3 * NY, img_d + r * S1, unsigned(3 * NY * sizeof(T)));
+                    if constexpr (LEVEL >= 2)
+                        bulk_store_smem_to_global(ddsph + (first + r) * 9 * NY, img_dd + r * S2,
+                                                  unsigned(9 * NY * sizeof(T)));
+                }
                 bulk_commit();
             }
         } else {
             __syncwarp();
-            for (int e = lane; e < npts * NY; e += 32) sph[first * NY + e] = img_sph[e];
+            // element e of a span's output lies in row e / row_length of the image
+            for (int e = lane; e < npts * NY; e += 32) sph[first * NY + e] = img_sph[e + PAD * (e / NY)];
             if constexpr (LEVEL >= 1)
-                for (int e = lane; e < npts * 3 * NY; e += 32) dsph[first * 3 * NY + e] = img_d[e];
+                for (int e = lane; e < npts * 3 * NY; e += 32) dsph[first * 3 * NY + e] = img_d[e + PAD * (e / (3 * NY))];
             if constexpr (LEVEL >= 2)
-                for (int e = lane; e < npts * 9 * NY; e += 32) ddsph[first * 9 * NY + e] = img_dd[e];
+                for (int e = lane; e < npts * 9 * NY; e += 32)
+                    ddsph[first * 9 * NY + e] = img_dd[e + PAD * (e / (9 * NY))];
             __syncwarp();
         }
     }
     // shared memory must outlive the engine's reads
-    if (use_bulk && lane == 0) bulk_wait_read_all();
+    if (bulk_lane) bulk_wait_read_all();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -218,7 +243,7 @@ static __device__ int g_tile_wait_gave_up = 0;
 
 // Per warp: two images of the tile's sph_grad rows (double buffer) followed by two mbarriers.
 template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_smem_bytes() {
-    return 2 * size_t(TILE_POINTS) * n_columns(LMAX) * sizeof(T) + 16;
+    return 2 * size_t(TILE_POINTS) * (n_columns(LMAX) + tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T) + 16;
 }
 
 // use_bulk != 0: the rows of sph_grad are fetched by the TMA engine (1-D bulk load, completion on
@@ -232,11 +257,16 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
     constexpr unsigned TILE_BYTES = unsigned(TILE_POINTS * NY * sizeof(T));
+    // padded rows (see tile_row_pad) arrive as one bulk load per row, issued by the row's lane
+    // (measured: worthwhile from 256-byte rows on; shorter padded rows are staged by the warp)
+    constexpr int PAD = tile_row_pad(NY, int(sizeof(T)));
+    constexpr int S = NY + PAD;
+    if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     unsigned char* mine = smem_raw + size_t(warp) * vjp_tile_smem_bytes<T, LMAX>();
-    T* img[2] = {reinterpret_cast<T*>(mine), reinterpret_cast<T*>(mine) + TILE_POINTS * NY};
-    unsigned long long* bar = reinterpret_cast<unsigned long long*>(mine + 2 * size_t(TILE_BYTES));
+    T* img[2] = {reinterpret_cast<T*>(mine), reinterpret_cast<T*>(mine) + TILE_POINTS * S};
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(mine + 2 * size_t(TILE_POINTS) * S * sizeof(T));
 
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long stride = (long long)gridDim.x * nwarps;
@@ -245,9 +275,18 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
     // a tile can come through the engine when it is full (its byte count is then a multiple of 16)
     auto engine_tile = [&](long long tile) { return use_bulk && (tile + 1) * TILE_POINTS <= n; };
     auto issue = [&](long long tile, int buf) {
-        if (lane == 0 && tile < ntiles && engine_tile(tile)) {
-            mbar_expect_tx(&bar[buf], TILE_BYTES);
-            bulk_load_global_to_smem(img[buf], sph_grad + tile * TILE_POINTS * NY, TILE_BYTES, &bar[buf]);
+        if (tile < ntiles && engine_tile(tile)) {  // the same for every lane
+            if constexpr (PAD == 0) {
+                if (lane == 0) {
+                    mbar_expect_tx(&bar[buf], TILE_BYTES);
+                    bulk_load_global_to_smem(img[buf], sph_grad + tile * TILE_POINTS * NY, TILE_BYTES, &bar[buf]);
+                }
+            } else {
+                if (lane == 0) mbar_expect_tx(&bar[buf], TILE_BYTES);
+                __syncwarp();
+                bulk_load_global_to_smem(img[buf] + lane * S, sph_grad + (tile * TILE_POINTS + lane) * NY,
+                                         unsigned(NY * sizeof(T)), &bar[buf]);
+            }
         }
     };
 
@@ -287,13 +326,13 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             phase[cur] ^= 1u;
         } else {
             const T* gsrc = sph_grad + first * NY;
-            for (int e = lane; e < TILE_POINTS * NY; e += 32) img[cur][e] = (e < npts * NY) ? gsrc[e] : T(0);
+            for (int e = lane; e < TILE_POINTS * NY; e += 32) img[cur][e + PAD * (e / NY)] = (e < npts * NY) ? gsrc[e] : T(0);
             __syncwarp();
         }
 
         // The chain rule through r -> r/|r| is linear in the gradient, so it is applied once to the
         // accumulated sum of raw gradients instead of to each of the (l_max+1)^2 columns.
-        VjpSink<T, NY> sink{img[cur] + lane * NY, T(0), T(0), T(0)};
+        VjpSink<T, NY> sink{img[cur] + lane * S, T(0), T(0), T(0)};
         eval_point<T, LMAX, 1, NORM, VjpSink<T, NY>, true>(x, y, z, tab, sink);
         if constexpr (NORM) {
             const T ir = T(1) / sqrt(x * x + y * y + z * z);
@@ -343,7 +382,7 @@ template <typename T, int NY, bool HAS_VALUE_GRAD> struct Vjp2Sink {
 
 // Per warp: the tile's 32 rows of sph_grad ([32][NY]) followed by its rows of dsph_grad ([32][3][NY]).
 template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp2_tile_smem_bytes() {
-    return size_t(TILE_POINTS) * 4 * n_columns(LMAX) * sizeof(T);
+    return size_t(TILE_POINTS) * (4 * n_columns(LMAX) + 2 * tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T);
 }
 
 // The upstream gradients of a tile are contiguous spans of their arrays; the warp stages them with
@@ -356,8 +395,10 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
     constexpr int NY = n_columns(LMAX);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    T* img_s = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * 4 * NY;
-    T* img_d = img_s + TILE_POINTS * NY;
+    constexpr int PAD = tile_row_pad(NY, int(sizeof(T)));
+    constexpr int S0 = NY + PAD, S1 = 3 * NY + PAD;
+    T* img_s = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * (S0 + S1);
+    T* img_d = img_s + TILE_POINTS * S0;
     const bool has_value_grad = sph_grad != nullptr;
 
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
@@ -375,23 +416,24 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
         __syncwarp();  // previous tile's reads of the images are complete
         if (has_value_grad) {
             const T* src = sph_grad + first * NY;
-            for (int e = lane; e < TILE_POINTS * NY; e += 32) img_s[e] = (e < npts * NY) ? src[e] : T(0);
+            for (int e = lane; e < TILE_POINTS * NY; e += 32) img_s[e + PAD * (e / NY)] = (e < npts * NY) ? src[e] : T(0);
         }
         {
             const T* src = dsph_grad + first * 3 * NY;
-            for (int e = lane; e < TILE_POINTS * 3 * NY; e += 32) img_d[e] = (e < npts * 3 * NY) ? src[e] : T(0);
+            for (int e = lane; e < TILE_POINTS * 3 * NY; e += 32)
+                img_d[e + PAD * (e / (3 * NY))] = (e < npts * 3 * NY) ? src[e] : T(0);
         }
         __syncwarp();
 
         T ax, ay, az;
         if (has_value_grad) {
-            Vjp2Sink<T, NY, true> sink{img_s + lane * NY, img_d + lane * 3 * NY, T(0), T(0), T(0)};
+            Vjp2Sink<T, NY, true> sink{img_s + lane * S0, img_d + lane * S1, T(0), T(0), T(0)};
             eval_point<T, LMAX, 2, NORM>(x, y, z, tab, sink);
             ax = sink.ax;
             ay = sink.ay;
             az = sink.az;
         } else {
-            Vjp2Sink<T, NY, false> sink{img_s, img_d + lane * 3 * NY, T(0), T(0), T(0)};
+            Vjp2Sink<T, NY, false> sink{img_s, img_d + lane * S1, T(0), T(0), T(0)};
             eval_point<T, LMAX, 2, NORM>(x, y, z, tab, sink);
             ax = sink.ax;
             ay = sink.ay;

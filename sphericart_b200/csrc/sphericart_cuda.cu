@@ -431,7 +431,8 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
 
     if (l_max <= TILE_LMAX && !force_band) {
         if (kind == 4) {
-            const size_t vjp2_per_warp = size_t(32) * 4 * n_columns(l_max) * sizeof(T);
+            const size_t vjp2_per_warp =
+                size_t(32) * (4 * n_columns(l_max) + 2 * tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T);
             if (vjp2_per_warp <= TILE_SMEM_LIMIT) {
                 check(TileDispatch<T>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables,
                                             tile_warps(vjp2_per_warp, props.smem_optin),
@@ -440,7 +441,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
                 return;
             }
         }
-        const size_t per_warp = kind == 3 ? 2 * size_t(32) * n_columns(l_max) * sizeof(T) + 16
+        const size_t per_warp = kind == 3 ? 2 * size_t(32) * (n_columns(l_max) + tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T) + 16
                                           : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
         if (kind == 3) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;

@@ -130,7 +130,7 @@ template <typename T, int LMAX, int LEVEL> constexpr bool tile_fits() {
 }  // namespace
 
 template <typename T, int LMAX> size_t TileLaunch<T, LMAX>::smem_per_warp(int level) {
-    return size_t(TILE_POINTS) * n_columns(LMAX) * level_components(level) * sizeof(T);
+    return size_t(TILE_POINTS) * tile_point_elems(n_columns(LMAX), level, int(sizeof(T))) * sizeof(T);
 }
 
 template <typename T, int LMAX>
