@@ -9,11 +9,26 @@
 
 namespace sph_b200 {
 
-constexpr int TILE_LMAX = 8;        // compile-time tile kernels cover l_max 0..8
+constexpr int TILE_LMAX = 12;       // compile-time tile kernels cover l_max 0..12
 constexpr int MAX_DEVICES = 64;
 
-// Largest 32-point tile image a tile kernel is used for; larger cases go to the band kernel.
-constexpr size_t TILE_SMEM_LIMIT = 100 * 1024;
+// Which cases the tile kernels (compile-time l_max, one lane per point) serve; the rest go to the
+// band kernel (run-time l_max, lanes share a point). kind 0..2: forward level, 3: VJP of the values,
+// 4: VJP of (values, gradients). The crossovers were measured on a B200 for both element types
+// (fraction of the copy peak, tile / band):
+//   values        l = 9..12: 1.01 / 0.22-0.44          -> tile wherever compiled
+//   gradients     l = 10: 0.70-0.76 / 0.54-0.56, l = 11: 0.58-0.63 / 0.61-0.67   -> tile up to 10
+//   Hessians      float32 l = 5: 0.59 / 0.47, l = 6: 0.48 / 0.71 (the Hessian columns need many registers
+//                 and the rows few images per SM)      -> tile up to 5 and a 100 KB image
+//   VJP           l = 9..12: 0.50-0.84 / 0.15-0.25     -> tile wherever compiled
+//   2nd-order VJP l = 5: 1.2-2.1 / 0.7-1.8 Gpoints/s, l = 6: 0.6-1.1 / 0.6-1.7   -> tile up to 5
+constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
+    if (l_max > TILE_LMAX) return false;
+    if (kind == 1) return l_max <= 10;
+    if (kind == 2) return l_max <= 5 && size_t(32) * (l_max + 1) * (l_max + 1) * 13 * elem_bytes <= 100 * 1024;
+    if (kind == 4) return l_max <= 5;
+    return true;
+}
 
 // Number of CTAs that keep every SM of `device` full for a persistent launch of `kernel` with
 // the given block size and dynamic shared memory (also raises the kernel's dynamic shared

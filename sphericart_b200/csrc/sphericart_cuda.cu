@@ -45,6 +45,7 @@ struct Knobs {
     int vjp_iters;      // the same for the backward tile kernels
     int band_iters;     // the same for the band kernels
     int tile_points;    // force the points per tile of the forward tile kernels (8, 16 or 32)
+    int tile_lmax;      // largest l_max served by the tile kernels (default: all they are compiled for)
 };
 
 int env_int(const char* name, int fallback) {
@@ -60,7 +61,7 @@ const Knobs& knobs() {
                             env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0),
                             env_int("SPH_B200_TILE_SPAN", 0),      env_int("SPH_B200_TILE_ITERS", 0),
                             env_int("SPH_B200_VJP_ITERS", 0),      env_int("SPH_B200_BAND_ITERS", 0),
-                            env_int("SPH_B200_TILE_POINTS", 0)};
+                            env_int("SPH_B200_TILE_POINTS", 0),    env_int("SPH_B200_TILE_LMAX", TILE_LMAX)};
     return k;
 }
 
@@ -429,17 +430,15 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
     const bool vjp = kind >= 3;
     const bool force_band = knobs().force_band != 0;
 
-    if (l_max <= TILE_LMAX && !force_band) {
+    if (tile_serves(kind, l_max, int(sizeof(T))) && l_max <= knobs().tile_lmax && !force_band) {
         if (kind == 4) {
             const size_t vjp2_per_warp =
                 size_t(32) * (4 * n_columns(l_max) + 2 * tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T);
-            if (vjp2_per_warp <= TILE_SMEM_LIMIT) {
-                check(TileDispatch<T>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables,
-                                            tile_warps(vjp2_per_warp, props.smem_optin),
-                                            resolve_iters(knobs().vjp_iters, 4), scope.device, stream),
-                      "tile second-order VJP kernel launch");
-                return;
-            }
+            check(TileDispatch<T>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables,
+                                        tile_warps(vjp2_per_warp, props.smem_optin), resolve_iters(knobs().vjp_iters, 4),
+                                        scope.device, stream),
+                  "tile second-order VJP kernel launch");
+            return;
         }
         const size_t per_warp = kind == 3 ? 2 * size_t(32) * (n_columns(l_max) + tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T) + 16
                                           : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
@@ -454,7 +453,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
                   "tile VJP kernel launch");
             return;
         }
-        if (kind < 3 && per_warp <= TILE_SMEM_LIMIT) {
+        if (kind < 3) {
             bool use_bulk = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
             if (knobs().no_bulk != 0) use_bulk = false;
             // One warp and one image per short-lived CTA: a CTA's shared memory is released as soon

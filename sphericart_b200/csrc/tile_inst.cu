@@ -123,9 +123,7 @@ cudaError_t launch_vjp2(const T* xyz, const T* sph_grad, const T* dsph_grad, lon
     return cudaGetLastError();
 }
 
-template <typename T, int LMAX, int LEVEL> constexpr bool tile_fits() {
-    return tile_smem_bytes<T, LMAX, LEVEL>() <= TILE_SMEM_LIMIT;
-}
+template <typename T, int LMAX, int LEVEL> constexpr bool tile_fits() { return tile_serves(LEVEL, LMAX, int(sizeof(T))); }
 
 }  // namespace
 
@@ -171,10 +169,14 @@ template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
                                       T* xyz_grad, const T* host_tables, int warps, int iters, int device,
                                       cudaStream_t stream) {
-    return normalized ? launch_vjp2<T, LMAX, true>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters, device,
-                                                   stream)
-                      : launch_vjp2<T, LMAX, false>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters,
-                                                    device, stream);
+    if constexpr (tile_serves(4, LMAX, int(sizeof(T)))) {
+        return normalized ? launch_vjp2<T, LMAX, true>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters,
+                                                       device, stream)
+                          : launch_vjp2<T, LMAX, false>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters,
+                                                        device, stream);
+    } else {
+        return cudaErrorInvalidConfiguration;
+    }
 }
 
 template <typename T, int LMAX> int TileLaunch<T, LMAX>::device_error_flag() {

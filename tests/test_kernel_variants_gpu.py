@@ -66,6 +66,8 @@ VARIANTS = [
     {"SPH_B200_TILE_POINTS": "8"},
     {"SPH_B200_TILE_POINTS": "16", "SPH_B200_TILE_ITERS": "-1"},
     {"SPH_B200_TILE_POINTS": "32"},
+    # the band kernel for every degree the tile kernels would otherwise take above l_max = 2
+    {"SPH_B200_TILE_LMAX": "2"},
 ]
 
 
