@@ -36,7 +36,7 @@ def _units():
     """(object name, source, extra defines)"""
     units = [("sphericart_cuda.o", "sphericart_cuda.cu", [])]
     for tname, t in (("f32", "float"), ("f64", "double")):
-        for l in range(0, 13):
+        for l in range(0, 21):
             units.append((f"tile_{tname}_l{l}.o", "tile_inst.cu", [f"-DSPH_T={t}", f"-DSPH_LMAX={l}"]))
         for g in (1, 2, 4, 8, 16, 32):
             units.append((f"band_{tname}_g{g}.o", "band_inst.cu", [f"-DSPH_T={t}", f"-DSPH_G={g}"]))

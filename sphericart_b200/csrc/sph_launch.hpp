@@ -9,7 +9,7 @@
 
 namespace sph_b200 {
 
-constexpr int TILE_LMAX = 12;       // compile-time tile kernels cover l_max 0..12
+constexpr int TILE_LMAX = 20;       // compile-time tile kernels cover l_max 0..20
 constexpr int MAX_DEVICES = 64;
 
 // Which cases the tile kernels (compile-time l_max, one lane per point) serve; the rest go to the
@@ -27,6 +27,8 @@ constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
     if (kind == 1) return l_max <= 10;
     if (kind == 2) return l_max <= 5 && size_t(32) * (l_max + 1) * (l_max + 1) * 13 * elem_bytes <= 100 * 1024;
     if (kind == 4) return l_max <= 5;
+    // the VJP kernel double-buffers a tile's upstream rows: at least two warps' worth per SM
+    if (kind == 3) return size_t(2) * 32 * (l_max + 1) * (l_max + 1) * elem_bytes <= 113 * 1024;
     return true;
 }
 

@@ -159,10 +159,14 @@ template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
                                      const T* host_tables, int warps, bool use_bulk, int iters, int device,
                                      cudaStream_t stream) {
-    return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters, device,
-                                                  stream)
-                      : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters, device,
-                                                   stream);
+    if constexpr (tile_serves(3, LMAX, int(sizeof(T)))) {
+        return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters,
+                                                      device, stream)
+                          : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters,
+                                                       device, stream);
+    } else {
+        return cudaErrorInvalidConfiguration;
+    }
 }
 
 template <typename T, int LMAX>

@@ -70,10 +70,11 @@ def _assert_close(oracle_mod, got, want, l_max, dtype, what):
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("level", [0, 1, 2])
 def test_all_degrees_small(sb, oracle_mod, dtype, level):
-    """l_max 0..12, 16, 20 for both classes; sizes around the 32-point tile; guard bands intact."""
+    """l_max 0..14, 16, 17, 20, 21, 24 for both classes (the tile kernels end at 20); sizes around the
+    32-point tile; guard bands intact."""
     rng = np.random.default_rng(42 + level)
     for cls, normalized in _classes(sb):
-        for l_max in list(range(0, 13)) + [16, 20]:
+        for l_max in list(range(0, 15)) + [16, 17, 20, 21, 24]:
             calc = cls(l_max)
             for n in (1, 2, 31, 32, 33, 95, 257):
                 xyz = (rng.standard_normal((n, 3)) * 1.7).astype(dtype)
@@ -161,9 +162,13 @@ def test_benchmark_configurations_sampled(sb, oracle_mod, config, n):
 
 
 def _vjp_reference(oracle_mod, xyz, g, l_max, normalized):
-    """float64 contraction of the checker's float64 gradients: the exact answer to compare with."""
-    x64 = xyz.astype(np.float64)
-    _, dsph, _ = _reference(oracle_mod, x64, l_max, normalized, 1)
+    """What the reference's backward computes (gradients, then product and sum:
+    sphericart-torch/python/sphericart/torch/register.py:90-108), with the sum taken in float64:
+    the checker's gradients in the precision of the input - beyond l_max = 18 the float32 prefactors
+    of the reference's own recipe lose bits (1 / (2 l)! leaves the normal range), and parity is with
+    the reference in the same precision - contracted in float64."""
+    _, dsph, _ = _reference(oracle_mod, xyz, l_max, normalized, 1)
+    dsph = dsph.astype(np.float64)
     want = np.einsum("nak,nk->na", dsph, g.astype(np.float64))
     scale = np.einsum("nak,nk->na", np.abs(dsph), np.abs(g.astype(np.float64))).max(axis=1, keepdims=True)
     return want, np.maximum(scale, 1e-300)
@@ -176,7 +181,7 @@ def test_fused_vjp(sb, oracle_mod, dtype):
     dev = torch.device("cuda", 0)
     tol = 1e-12 if dtype == np.float64 else 1e-5
     for cls, normalized in _classes(sb):
-        for l_max in list(range(0, 14)) + [16]:  # tile kernels up to 12, band kernel beyond
+        for l_max in list(range(0, 15)) + [16, 19, 20, 21, 24]:  # tile kernels up to 13 / 19 / 20, band kernel beyond
             for n in (1, 33, 1000):
                 xyz = (rng.standard_normal((n, 3)) * 1.4).astype(dtype)
                 g = rng.standard_normal((n, (l_max + 1) ** 2)).astype(dtype)
