@@ -370,6 +370,11 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         const T* grow = region0 + pt * ny;  // VJP: this point's upstream-gradient row
 
         [[maybe_unused]] T ax = T(0), ay = T(0), az = T(0);  // VJP accumulators
+        // second-order VJP of the normalised harmonics: sums of raw derivatives, projected once per
+        // point (see Vjp2RawSink in sph_tile.cuh for the algebra): B and C next to A = (ax, ay, az)
+        constexpr bool RAW2 = VJP && LEVEL >= 2 && NORM;
+        [[maybe_unused]] T rb[3] = {T(0), T(0), T(0)};
+        [[maybe_unused]] T rc[9] = {T(0), T(0), T(0), T(0), T(0), T(0), T(0), T(0), T(0)};
         if constexpr (VJP) {
             // the P rows of each upstream gradient are one contiguous span: coalesced loads
             if (a.sph_grad != nullptr) {
@@ -412,9 +417,20 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                     const T wy = lds_at<T, 0>(ad);
                     ad += ny_b;
                     const T wz = lds_at<T, 0>(ad);
-                    ax += wx * v.hxx + wy * v.hxy + wz * v.hxz;
-                    ay += wx * v.hxy + wy * v.hyy + wz * v.hyz;
-                    az += wx * v.hxz + wy * v.hyz + wz * v.hzz;
+                    if constexpr (RAW2) {
+                        const T t = T(us.x) * wx + T(us.y) * wy + T(us.z) * wz;
+                        const T px = wx - T(us.x) * t, py = wy - T(us.y) * t, pz = wz - T(us.z) * t;
+                        rb[0] += v.hxx * px + v.hxy * py + v.hxz * pz;
+                        rb[1] += v.hxy * px + v.hyy * py + v.hyz * pz;
+                        rb[2] += v.hxz * px + v.hyz * py + v.hzz * pz;
+                        rc[0] += wx * v.gx;  rc[1] += wx * v.gy;  rc[2] += wx * v.gz;
+                        rc[3] += wy * v.gx;  rc[4] += wy * v.gy;  rc[5] += wy * v.gz;
+                        rc[6] += wz * v.gx;  rc[7] += wz * v.gy;  rc[8] += wz * v.gz;
+                    } else {
+                        ax += wx * v.hxx + wy * v.hxy + wz * v.hxz;
+                        ay += wx * v.hxy + wy * v.hyy + wz * v.hyz;
+                        az += wx * v.hxz + wy * v.hyz + wz * v.hzz;
+                    }
                 }
             } else if constexpr (DIRECT) {
                 // streaming stores: the data is written once and never read back by this kernel
@@ -474,7 +490,7 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
         constexpr bool PACKED = sizeof(T) == 4 && LEVEL >= 1;
         [[maybe_unused]] UnitSphere2 us2{};
         // (the first-order VJP applies the linear chain rule once to its sum; everything else per column)
-        constexpr bool CHAIN_PER_COLUMN = NORM && LEVEL >= 1 && !(VJP && LEVEL == 1);
+        constexpr bool CHAIN_PER_COLUMN = NORM && LEVEL >= 1 && !VJP;
         if constexpr (PACKED && CHAIN_PER_COLUMN) {
             UnitSphere<float> usf{float(us.x), float(us.y), float(us.z), float(us.ir), float(us.irsq)};
             us2 = make_unit_sphere2<LEVEL>(usf);
@@ -603,6 +619,12 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                 ax += __shfl_xor_sync(0xffffffffu, ax, off);
                 ay += __shfl_xor_sync(0xffffffffu, ay, off);
                 az += __shfl_xor_sync(0xffffffffu, az, off);
+                if constexpr (RAW2) {
+#pragma unroll
+                    for (int q = 0; q < 3; ++q) rb[q] += __shfl_xor_sync(0xffffffffu, rb[q], off);
+#pragma unroll
+                    for (int q = 0; q < 9; ++q) rc[q] += __shfl_xor_sync(0xffffffffu, rc[q], off);
+                }
             }
             if constexpr (NORM && LEVEL == 1) {
                 // linear chain rule, applied once to the sum of raw gradients
@@ -610,6 +632,23 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
                 ax = (ax - us.x * t) * us.ir;
                 ay = (ay - us.y * t) * us.ir;
                 az = (az - us.z * t) * us.ir;
+            }
+            if constexpr (RAW2) {
+                const T ux = T(us.x), uy = T(us.y), uz = T(us.z), ir = T(us.ir);
+                const T sx = ax + rb[0] * ir, sy = ay + rb[1] * ir, sz = az + rb[2] * ir;
+                const T d = ux * sx + uy * sy + uz * sz;
+                const T tr = rc[0] + rc[4] + rc[8];
+                const T ucx = ux * rc[0] + uy * rc[3] + uz * rc[6];
+                const T ucy = ux * rc[1] + uy * rc[4] + uz * rc[7];
+                const T ucz = ux * rc[2] + uy * rc[5] + uz * rc[8];
+                const T cux = rc[0] * ux + rc[1] * uy + rc[2] * uz;
+                const T cuy = rc[3] * ux + rc[4] * uy + rc[5] * uz;
+                const T cuz = rc[6] * ux + rc[7] * uy + rc[8] * uz;
+                const T k = T(3) * (ucx * ux + ucy * uy + ucz * uz) - tr;
+                const T irsq = ir * ir;
+                ax = (sx - ux * d) * ir + (ux * k - ucx - cux) * irsq;
+                ay = (sy - uy * d) * ir + (uy * k - ucy - cuy) * irsq;
+                az = (sz - uz * d) * ir + (uz * k - ucz - cuz) * irsq;
             }
             if (g == 0 && valid) {
                 a.xyz_grad[3 * i + 0] = ax;

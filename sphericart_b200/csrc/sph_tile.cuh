@@ -380,6 +380,55 @@ template <typename T, int NY, bool HAS_VALUE_GRAD> struct Vjp2Sink {
     }
 };
 
+// The same contraction for the normalised harmonics Y(x) = S(u), u = x / r, without the chain rule
+// per column. With G_c = dS/du_c, H_cd = d2S/du_c du_d (what eval_point hands over in RAW mode),
+// J = du/dx = (1 - u u^T) / r and K^c_ab = d2u_c/dx_a dx_b, the result is
+//   out_b = sum_c J_cb (A_c + B_c) + sum_{a,c} K^c_ab C_ac,
+//   A_c = sum_k g_k G_k,c,   B = (1/r) sum_k H_k (w_k - u (u . w_k)),   C_ac = sum_k w_a,k G_k,c,
+// (w_k = the three dsph_grad entries of column k), so each column costs 27 multiply-adds on raw
+// derivatives and the projection is applied once per point (finish()). The reference applies it to
+// every Hessian column (sphericart/include/templates.hpp:214-254) before contracting.
+template <typename T, int NY, bool HAS_VALUE_GRAD> struct Vjp2RawSink {
+    const T* gs;
+    const T* gd;
+    T ux, uy, uz;
+    T a[3], b[3], c[9];
+    template <int K> __device__ __forceinline__ void put(const Column<T>& v) {
+        const T wx = gd[K], wy = gd[NY + K], wz = gd[2 * NY + K];
+        const T t = ux * wx + uy * wy + uz * wz;
+        const T px = wx - ux * t, py = wy - uy * t, pz = wz - uz * t;
+        b[0] += v.hxx * px + v.hxy * py + v.hxz * pz;
+        b[1] += v.hxy * px + v.hyy * py + v.hyz * pz;
+        b[2] += v.hxz * px + v.hyz * py + v.hzz * pz;
+        c[0] += wx * v.gx;  c[1] += wx * v.gy;  c[2] += wx * v.gz;
+        c[3] += wy * v.gx;  c[4] += wy * v.gy;  c[5] += wy * v.gz;
+        c[6] += wz * v.gx;  c[7] += wz * v.gy;  c[8] += wz * v.gz;
+        if constexpr (HAS_VALUE_GRAD) {
+            const T gk = gs[K];
+            a[0] += gk * v.gx;
+            a[1] += gk * v.gy;
+            a[2] += gk * v.gz;
+        }
+    }
+    __device__ __forceinline__ void finish(T ir, T& ox, T& oy, T& oz) const {
+        const T sx = a[0] + b[0] * ir, sy = a[1] + b[1] * ir, sz = a[2] + b[2] * ir;
+        const T d = ux * sx + uy * sy + uz * sz;
+        const T tr = c[0] + c[4] + c[8];
+        const T ucx = ux * c[0] + uy * c[3] + uz * c[6];  // (u^T C)_b
+        const T ucy = ux * c[1] + uy * c[4] + uz * c[7];
+        const T ucz = ux * c[2] + uy * c[5] + uz * c[8];
+        const T cux = c[0] * ux + c[1] * uy + c[2] * uz;  // (C u)_b
+        const T cuy = c[3] * ux + c[4] * uy + c[5] * uz;
+        const T cuz = c[6] * ux + c[7] * uy + c[8] * uz;
+        const T ucu = ucx * ux + ucy * uy + ucz * uz;
+        const T k = T(3) * ucu - tr;
+        const T irsq = ir * ir;
+        ox = (sx - ux * d) * ir + (ux * k - ucx - cux) * irsq;
+        oy = (sy - uy * d) * ir + (uy * k - ucy - cuy) * irsq;
+        oz = (sz - uz * d) * ir + (uz * k - ucz - cuz) * irsq;
+    }
+};
+
 // Per warp: the tile's 32 rows of sph_grad ([32][NY]) followed by its rows of dsph_grad ([32][3][NY]).
 template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp2_tile_smem_bytes() {
     return size_t(TILE_POINTS) * (4 * n_columns(LMAX) + 2 * tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T);
@@ -426,7 +475,20 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
         __syncwarp();
 
         T ax, ay, az;
-        if (has_value_grad) {
+        if constexpr (NORM) {
+            // same normalisation as eval_point (and the reference: sphericart/include/templates.hpp:392-396)
+            const T ir = T(1) / sqrt(x * x + y * y + z * z);
+            const T ux = x * ir, uy = y * ir, uz = z * ir;
+            if (has_value_grad) {
+                Vjp2RawSink<T, NY, true> sink{img_s + lane * S0, img_d + lane * S1, ux, uy, uz, {}, {}, {}};
+                eval_point<T, LMAX, 2, NORM, Vjp2RawSink<T, NY, true>, true>(x, y, z, tab, sink);
+                sink.finish(ir, ax, ay, az);
+            } else {
+                Vjp2RawSink<T, NY, false> sink{img_s, img_d + lane * S1, ux, uy, uz, {}, {}, {}};
+                eval_point<T, LMAX, 2, NORM, Vjp2RawSink<T, NY, false>, true>(x, y, z, tab, sink);
+                sink.finish(ir, ax, ay, az);
+            }
+        } else if (has_value_grad) {
             Vjp2Sink<T, NY, true> sink{img_s + lane * S0, img_d + lane * S1, T(0), T(0), T(0)};
             eval_point<T, LMAX, 2, NORM>(x, y, z, tab, sink);
             ax = sink.ax;
