@@ -264,7 +264,8 @@ SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_with_gradi
 /* No counterpart in the reference. Values and gradients (float64, level 1) for hosts that do not
  * let a plugin allocate device memory of its own - a runtime that reserved the whole device arena
  * at start-up, or a latency-bound service loop where cudaMalloc's device-wide synchronisation is
- * not acceptable. The calculators above cudaMalloc their tables on first use when l_max > 8; this
+ * not acceptable. The calculators above cudaMalloc their tables on first use of their run-time-
+ * degree kernel (values and gradients: l_max > 10); this
  * entry point instead keeps them in a fixed 16 KiB array that is part of the library image (every
  * GPU that loads the library holds it until the process exits) and calls no allocating routine.
  * Limit: l_max <= 32; larger values are rejected with an error. normalized != 0 selects spherical

@@ -1,6 +1,7 @@
 // "Band" kernels: any maximum degree (run-time l_max), any derivative level, and the fused
-// vector-Jacobian product. Used wherever the compile-time tile kernels do not apply: l_max > 8,
-// and the cases whose 32-point tile image would not fit shared memory.
+// vector-Jacobian product. Used wherever the compile-time tile kernels do not apply (see
+// tile_serves() in sph_launch.hpp: high degrees, and the cases with rows so long that too few tile
+// images fit an SM).
 //
 // Two phases per point, G lanes (1, 2, 4, ... 32) sharing a point, P = 32 / G points per warp:
 //

@@ -1,5 +1,6 @@
-// "Tile" kernels: one thread per point, one warp per tile of 32 consecutive points, maximum
-// degree known at compile time (l_max <= 8).
+// "Tile" kernels: one thread per point, one warp per tile of 32 (or 16, or 8) consecutive points,
+// maximum degree known at compile time (l_max <= 20; which cases they serve: tile_serves() in
+// sph_launch.hpp).
 //
 // Data movement. The outputs are row-major [N][ny], [N][3][ny], [N][3][3][ny], so the rows of
 // 32 consecutive points form ONE contiguous span in each output array. A warp builds the exact
@@ -10,11 +11,14 @@
 // straight on to its next tile; it only waits, before overwriting the slice, for the engine to
 // have finished READING shared memory. Spans start at multiples of 32*ny*sizeof(T) bytes from
 // the array base, i.e. 16-byte aligned whenever the base is; a base that is not 16-byte aligned
-// and the ragged last tile fall back to coalesced plain stores from the same image.
+// and the ragged last tile fall back to coalesced plain stores from the same image. Row lengths
+// that are multiples of 16 elements get padded rows (tile_row_pad() in sph_core.cuh) and leave row
+// by row.
 //
 // There is no communication between warps, CTAs or GPUs and no spin-wait anywhere.
 //
-// Replaces spherical_harmonics_kernel (sphericart/src/sphericart_impl.cu:207-615) for l_max <= 8.
+// Replaces spherical_harmonics_kernel (sphericart/src/sphericart_impl.cu:207-615) for the cases
+// tile_serves() lists.
 #pragma once
 
 #include "sph_core.cuh"

@@ -36,7 +36,7 @@ struct Knobs {
     int band_lanes;     // force lanes per point (1..32, power of two)
     int band_warps;     // force warps per CTA of the band kernel (1..4)
     int tile_warps;     // force warps per CTA of the tile kernels (1..8)
-    int force_band;     // route l_max <= 8 through the band kernel too
+    int force_band;     // route every call through the band kernel
     int no_bulk;        // copy tiles out with plain stores instead of TMA bulk stores
     int band_direct;    // 1: force direct global stores in the band kernel, -1: forbid them
     int band_max_ctas;  // cap on resident CTAs per SM of the band kernel (0 = no cap)
@@ -765,8 +765,9 @@ SPH_CAPI_VJP2(solid, _f, float)
 // device memory of its own. Examples are runtimes that reserve the whole device arena when the
 // process starts, so a later cudaMalloc from a plugin simply fails, and latency-bound service
 // loops in which cudaMalloc is off limits because it synchronises the device and may block. The
-// calculators above cannot serve such hosts for l_max > 8: their run-time-degree kernel reads the
-// prefactor tables from a device buffer that they cudaMalloc on first use.
+// calculators above cannot serve such hosts whenever a call goes to their run-time-degree kernel
+// (values and gradients: l_max > 10), which reads the prefactor tables from a device buffer that
+// they cudaMalloc on first use.
 //
 // This variant runs the same kernel (float64, values + gradients, run-time l_max) with those
 // tables placed in a fixed array that is part of the library image, so every GPU

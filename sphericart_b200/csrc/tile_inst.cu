@@ -1,5 +1,5 @@
 // Instantiates the tile kernels for one (type, l_max) pair: compile with
-//   -DSPH_T=float|double -DSPH_LMAX=0..8
+//   -DSPH_T=float|double -DSPH_LMAX=0..20
 #include "sph_launch.hpp"
 #include "sph_tile.cuh"
 
@@ -9,7 +9,7 @@
 #error "compile with -DSPH_T=float or -DSPH_T=double"
 #endif
 #ifndef SPH_LMAX
-#error "compile with -DSPH_LMAX=<0..8>"
+#error "compile with -DSPH_LMAX=<0..20>"
 #endif
 
 namespace sph_b200 {
