@@ -26,7 +26,7 @@ cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t str
     constexpr int P = 32 / G;
     const long long ngroups = (a.n + P - 1) / P;
     const long long want = (ngroups + a.warps - 1) / a.warps;
-    int grid = work_grid(want, max_blocks, a.iters);
+    int grid = work_grid(want, max_blocks, a.iters, /*all_or_nothing=*/true);
     if (a.iters <= 0 && a.grid_cap > 0 && grid > a.grid_cap) grid = a.grid_cap;
     BandArgs<T> k{};
     k.xyz = a.xyz;

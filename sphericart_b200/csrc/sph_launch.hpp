@@ -48,8 +48,17 @@ int device_sm_count(int device);
 // values+gradients: 7.0 against 5.8 TB/s of output): work follows the SMs that drain their stores
 // fastest instead of being split evenly in advance, and the CTAs' store bursts end up staggered.
 // `ctas_wanted` is the number of CTAs at one item per warp.
-inline int work_grid(long long ctas_wanted, int resident, int iters) {
+inline int work_grid(long long ctas_wanted, int resident, int iters, bool all_or_nothing = false) {
     long long grid = ctas_wanted < resident ? ctas_wanted : resident;
+    // Several items per warp only pay on large calls: below about sixteen waves of CTAs the partly
+    // filled last wave costs more than the staggering gains. A smaller call gets fewer items per
+    // warp; a kernel whose CTAs have a set-up to amortise (all_or_nothing: the band kernel and its
+    // tables) is launched persistently instead (l_max = 16 Hessians, 262,144 points: 0.76 ms against
+    // 0.80 ms).
+    if (iters > 1 && resident > 0) {
+        const long long fit = ctas_wanted / (16LL * resident);
+        if (fit < iters) iters = all_or_nothing ? 0 : (fit < 1 ? 1 : int(fit));
+    }
     if (iters > 0) grid = (ctas_wanted + iters - 1) / iters;
     if (grid > 0x7fffffffLL) grid = 0x7fffffffLL;  // the grid-stride loops cover the remainder
     return int(grid < 1 ? 1 : grid);

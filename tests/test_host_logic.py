@@ -95,3 +95,53 @@ def test_reference_arm_prints_one_json_line():
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "points/s" and line["value"] > 0
     assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+LAUNCH_RULES_PROGRAM = r"""
+#include "sph_launch.hpp"
+#include <cstdio>
+using namespace sph_b200;
+int main() {
+    // work_grid(ctas wanted at one item per warp, resident CTAs, items per warp)
+    std::printf("grid %d %d %d %d %d %d %d\n", work_grid(100, 444, 0), work_grid(100000, 444, 0), work_grid(131072, 740, 1),
+                work_grid(16384, 444, 32, true), work_grid(500000, 444, 32, true), work_grid(1LL << 40, 444, 1),
+                work_grid(40000, 1184, 4));
+    // tile_serves(kind, l_max, element bytes): kind 0..2 forward level, 3 VJP, 4 second-order VJP
+    for (int kind = 0; kind < 5; ++kind) {
+        for (int elem = 4; elem <= 8; elem += 4) {
+            int last = -1;
+            for (int l = 0; l <= 40; ++l) if (tile_serves(kind, l, elem)) last = l;
+            std::printf("serves %d %d %d\n", kind, elem, last);
+        }
+    }
+    return 0;
+}
+"""
+
+
+def test_launch_rules(tmp_path):
+    """The host-side rules that size grids and pick the kernel family, compiled from the library's
+    own header: persistent launches take min(wanted, resident) CTAs; short-lived launches divide the
+    work by the items per warp, unless that leaves fewer than sixteen waves of CTAs (then fewer items
+    per warp, or - for the band kernel - a persistent launch); grids never exceed the hardware limit;
+    the tile kernels end where the measured crossovers put them."""
+    src = tmp_path / "rules.cpp"
+    src.write_text(LAUNCH_RULES_PROGRAM)
+    exe = tmp_path / "rules"
+    csrc = os.path.join(ROOT, "sphericart_b200", "csrc")
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    subprocess.run(["g++", "-std=c++17", "-I", csrc, "-I", cuda_inc, str(src), "-o", str(exe)], check=True)
+    lines = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split("\n")
+    grid = [int(v) for v in lines[0].split()[1:]]
+    assert grid[0] == 100 and grid[1] == 444          # persistent
+    assert grid[2] == 131072                          # one item per warp: one CTA per item
+    assert grid[3] == 444                             # 512 CTAs would be 1.2 waves: persistent instead
+    assert grid[4] == (500000 + 31) // 32             # large call: the full 32 items per warp
+    assert grid[5] == 2 ** 31 - 1                     # clamped; the kernels' loops cover the rest
+    assert grid[6] == 20000                           # 4 items asked, 2 kept: 40000 / (16 * 1184) = 2
+    serves = {(int(a), int(b)): int(c) for a, b, c in (ln.split()[1:] for ln in lines[1:] if ln.startswith("serves"))}
+    assert serves[(0, 4)] == 20 and serves[(0, 8)] == 20          # values
+    assert serves[(1, 4)] == 10 and serves[(1, 8)] == 10          # gradients
+    assert serves[(2, 4)] == 5 and serves[(2, 8)] == 4            # Hessians: also bounded by a 100 KB image
+    assert serves[(3, 4)] == 20 and serves[(3, 8)] == 14          # VJP: two double-buffered tiles per SM
+    assert serves[(4, 4)] == 5 and serves[(4, 8)] == 5            # second-order VJP
