@@ -277,18 +277,29 @@ __global__ void __launch_bounds__(128) sph_band_kernel(const __grid_constant__ B
 
     const long long ngroups = (a.n + P - 1) / P;
     const long long stride = (long long)gridDim.x * nwarps;
+    // A group's point is fetched while the previous group is evaluated: under a saturated write
+    // stream a DRAM read takes microseconds, and a warp has nothing else to do until it has its point.
+    auto fetch_point = [&](long long group, T& px, T& py, T& pz) {
+        px = T(1);
+        py = T(0);
+        pz = T(0);
+        const long long ip = group * P + pt;
+        if (group < ngroups && ip < a.n) {
+            px = a.xyz[3 * ip + 0];
+            py = a.xyz[3 * ip + 1];
+            pz = a.xyz[3 * ip + 2];
+        }
+    };
+    T next_x, next_y, next_z;
+    fetch_point((long long)blockIdx.x * nwarps + warp, next_x, next_y, next_z);
     for (long long grp = (long long)blockIdx.x * nwarps + warp; grp < ngroups; grp += stride) {
         const long long first = grp * P;
         const long long i = first + pt;
         const bool valid = i < a.n;
         const int nvalid = (a.n - first) < P ? int(a.n - first) : P;
 
-        T x = T(1), y = T(0), z = T(0);
-        if (valid) {
-            x = a.xyz[3 * i + 0];
-            y = a.xyz[3 * i + 1];
-            z = a.xyz[3 * i + 2];
-        }
+        T x = next_x, y = next_y, z = next_z;
+        fetch_point(grp + stride, next_x, next_y, next_z);
         UnitSphere<T> us{x, y, z, T(0), T(0)};
         if constexpr (NORM) {
             const T ir = T(1) / sqrt(x * x + y * y + z * z);
