@@ -14,13 +14,15 @@ backward passes materialise ``dsph`` / ``ddsph`` and reduce them with tensor exp
 * values, gradients and Hessians -> contraction of the saved outputs, as in the reference
                             (third derivatives are not supported).
 
-    import sphericart_b200.torch_ops            # registers the operators
+    import sphericart_b200.torch_ops as sbt     # registers the operators
     sph = torch.ops.sphericart_b200.spherical_harmonics(xyz_cuda, 8)
+    sph = sbt.SphericalHarmonics(8)(xyz_cuda)    # the same through a (scriptable) torch.nn.Module
 
 Only CUDA tensors are served; a CPU tensor raises ``NotImplementedError`` from the dispatcher.
 """
 
 import os
+from typing import Tuple
 
 import torch
 
@@ -81,3 +83,64 @@ def _register_vmap(prefix):
 for _prefix in ("spherical_harmonics", "solid_harmonics"):
     _register_fakes(_prefix)
     _register_vmap(_prefix)
+
+
+class SphericalHarmonics(torch.nn.Module):
+    """Real spherical harmonics of CUDA points as a ``torch.nn.Module`` over the operators above:
+    the interface of the reference's ``sphericart.torch.SphericalHarmonics``
+    (``sphericart-torch/python/sphericart/torch/spherical_hamonics.py:7-161``) - ``forward`` and
+    ``compute`` return ``(n_samples, (l_max+1)^2)`` values and are differentiable (twice) through
+    the fused backward kernels; ``compute_with_gradients`` / ``compute_with_hessians`` also return
+    ``(n_samples, 3, ny)`` gradients and ``(n_samples, 3, 3, ny)`` Hessians. Works under
+    ``torch.jit.script``. There is no CPU code path: CPU tensors are refused."""
+
+    def __init__(self, l_max: int):
+        super().__init__()
+        self._l_max = l_max
+
+    def forward(self, xyz: torch.Tensor) -> torch.Tensor:
+        return torch.ops.sphericart_b200.spherical_harmonics(xyz, self._l_max)
+
+    @torch.jit.export
+    def compute(self, xyz: torch.Tensor) -> torch.Tensor:
+        return self.forward(xyz)
+
+    @torch.jit.export
+    def compute_with_gradients(self, xyz: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        return torch.ops.sphericart_b200.spherical_harmonics_with_gradients(xyz, self._l_max)
+
+    @torch.jit.export
+    def compute_with_hessians(self, xyz: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        return torch.ops.sphericart_b200.spherical_harmonics_with_hessians(xyz, self._l_max)
+
+    @torch.jit.export
+    def l_max(self) -> int:
+        return self._l_max
+
+
+class SolidHarmonics(torch.nn.Module):
+    """Solid harmonics ``r^l Y_l^m``: same interface as :class:`SphericalHarmonics`
+    (reference: ``spherical_hamonics.py:164-209``)."""
+
+    def __init__(self, l_max: int):
+        super().__init__()
+        self._l_max = l_max
+
+    def forward(self, xyz: torch.Tensor) -> torch.Tensor:
+        return torch.ops.sphericart_b200.solid_harmonics(xyz, self._l_max)
+
+    @torch.jit.export
+    def compute(self, xyz: torch.Tensor) -> torch.Tensor:
+        return self.forward(xyz)
+
+    @torch.jit.export
+    def compute_with_gradients(self, xyz: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        return torch.ops.sphericart_b200.solid_harmonics_with_gradients(xyz, self._l_max)
+
+    @torch.jit.export
+    def compute_with_hessians(self, xyz: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        return torch.ops.sphericart_b200.solid_harmonics_with_hessians(xyz, self._l_max)
+
+    @torch.jit.export
+    def l_max(self) -> int:
+        return self._l_max

@@ -144,6 +144,39 @@ class _Module(torch.nn.Module):
         return self._ops.solid_harmonics(xyz, 4)
 
 
+def test_modules_script_and_train(ops, oracle_mod):
+    """The torch.nn.Module wrappers under TorchScript, as the reference tests its own
+    (sphericart-torch/python/tests/test_script.py): scripted and eager modules agree, gradients flow."""
+    import sphericart_b200.torch_ops as sbt
+
+    class Wrapper(torch.nn.Module):
+        def __init__(self, l_max: int, normalized: bool):
+            super().__init__()
+            self._sph = sbt.SphericalHarmonics(l_max) if normalized else sbt.SolidHarmonics(l_max)
+
+        def forward(self, xyz):
+            sph, dsph = self._sph.compute_with_gradients(xyz)
+            return self._sph.compute(xyz), sph, dsph
+
+    torch.manual_seed(8)
+    xyz = (6 * torch.randn(100, 3, dtype=torch.float64, device="cuda")).requires_grad_(True)
+    for normalized in (True, False):
+        eager = Wrapper(6, normalized)
+        scripted = torch.jit.script(eager)
+        for a, b in zip(eager(xyz), scripted(xyz)):
+            assert torch.equal(a, b)
+        want = _reference(oracle_mod, xyz.detach().cpu().numpy(), 6, normalized, 1)
+        err, bad = oracle_mod.scaled_error(scripted(xyz)[0].detach().cpu().numpy(), want[0], 6)
+        assert bad == 0 and err <= 1e-12
+        w = torch.randn(49, dtype=torch.float64, device="cuda")
+        loss = (torch.sin(scripted(xyz)[0]) @ w).sum()
+        (grad,) = torch.autograd.grad(loss, xyz)
+        sph, dsph = eager(xyz)[1].detach(), eager(xyz)[2].detach()
+        expected = torch.einsum("nk,nak->na", torch.cos(sph) * w, dsph)
+        assert torch.allclose(grad, expected, rtol=1e-9, atol=1e-10 * float(expected.abs().max()))
+        assert eager._sph.l_max() == 6
+
+
 def test_operators_record_into_a_cuda_graph(ops):
     """Forward and backward of a small model recorded once and replayed on new data; the operators'
     output allocations come from the graph's private pool."""
