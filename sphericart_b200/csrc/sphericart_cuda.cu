@@ -243,9 +243,10 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
     plan.warps = warps;
     plan.grid_cap = 0;
     if (plan.mode == 2 && forced_warps == 0) {
-        // Direct stores: every warp keeps several write streams open in L2 / DRAM, and measured
-        // throughput peaks at eight warps per SM (12 warps: 12 % slower, 4 warps: 28 % slower on a
-        // B200 at l_max = 32, float64). Two CTAs of four warps.
+        // Direct stores: every warp keeps several write streams open in L2 / DRAM. In a persistent
+        // launch (smaller calls, see work_grid()) measured throughput peaks at eight warps per SM
+        // (12 warps: 12 % slower, 4 warps: 28 % slower on a B200 at l_max = 32, float64), hence the
+        // cap of two CTAs of four warps per SM; a launch of short-lived CTAs is not capped.
         plan.warps = warps = 4;
         if (table_bytes + 4 * per_warp > smem_limit) plan.warps = warps = 1;
         plan.grid_cap = (warps == 4 ? 2 : 8) * sm_count;

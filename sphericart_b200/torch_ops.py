@@ -144,3 +144,59 @@ class SolidHarmonics(torch.nn.Module):
     @torch.jit.export
     def l_max(self) -> int:
         return self._l_max
+
+
+def e3nn_spherical_harmonics(l_list, x: torch.Tensor, normalize: bool = False, normalization: str = "integral"):
+    """Harmonics in the conventions of ``e3nn.o3.spherical_harmonics``: the function the reference
+    offers in ``sphericart-torch/python/sphericart/torch/e3nn.py:10-80``, for CUDA tensors.
+
+    ``l_list``: one degree or a list of degrees (everything up to the largest is evaluated, the
+    listed blocks are returned in the listed order); ``x``: ``(n, 3)`` points with e3nn's axis order
+    (y, z, x in this library's terms); ``normalize``: spherical (True) or solid (False) harmonics;
+    ``normalization``: "integral" (this library's), "component" (times sqrt(4 pi)) or "norm" (times
+    sqrt(4 pi / (2 l + 1))). Axis permutation, scaling and block selection are one gather of the
+    input and one indexed multiply of the output; autograd flows through the operators."""
+    import math
+
+    degrees = [int(v) for v in l_list] if hasattr(l_list, "__len__") else [int(l_list)]
+    if normalization not in ("integral", "norm", "component"):
+        raise ValueError('normalization must be "integral", "norm" or "component"')
+    l_max = max(degrees)
+    xyz = x[:, [2, 0, 1]]
+    op = ops.spherical_harmonics if normalize else ops.solid_harmonics
+    sh = op(xyz, l_max)
+    columns, scales = [], []
+    for l in degrees:
+        scale = 1.0 if normalization == "integral" else math.sqrt(4 * math.pi)
+        if normalization == "norm":
+            scale /= math.sqrt(2 * l + 1)
+        columns.extend(range(l * l, (l + 1) * (l + 1)))
+        scales.extend([scale] * (2 * l + 1))
+    whole = columns == list(range((l_max + 1) ** 2))
+    if not whole:
+        sh = sh[:, torch.tensor(columns, dtype=torch.long, device=sh.device)]
+    if normalization != "integral":
+        sh = sh * torch.tensor(scales, dtype=sh.dtype, device=sh.device)
+    return sh
+
+
+_E3NN_ORIGINAL = None
+
+
+def patch_e3nn(e3nn_module) -> None:
+    """Makes ``e3nn_module.o3.spherical_harmonics`` call :func:`e3nn_spherical_harmonics`
+    (reference: ``e3nn.py:86-103``)."""
+    global _E3NN_ORIGINAL
+    if _E3NN_ORIGINAL is not None:
+        raise RuntimeError("It appears that e3nn has already been patched")
+    _E3NN_ORIGINAL = e3nn_module.o3.spherical_harmonics
+    e3nn_module.o3.spherical_harmonics = e3nn_spherical_harmonics
+
+
+def unpatch_e3nn(e3nn_module) -> None:
+    """Restores the function :func:`patch_e3nn` replaced (reference: ``e3nn.py:106-116``)."""
+    global _E3NN_ORIGINAL
+    if _E3NN_ORIGINAL is None:
+        raise RuntimeError("It appears that e3nn has not been patched")
+    e3nn_module.o3.spherical_harmonics = _E3NN_ORIGINAL
+    _E3NN_ORIGINAL = None

@@ -177,6 +177,40 @@ def test_modules_script_and_train(ops, oracle_mod):
         assert eager._sph.l_max() == 6
 
 
+def test_e3nn_conventions(ops):
+    """Axis order, block selection and the three normalisations of the e3nn-style entry point
+    (reference: sphericart-torch/python/sphericart/torch/e3nn.py:10-80; its test compares with e3nn
+    itself, which is not installed here, so the closed forms of l = 0, 1 stand in for it)."""
+    import math
+    import types
+
+    import sphericart_b200.torch_ops as sbt
+
+    torch.manual_seed(9)
+    x = torch.randn(50, 3, dtype=torch.float64, device="cuda", requires_grad=True)
+    full = ops.spherical_harmonics(x[:, [2, 0, 1]], 3)
+    got = sbt.e3nn_spherical_harmonics([1, 3], x, normalize=True, normalization="norm")
+    assert tuple(got.shape) == (50, 3 + 7)
+    assert torch.allclose(got[:, :3], full[:, 1:4] * math.sqrt(4 * math.pi / 3))
+    assert torch.allclose(got[:, 3:], full[:, 9:16] * math.sqrt(4 * math.pi / 7))
+    # e3nn: component normalisation, l = 1 -> sqrt(3) * (x, y, z) / r in e3nn's own axis order
+    comp = sbt.e3nn_spherical_harmonics(1, x, normalize=True, normalization="component")
+    unit = x / x.norm(dim=1, keepdim=True)
+    assert torch.allclose(comp, math.sqrt(3) * unit, atol=1e-12)
+    # solid harmonics, integral normalisation, all blocks: this library's own output on permuted axes
+    solid = sbt.e3nn_spherical_harmonics([0, 1, 2], x, normalize=False)
+    assert torch.equal(solid, ops.solid_harmonics(x[:, [2, 0, 1]], 2))
+    comp.sum().backward()
+    assert x.grad is not None and bool(torch.isfinite(x.grad).all())
+    fake = types.SimpleNamespace(o3=types.SimpleNamespace(spherical_harmonics="original"))
+    sbt.patch_e3nn(fake)
+    assert fake.o3.spherical_harmonics is sbt.e3nn_spherical_harmonics
+    with pytest.raises(RuntimeError):
+        sbt.patch_e3nn(fake)
+    sbt.unpatch_e3nn(fake)
+    assert fake.o3.spherical_harmonics == "original"
+
+
 def test_operators_record_into_a_cuda_graph(ops):
     """Forward and backward of a small model recorded once and replayed on new data; the operators'
     output allocations come from the graph's private pool."""
