@@ -70,6 +70,53 @@ template <typename T, int NY, int LEVEL> struct TileSink {
     }
 };
 
+// Copies `rows` rows of LEN elements, kept in shared memory with row stride STRIDE, to a contiguous
+// 16-byte aligned span of global memory in 16-byte pieces (LEN is a multiple of 16 elements, so a
+// piece never straddles two rows; the shared-memory side is read element by element because
+// padded rows are not 16-byte aligned).
+template <typename T, int LEN, int STRIDE>
+__device__ __forceinline__ void copy_rows_out_16(T* __restrict__ gdst, const T* img, int rows, int lane) {
+    constexpr int Q = 16 / int(sizeof(T));
+    const int pieces = rows * (LEN / Q);
+    for (int v = lane; v < pieces; v += 32) {
+        const int e = v * Q;
+        const T* src = img + (e / LEN) * STRIDE + (e % LEN);
+        if constexpr (sizeof(T) == 4) {
+            const float4 piece = make_float4(src[0], src[1], src[2], src[3]);
+            reinterpret_cast<float4*>(gdst)[v] = piece;
+        } else {
+            const double2 piece = make_double2(src[0], src[1]);
+            reinterpret_cast<double2*>(gdst)[v] = piece;
+        }
+    }
+}
+
+// The reverse: a contiguous 16-byte aligned span of global memory into padded rows, at most
+// MAXROWS of them (a compile-time trip count, so that the loop unrolls and its loads overlap).
+template <typename T, int LEN, int STRIDE, int MAXROWS>
+__device__ __forceinline__ void copy_rows_in_16(T* img, const T* __restrict__ gsrc, int rows, int lane) {
+    constexpr int Q = 16 / int(sizeof(T));
+    const int pieces = rows * (LEN / Q);
+#pragma unroll
+    for (int v0 = 0; v0 < MAXROWS * (LEN / Q); v0 += 32) {
+        const int v = v0 + lane;
+        if (v >= pieces) continue;
+        const int e = v * Q;
+        T* dst = img + (e / LEN) * STRIDE + (e % LEN);
+        if constexpr (sizeof(T) == 4) {
+            const float4 piece = reinterpret_cast<const float4*>(gsrc)[v];
+            dst[0] = piece.x;
+            dst[1] = piece.y;
+            dst[2] = piece.z;
+            dst[3] = piece.w;
+        } else {
+            const double2 piece = reinterpret_cast<const double2*>(gsrc)[v];
+            dst[0] = piece.x;
+            dst[1] = piece.y;
+        }
+    }
+}
+
 template <typename T, int LMAX, int LEVEL> constexpr size_t tile_smem_bytes() {
     return size_t(TILE_POINTS) * tile_point_elems(n_columns(LMAX), LEVEL, int(sizeof(T))) * sizeof(T);
 }
@@ -94,7 +141,9 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
     constexpr int PAD = tile_row_pad(NY, int(sizeof(T)));
     constexpr int S0 = NY + PAD, S1 = 3 * NY + PAD, S2 = 9 * NY + PAD;
     constexpr int ROW = tile_point_elems(NY, LEVEL, int(sizeof(T)));
-    // (measured: worthwhile from 256-byte rows on; shorter padded rows are copied out by the warp)
+    // (measured: worthwhile from 256-byte rows on; shorter padded rows are copied out by the warp,
+    // in 16-byte pieces when the outputs are 16-byte aligned - which is what use_bulk says)
+    const bool aligned16_out = use_bulk != 0;
     if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     // bulk-store groups are per thread: with padded rows every lane issues and waits for its own
     const bool bulk_lane = use_bulk && (PAD != 0 || lane_of_warp() == 0);
@@ -167,6 +216,12 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
                 }
                 bulk_commit();
             }
+        } else if (PAD != 0 && aligned16_out) {
+            __syncwarp();
+            copy_rows_out_16<T, NY, S0>(sph + first * NY, img_sph, npts, lane);
+            if constexpr (LEVEL >= 1) copy_rows_out_16<T, 3 * NY, S1>(dsph + first * 3 * NY, img_d, npts, lane);
+            if constexpr (LEVEL >= 2) copy_rows_out_16<T, 9 * NY, S2>(ddsph + first * 9 * NY, img_dd, npts, lane);
+            __syncwarp();
         } else {
             __syncwarp();
             // element e of a span's output lies in row e / row_length of the image
@@ -265,6 +320,7 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
     // (measured: worthwhile from 256-byte rows on; shorter padded rows are staged by the warp)
     constexpr int PAD = tile_row_pad(NY, int(sizeof(T)));
     constexpr int S = NY + PAD;
+    const bool aligned16_in = use_bulk != 0;
     if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
@@ -330,7 +386,13 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             phase[cur] ^= 1u;
         } else {
             const T* gsrc = sph_grad + first * NY;
-            for (int e = lane; e < TILE_POINTS * NY; e += 32) img[cur][e + PAD * (e / NY)] = (e < npts * NY) ? gsrc[e] : T(0);
+            if (PAD != 0 && aligned16_in) {
+                // rows past the end of the input keep whatever they hold: their lanes write no result
+                copy_rows_in_16<T, NY, S, TILE_POINTS>(img[cur], gsrc, npts, lane);
+            } else {
+                for (int e = lane; e < TILE_POINTS * NY; e += 32)
+                    img[cur][e + PAD * (e / NY)] = (e < npts * NY) ? gsrc[e] : T(0);
+            }
             __syncwarp();
         }
 
