@@ -11,7 +11,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = os.path.join(ROOT, "include", "sphericart_b200.h")
-REFERENCE_HEADER_DIR = "/root/reference/sphericart/include"
+REFERENCE_HEADER_DIR = os.path.join(os.environ.get("SPHERICART_REF", "/root/reference"), "sphericart", "include")
 
 
 def _declared_functions():
