@@ -255,6 +255,12 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
     while (warps > 1 && table_bytes + warps * per_warp > smem_limit) --warps;  // a forced count may not fit
     plan.warps = warps;
     plan.smem = table_bytes + warps * per_warp;
+    if (knobs().band_max_ctas > 0) {
+        // the cap also holds for launches of short-lived CTAs: ask for so much shared memory that no
+        // more CTAs fit an SM (228 KB per SM, 1 KB reserved per CTA)
+        const size_t floor_bytes = size_t(233472) / (size_t(knobs().band_max_ctas) + 1) - 1024 + 256;
+        if (plan.smem < floor_bytes && floor_bytes <= smem_limit) plan.smem = floor_bytes;
+    }
     if (plan.smem > smem_limit) plan.feasible = false;
     // Short-lived CTAs (see work_grid()); each one rebuilds the tables in shared memory, which a few
     // dozen groups per warp amortise. Measured on a B200: l_max = 16 float32 Hessians 0.78 -> 0.81 of
