@@ -274,3 +274,77 @@ def test_host_cost_of_one_call(ops, capsys):
     with capsys.disabled():
         print(f"\n[host cost per call, 64 points l_max=8 f64] {line}")
     assert t_op <= 1.5 * t_py
+
+
+def test_float32_tracks_float64(ops):
+    """Values and gradients of a loss in float32 against float64 on the same points
+    (the check of sphericart-torch/python/tests/test_precision.py, solid harmonics, l_max = 4)."""
+    import sphericart_b200.torch_ops as sbt
+
+    torch.manual_seed(10)
+    base = 6 * torch.randn(100, 3, dtype=torch.float64, device="cuda")
+    x64 = base.clone().requires_grad_(True)
+    x32 = base.to(torch.float32).requires_grad_(True)
+    calc = sbt.SolidHarmonics(4)
+    s64, s32 = calc.compute(x64), calc.compute(x32)
+    assert float(((s64.detach() / s32.detach() - 1) ** 2).sum()) < 1e-5
+    (s64 ** 2).sum().backward()
+    (s32 ** 2).sum().backward()
+    assert torch.allclose(x64.grad, x32.grad.to(torch.float64), rtol=1e-4, atol=1e-4 * float(x64.grad.abs().max()))
+
+
+@pytest.mark.parametrize("l_max", [0, 3, 7, 10, 20, 50])
+def test_no_points(ops, l_max):
+    """Empty inputs give empty outputs of the right shape from every operator, also beyond the
+    degrees the compile-time kernels cover (sphericart-torch/python/tests/test_no_points.py)."""
+    ny = (l_max + 1) ** 2
+    for dtype in (torch.float32, torch.float64):
+        if dtype == torch.float32 and l_max > 28:
+            continue
+        xyz = torch.empty((0, 3), dtype=dtype, device="cuda")
+        for prefix in ("spherical_harmonics", "solid_harmonics"):
+            assert tuple(getattr(ops, prefix)(xyz, l_max).shape) == (0, ny)
+            shapes = [tuple(t.shape) for t in getattr(ops, prefix + "_with_hessians")(xyz, l_max)]
+            assert shapes == [(0, ny), (0, 3, ny), (0, 3, 3, ny)]
+            g = torch.empty((0, ny), dtype=dtype, device="cuda")
+            assert tuple(getattr(ops, prefix + "_vjp")(xyz, g, l_max).shape) == (0, 3)
+
+
+def test_scripted_module_survives_save_and_load(ops, tmp_path):
+    import sphericart_b200.torch_ops as sbt
+
+    xyz = torch.randn(33, 3, dtype=torch.float64, device="cuda")
+    scripted = torch.jit.script(sbt.SphericalHarmonics(5))
+    path = str(tmp_path / "sph.pt")
+    torch.jit.save(scripted, path)
+    loaded = torch.jit.load(path)
+    assert torch.equal(loaded(xyz), scripted(xyz))
+    assert all(torch.equal(a, b) for a, b in zip(loaded.compute_with_hessians(xyz), scripted.compute_with_hessians(xyz)))
+
+
+def test_torch_compile_keeps_the_operator_in_one_graph(ops):
+    """torch.compile(fullgraph=True) around the module: the operator is an opaque node with a shape
+    rule, so there is no graph break, and results and gradients agree with eager mode
+    (sphericart-torch/python/tests/test_compile.py). The compiler only handles the surrounding
+    tensor expressions; the harmonics still come from this library's kernels."""
+    import sphericart_b200.torch_ops as sbt
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self._sph = sbt.SphericalHarmonics(10)
+
+        def forward(self, xyz):
+            return torch.tanh(self._sph.compute(xyz)).sum(dim=1)
+
+    torch.manual_seed(11)
+    base = 6 * torch.randn(100, 3, dtype=torch.float64, device="cuda")
+    model = Model()
+    x_eager = base.clone().requires_grad_(True)
+    model(x_eager).sum().backward()
+    compiled = torch.compile(model, fullgraph=True)
+    x_comp = base.clone().requires_grad_(True)
+    out = compiled(x_comp)
+    out.sum().backward()
+    assert torch.allclose(out, model(base))
+    assert torch.allclose(x_comp.grad, x_eager.grad, rtol=1e-10, atol=1e-12)
