@@ -31,6 +31,7 @@ class _BaseHarmonics:
         self._l_max = int(l_max)
         self._lib = _c_lib.get_library()
         self._calculators = {}
+        self._deleted = False
 
     @property
     def l_max(self) -> int:
@@ -43,9 +44,12 @@ class _BaseHarmonics:
                 sfx = "" if dtype == torch.float64 else "_f"
                 getattr(lib, f"{self._prefix}_delete{sfx}")(handle)
         self._calculators = {}
+        self._deleted = True  # as in the reference front end: deleting twice is fine, using it afterwards is not
 
     # -- plumbing ---------------------------------------------------------------------------
     def _calculator(self, dtype):
+        if self._deleted:
+            raise ValueError("can not use a deleted calculator")
         handle = self._calculators.get(dtype)
         if handle is None:
             sfx = "" if dtype == torch.float64 else "_f"

@@ -91,6 +91,18 @@ def test_front_end_validates_before_touching_the_device():
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_deleted_calculators_refuse_work():
+    """python/tests/test_corner_cases.py:20-32: deleting twice is harmless, use after deletion raises."""
+    import sphericart_b200
+
+    for cls in (sphericart_b200.SphericalHarmonics, sphericart_b200.SolidHarmonics):
+        calc = cls(4)
+        calc.__del__()
+        calc.__del__()
+        with pytest.raises(ValueError, match="can not use a deleted calculator"):
+            calc._calculator(torch.float64)
+
+
 def test_no_gpu_means_failure_not_fallback():
     from sphericart_b200 import _c_lib
 
