@@ -61,7 +61,9 @@ class _BaseHarmonics:
 
     def _validate_xyz(self, xyz):
         if not isinstance(xyz, torch.Tensor):
-            raise TypeError("xyz must be a torch.Tensor on a CUDA device")
+            if not hasattr(xyz, "__cuda_array_interface__"):
+                raise TypeError("xyz must be a torch.Tensor or a CUDA array (CuPy, Numba) on a CUDA device")
+            xyz = torch.as_tensor(xyz, device="cuda")  # no copy: the same device memory
         if not xyz.is_cuda:
             raise TypeError("xyz must live on a CUDA device: this library has no CPU code path")
         if xyz.dtype not in (torch.float32, torch.float64):
@@ -99,18 +101,32 @@ class _BaseHarmonics:
         self.compute_raw(xyz.dtype, level, _ptr(xyz), n, _ptr(sph), _ptr(dsph), _ptr(ddsph), stream)
         return sph, dsph, ddsph
 
+    @staticmethod
+    def _like_input(xyz, tensors):
+        """Outputs in the array type of the input: torch tensors for torch tensors; for another
+        CUDA array type (the reference's front end serves CuPy arrays:
+        python/src/sphericart/spherical_harmonics.py:140-178) CuPy arrays over the same memory when
+        CuPy is installed, torch tensors otherwise."""
+        if isinstance(xyz, torch.Tensor):
+            return tensors
+        try:
+            import cupy
+        except ImportError:
+            return tensors
+        return tuple(None if t is None else cupy.asarray(t) for t in tensors)
+
     # -- public API -------------------------------------------------------------------------
     def compute(self, xyz, out=None) -> torch.Tensor:
-        """Harmonics for an ``(n_samples, 3)`` CUDA tensor -> ``(n_samples, (l_max+1)^2)``."""
-        return self._compute_impl(xyz, 0, out)[0]
+        """Harmonics for an ``(n_samples, 3)`` CUDA tensor (or CuPy / Numba array) -> ``(n_samples, (l_max+1)^2)``."""
+        return self._like_input(xyz, self._compute_impl(xyz, 0, out))[0]
 
     def compute_with_gradients(self, xyz, out=None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Values and Cartesian gradients ``(n_samples, 3, (l_max+1)^2)``."""
-        return self._compute_impl(xyz, 1, out)[:2]
+        return self._like_input(xyz, self._compute_impl(xyz, 1, out))[:2]
 
     def compute_with_hessians(self, xyz, out=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Values, gradients and Hessians ``(n_samples, 3, 3, (l_max+1)^2)``."""
-        return self._compute_impl(xyz, 2, out)
+        return self._like_input(xyz, self._compute_impl(xyz, 2, out))
 
     def compute_vjp(self, xyz, sph_grad, out=None) -> torch.Tensor:
         """``xyz_grad[i, a] = sum_k sph_grad[i, k] * dsph[i, a, k]`` in one kernel, no dsph in memory."""

@@ -363,3 +363,24 @@ def test_calls_can_be_recorded_in_a_cuda_graph(sb):
             torch.cuda.synchronize(dev)
             for a, b in zip(replayed, outs + [xyz_grad]):
                 assert torch.equal(a, b)
+
+
+def test_cuda_array_interface_inputs(sb):
+    """Any array that exposes ``__cuda_array_interface__`` (CuPy, Numba) is accepted in place, as the
+    reference's front end accepts CuPy arrays (python/src/sphericart/spherical_harmonics.py:140-178).
+    CuPy is not installed here, so a minimal stand-in carries the interface of a torch tensor."""
+
+    class DeviceArray:
+        def __init__(self, tensor):
+            self._keep = tensor
+            self.__cuda_array_interface__ = tensor.__cuda_array_interface__
+
+    torch.manual_seed(2)
+    xyz = torch.randn(77, 3, dtype=torch.float64, device="cuda")
+    calc = sb.SolidHarmonics(5)
+    want = calc.compute_with_gradients(xyz)
+    got = calc.compute_with_gradients(DeviceArray(xyz))
+    for a, b in zip(got, want):
+        assert torch.equal(torch.as_tensor(a, device="cuda"), b)
+    with pytest.raises(TypeError):
+        calc.compute(xyz.cpu().numpy())
