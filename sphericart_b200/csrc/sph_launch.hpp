@@ -20,15 +20,15 @@ constexpr int MAX_DEVICES = 64;
 //   gradients     l = 10: 0.70-0.76 / 0.54-0.56, l = 11: 0.58-0.63 / 0.61-0.67   -> tile up to 10
 //   Hessians      float32 l = 5: 0.59 / 0.47, l = 6: 0.48 / 0.71 (the Hessian columns need many registers
 //                 and the rows few images per SM)      -> tile up to 5 and a 100 KB image
-//   VJP           l = 9..12: 0.50-0.84 / 0.15-0.25     -> tile wherever compiled
+//   VJP           l = 9..20: 0.57-1.03 / 0.15-0.25     -> tile wherever compiled
 //   2nd-order VJP l = 5: 1.2-2.1 / 0.7-1.8 Gpoints/s, l = 6: 0.6-1.1 / 0.6-1.7   -> tile up to 5
 constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
     if (l_max > TILE_LMAX) return false;
     if (kind == 1) return l_max <= 10;
     if (kind == 2) return l_max <= 5 && size_t(32) * (l_max + 1) * (l_max + 1) * 13 * elem_bytes <= 100 * 1024;
     if (kind == 4) return l_max <= 5;
-    // the VJP kernel double-buffers a tile's upstream rows: at least two warps' worth per SM
-    if (kind == 3) return size_t(2) * 32 * (l_max + 1) * (l_max + 1) * elem_bytes <= 113 * 1024;
+    // the VJP kernel keeps a tile's upstream rows in shared memory: at least two tiles per SM
+    if (kind == 3) return size_t(32) * (l_max + 1) * (l_max + 1) * elem_bytes <= 113 * 1024;
     return true;
 }
 
@@ -73,8 +73,10 @@ template <typename T, int LMAX> struct TileLaunch {
     static cudaError_t forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
                                const T* host_tables, int warps, int span_tiles, bool use_bulk, int iters,
                                int tile_points, int device, cudaStream_t stream);
+    // buffers: 2 = the next tile's upstream rows stream in during the arithmetic, 1 = half the shared memory
     static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* host_tables, int warps, bool use_bulk, int iters, int device, cudaStream_t stream);
+                           const T* host_tables, int warps, bool use_bulk, int buffers, int iters, int device,
+                           cudaStream_t stream);
     // second-order backward: VJP of (values, gradients); sph_grad may be null
     static cudaError_t vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
                             T* xyz_grad, const T* host_tables, int warps, int iters, int device, cudaStream_t stream);

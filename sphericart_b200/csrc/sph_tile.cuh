@@ -300,9 +300,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 // translation unit, read by TileLaunch::device_error_flag().
 static __device__ int g_tile_wait_gave_up = 0;
 
-// Per warp: two images of the tile's sph_grad rows (double buffer) followed by two mbarriers.
-template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_smem_bytes() {
-    return 2 * size_t(TILE_POINTS) * (n_columns(LMAX) + tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T) + 16;
+// Per warp: one or two images of the tile's sph_grad rows followed by two mbarriers. Two images
+// (a double buffer) let the next tile stream in during the arithmetic; for long rows one image
+// leaves room for twice the warps per SM, which hides the latency better.
+template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_smem_bytes(int buffers) {
+    return size_t(buffers) * TILE_POINTS * (n_columns(LMAX) + tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T) + 16;
 }
 
 // use_bulk != 0: the rows of sph_grad are fetched by the TMA engine (1-D bulk load, completion on
@@ -312,7 +314,7 @@ template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_sm
 template <typename T, int LMAX, bool NORM>
 __global__ void __launch_bounds__(256)
 sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, long long n,
-                    T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk) {
+                    T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk, int buffers) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
     constexpr unsigned TILE_BYTES = unsigned(TILE_POINTS * NY * sizeof(T));
@@ -324,9 +326,10 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
     if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    unsigned char* mine = smem_raw + size_t(warp) * vjp_tile_smem_bytes<T, LMAX>();
-    T* img[2] = {reinterpret_cast<T*>(mine), reinterpret_cast<T*>(mine) + TILE_POINTS * S};
-    unsigned long long* bar = reinterpret_cast<unsigned long long*>(mine + 2 * size_t(TILE_POINTS) * S * sizeof(T));
+    unsigned char* mine = smem_raw + size_t(warp) * vjp_tile_smem_bytes<T, LMAX>(buffers);
+    T* img[2] = {reinterpret_cast<T*>(mine), reinterpret_cast<T*>(mine) + (buffers == 2 ? TILE_POINTS * S : 0)};
+    unsigned long long* bar =
+        reinterpret_cast<unsigned long long*>(mine + size_t(buffers) * TILE_POINTS * S * sizeof(T));
 
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long stride = (long long)gridDim.x * nwarps;
@@ -362,7 +365,7 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
 
     unsigned phase[2] = {0u, 0u};
     int cur = 0;
-    for (long long tile = tile0; tile < ntiles; tile += stride, cur ^= 1) {
+    for (long long tile = tile0; tile < ntiles; tile += stride) {
         const long long first = tile * TILE_POINTS;
         const long long i = first + lane;
         const int npts = (n - first) < TILE_POINTS ? int(n - first) : TILE_POINTS;
@@ -374,13 +377,14 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
         }
         // every lane finished reading the other buffer in the previous iteration (barrier at its
         // end), so the next tile may stream into it while this one is being processed
-        issue(tile + stride, cur ^ 1);
+        if (buffers == 2) issue(tile + stride, cur ^ 1);
 
         if (engine_tile(tile)) {
             if (!mbar_wait_bounded(&bar[cur], phase[cur])) {
                 g_tile_wait_gave_up = 1;
                 // do not leave with a copy in flight towards this CTA's shared memory
-                if (tile + stride < ntiles && engine_tile(tile + stride)) mbar_wait_bounded(&bar[cur ^ 1], phase[cur ^ 1]);
+                if (buffers == 2 && tile + stride < ntiles && engine_tile(tile + stride))
+                    mbar_wait_bounded(&bar[cur ^ 1], phase[cur ^ 1]);
                 return;
             }
             phase[cur] ^= 1u;
@@ -414,6 +418,11 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             xyz_grad[3 * i + 2] = sink.az;
         }
         __syncwarp();  // all lanes are done with img[cur]
+        if (buffers == 2) {
+            cur ^= 1;
+        } else {
+            issue(tile + stride, 0);  // single image: the next tile can only come in now
+        }
     }
 }
 

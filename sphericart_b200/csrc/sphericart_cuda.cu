@@ -46,6 +46,7 @@ struct Knobs {
     int band_iters;     // the same for the band kernels
     int tile_points;    // force the points per tile of the forward tile kernels (8, 16 or 32)
     int tile_lmax;      // largest l_max served by the tile kernels (default: all they are compiled for)
+    int vjp_buffers;    // force one or two upstream-gradient images per warp in the VJP tile kernel
 };
 
 int env_int(const char* name, int fallback) {
@@ -61,7 +62,8 @@ const Knobs& knobs() {
                             env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0),
                             env_int("SPH_B200_TILE_SPAN", 0),      env_int("SPH_B200_TILE_ITERS", 0),
                             env_int("SPH_B200_VJP_ITERS", 0),      env_int("SPH_B200_BAND_ITERS", 0),
-                            env_int("SPH_B200_TILE_POINTS", 0),    env_int("SPH_B200_TILE_LMAX", TILE_LMAX)};
+                            env_int("SPH_B200_TILE_POINTS", 0),    env_int("SPH_B200_TILE_LMAX", TILE_LMAX),
+                            env_int("SPH_B200_VJP_BUFFERS", 0)};
     return k;
 }
 
@@ -357,13 +359,14 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* tables, int warps, bool use_bulk, int iters, int device, cudaStream_t stream) {
+                           const T* tables, int warps, bool use_bulk, int buffers, int iters, int device,
+                           cudaStream_t stream) {
         if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, iters, device,
-                                            stream);
+            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, buffers, iters,
+                                            device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk,
-                                                  iters, device, stream);
+                                                  buffers, iters, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp2(int l_max, bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
@@ -447,16 +450,23 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
                   "tile second-order VJP kernel launch");
             return;
         }
-        const size_t per_warp = kind == 3 ? 2 * size_t(32) * (n_columns(l_max) + tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T) + 16
+        // VJP: one image of upstream rows per warp. A second one (the next tile streaming in during the
+        // arithmetic) measured slower at every degree: more resident warps hide the load better
+        // (l_max = 10 float32: 1.03 against 0.61 of the copy peak, l_max = 4: 1.06 against 0.99).
+        const size_t vjp_image = size_t(32) * (n_columns(l_max) + tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T);
+        int vjp_buffers = 1;
+        if (knobs().vjp_buffers == 1 || knobs().vjp_buffers == 2) vjp_buffers = knobs().vjp_buffers;
+        const size_t per_warp = kind == 3 ? vjp_buffers * vjp_image + 16
                                           : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
         if (kind == 3) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
-            // short-lived CTAs of four warps with four tiles each: measured best on a B200 (l_max = 4)
-            const int iters = resolve_iters(knobs().vjp_iters, 4);
+            // short-lived CTAs of four warps; one tile per warp with a single image (nothing to overlap a
+            // second tile with), four with the double buffer
+            const int iters = resolve_iters(knobs().vjp_iters, vjp_buffers == 1 ? 1 : 4);
             int warps = tile_warps(per_warp, props.smem_optin);
             if (iters > 0 && knobs().tile_warps == 0) warps = int(std::min<size_t>(4, std::max<size_t>(1, props.smem_optin / per_warp)));
-            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters,
-                                       scope.device, stream),
+            check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk,
+                                       vjp_buffers, iters, scope.device, stream),
                   "tile VJP kernel launch");
             return;
         }

@@ -94,17 +94,18 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
 
 template <typename T, int LMAX, bool NORM>
 cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, int warps,
-                       bool use_bulk, int iters, int device, cudaStream_t stream) {
-    static GridCache cache{};
+                       bool use_bulk, int buffers, int iters, int device, cudaStream_t stream) {
+    static GridCache cache[2] = {};
+    if (buffers != 1 && buffers != 2) return cudaErrorInvalidValue;
     auto kernel = sph_vjp_tile_kernel<T, LMAX, NORM>;
-    const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>();
-    const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
+    const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>(buffers);
+    const int max_blocks = cached_grid(cache[buffers - 1], kernel, warps, smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long want = (ntiles + warps - 1) / warps;
     const int grid = work_grid(want, max_blocks, iters);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables),
-                                               use_bulk ? 1 : 0);
+                                               use_bulk ? 1 : 0, buffers);
     return cudaGetLastError();
 }
 
@@ -157,13 +158,13 @@ cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xy
 
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                     const T* host_tables, int warps, bool use_bulk, int iters, int device,
+                                     const T* host_tables, int warps, bool use_bulk, int buffers, int iters, int device,
                                      cudaStream_t stream) {
     if constexpr (tile_serves(3, LMAX, int(sizeof(T)))) {
-        return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters,
-                                                      device, stream)
-                          : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, iters,
-                                                       device, stream);
+        return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, buffers,
+                                                      iters, device, stream)
+                          : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, buffers,
+                                                       iters, device, stream);
     } else {
         return cudaErrorInvalidConfiguration;
     }
