@@ -308,9 +308,11 @@ template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_sm
 }
 
 // use_bulk != 0: the rows of sph_grad are fetched by the TMA engine (1-D bulk load, completion on
-// an mbarrier), one tile ahead of the arithmetic, so the warp neither spends issue slots on the
-// staging copy nor waits for it. Requires a 16-byte aligned sph_grad; otherwise, and for the
-// ragged last tile, the warp stages the rows itself with coalesced loads.
+// an mbarrier), so the warp spends no issue slots on the staging copy; with buffers == 2 the next
+// tile is fetched one tile ahead of the arithmetic, with buffers == 1 (the default: half the
+// shared memory, twice the warps per SM) the other resident warps cover the wait. Requires a
+// 16-byte aligned sph_grad; otherwise, and for the ragged last tile, the warp stages the rows
+// itself with coalesced loads.
 template <typename T, int LMAX, bool NORM>
 __global__ void __launch_bounds__(256)
 sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, long long n,
