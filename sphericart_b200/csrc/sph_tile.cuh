@@ -419,6 +419,9 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             xyz_grad[3 * i + 1] = sink.ay;
             xyz_grad[3 * i + 2] = sink.az;
         }
+        // this buffer is written next by the TMA engine (async proxy) after having been read through
+        // ordinary loads: order the two
+        fence_proxy_async_smem();
         __syncwarp();  // all lanes are done with img[cur]
         if (buffers == 2) {
             cur ^= 1;
