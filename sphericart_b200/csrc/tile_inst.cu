@@ -46,12 +46,17 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
     static GridCache cache[3][9] = {};
     if (span_tiles < 1 || span_tiles > 8) return cudaErrorInvalidValue;
     auto kernel = sph_tile_kernel<T, LMAX, LEVEL, NORM>;
-    // Points per tile. For throughput: the widest tile of which an SM holds at least four images
+    // Points per tile. For throughput: the widest tile of which an SM holds at least five images
     // (measured on a B200, l_max = 8 gradients, 10^6 points: float64 32 / 16 / 8 points -> 0.70 / 0.96 /
-    // 0.84 of the copy peak with 2 / 4 / 10 images per SM; float32 32 / 16 -> 1.03 / 0.98 with 5 / 10).
+    // 0.84 of the copy peak with 2 / 5 / 10 images per SM; float32 32 / 16 -> 1.03 / 0.98 with 5 / 10;
+    // l_max = 9 float32 32 / 16 -> 0.87 / 0.90 with 4 / 8), at least eight where padded rows leave
+    // one by one (l_max = 7 float32 gradients 32 / 16 -> 0.76 / 0.91 with 6 / 12).
     // For calls that fit in one wave of resident CTAs a tile's latency is what counts: narrower
     // tiles still, as long as the call keeps fitting in one wave.
     const int candidates[3] = {32, 16, 8};
+    constexpr int NY_ = n_columns(LMAX);
+    constexpr bool ROW_WISE = tile_row_pad(NY_, int(sizeof(T))) != 0 && NY_ * sizeof(T) >= 256;
+    constexpr int MIN_IMAGES = ROW_WISE ? 8 : 5;
     const int sms = device_sm_count(device);
     int chosen = -1, max_blocks = 0;
     size_t smem = 0;
@@ -70,7 +75,7 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
             if (tile_points != 0) return cudaErrorLaunchOutOfResources;
             continue;
         }
-        if (tile_points != 0 || c == 2 || max_blocks * warps >= 4 * sms) chosen = c;
+        if (tile_points != 0 || c == 2 || max_blocks * warps >= MIN_IMAGES * sms) chosen = c;
     }
     if (chosen < 0) return tile_points != 0 ? cudaErrorInvalidValue : cudaErrorLaunchOutOfResources;
     if (tile_points == 0 && ctas_needed(chosen) <= max_blocks) {
