@@ -237,66 +237,6 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def run_sweep(degrees):
-    """Efficiency map, not part of the benchmark contract: for each element type and l_max, the
-    fraction of the measured copy peak that values, values+gradients, values+gradients+Hessians, the
-    fused VJP and the fused second-order VJP reach on one GPU (about 1.2 GB of traffic per launch,
-    CUDA events over 8 launches after 3 warm-ups). One text line per (type, l_max)."""
-    import torch
-
-    import sphericart_b200
-
-    device = torch.device("cuda", 0)
-    peak, _ = _peaks()
-
-    def timed(fn, iters=8):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize(device)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize(device)
-        return e0.elapsed_time(e1) / iters
-
-    def points_for(bytes_per_point):
-        return int(min(2 ** 23, max(1024, 1.2e9 // bytes_per_point))) // 32 * 32
-
-    for name, tdtype, size in (("f32", torch.float32, 4), ("f64", torch.float64, 8)):
-        for l_max in degrees:
-            if name == "f32" and l_max > 28:
-                continue
-            ny = (l_max + 1) ** 2
-            calc = sphericart_b200.SphericalHarmonics(l_max)
-            cells = []
-            for level in (0, 1, 2):
-                bpp = size * (3 + ny * (1, 4, 13)[level])
-                n = points_for(bpp)
-                xyz = torch.randn(n, 3, dtype=tdtype, device=device)
-                out = [torch.empty(s, dtype=tdtype, device=device) for s in [(n, ny), (n, 3, ny), (n, 3, 3, ny)][: level + 1]]
-                ms = timed(lambda: calc._compute_impl(xyz, level, out + [None] * (2 - level)))
-                cells.append(f"{('values', 'gradients', 'hessians')[level]} {bpp * n / ms / 1e6 / peak:.3f}")
-                del out
-            bpp = size * (6 + ny)
-            n = points_for(bpp)
-            xyz = torch.randn(n, 3, dtype=tdtype, device=device)
-            g = torch.randn(n, ny, dtype=tdtype, device=device)
-            o = torch.empty(n, 3, dtype=tdtype, device=device)
-            ms = timed(lambda: calc.compute_vjp(xyz, g, o))
-            cells.append(f"vjp {bpp * n / ms / 1e6 / peak:.3f}")
-            bpp = size * (6 + 4 * ny)
-            n = points_for(bpp)
-            xyz = torch.randn(n, 3, dtype=tdtype, device=device)
-            g = torch.randn(n, ny, dtype=tdtype, device=device)
-            dg = torch.randn(n, 3, ny, dtype=tdtype, device=device)
-            o = torch.empty(n, 3, dtype=tdtype, device=device)
-            ms = timed(lambda: calc.compute_vjp_with_gradients(xyz, g, dg, o))
-            cells.append(f"vjp2 {bpp * n / ms / 1e6 / peak:.3f}")
-            print(f"{name} l_max={l_max:2d} | " + " | ".join(cells), flush=True)
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -309,12 +249,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--config", default="metric", choices=sorted(workloads.CONFIGS),
                     help="metric = the headline case; cfg1..cfg5 = the other benchmark configurations")
-    ap.add_argument("--sweep", default=None, metavar="L1,L2,...",
-                    help="print the efficiency map over these degrees instead of the benchmark line (one GPU)")
     args = ap.parse_args()
-    if args.sweep:
-        run_sweep([int(v) for v in args.sweep.split(",")])
-        return
     if args.impl == "reference":
         run_reference_arm(args)
         return

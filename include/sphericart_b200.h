@@ -1,7 +1,7 @@
 /*
  * C ABI of the B200 (sm_100a) implementation of sphericart's CUDA calculators.
  *
- * The first 24 functions are, name for name and argument for argument, the CUDA half of the
+ * The first 20 functions are, name for name and argument for argument, the CUDA half of the
  * reference's C API (sphericart/include/sphericart.h:641-779, implemented in
  * sphericart/src/sphericart-capi.cpp:637-876); each declaration cites the line it replaces.
  * They keep the reference's conventions: *_new returns NULL on any failure, *_delete swallows
@@ -270,7 +270,10 @@ SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_with_gradi
  * GPU that loads the library holds it until the process exits) and calls no allocating routine.
  * Limit: l_max <= 32; larger values are rejected with an error. normalized != 0 selects spherical
  * harmonics, 0 solid harmonics. The first call on each device looks up the array's device address
- * and opts the kernel into its shared memory, so make that call before any stream capture. All
+ * and opts the kernel into its shared memory, so make that call before any stream capture. The
+ * first call on a device and any call whose l_max differs from the previous call's also enqueue a
+ * small host-to-device copy of the tables (from a host table the library keeps for the life of the
+ * process) in front of the kernel; a call made during stream capture always records that copy. All
  * calls on a device share the array: calls that can overlap on the GPU race on it, so order them.
  * Returns 0 on success; otherwise non-zero, message in sphericart_cuda_last_error(). */
 SPHERICART_EXPORT int sphericart_cuda_harmonics_with_gradients_no_alloc(

@@ -13,7 +13,11 @@
 //    n_samples x 3, n_samples x (l_max+1)^2, n_samples x 3 x (l_max+1)^2 and
 //    n_samples x 3 x 3 x (l_max+1)^2 elements; column (l, m) sits at l*l + l + m.
 //  * cuda_stream is a cudaStream_t cast to void* (nullptr = default stream). The call only
-//    enqueues work; it never synchronises and never allocates or frees the caller's buffers.
+//    enqueues work; it never allocates or frees the caller's buffers and, with one exception,
+//    never synchronises: the first call per calculator and device that is served by the
+//    run-time-degree kernel (values: l_max > 20, gradients: l_max > 10, Hessians: l_max > 5)
+//    allocates a few KB on that device for the calculator's tables and fills them with a blocking
+//    copy. Make that call once before recording a CUDA graph or entering a latency-critical loop.
 //  * The work runs on the device that owns xyz; the caller's current device is restored.
 //  * n_samples == 0 returns at once, even with null outputs. A null sph (or a null dsph / ddsph
 //    when that output was asked for) and every CUDA failure throw std::runtime_error.

@@ -3,7 +3,6 @@
 #include "sph_band.cuh"
 #include "sph_launch.hpp"
 
-#include <atomic>
 
 #ifndef SPH_T
 #error "compile with -DSPH_T=float or -DSPH_T=double"
@@ -19,9 +18,23 @@ namespace {
 template <typename T, int LEVEL, bool NORM, int G, bool VJP, bool DIRECT>
 cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t stream) {
     auto kernel = sph_band_kernel<T, LEVEL, NORM, G, VJP, DIRECT>;
-    // shared memory differs between calculators, so the occupancy query is not cached by kernel
-    // alone; it is cheap next to the work these kernels do per launch.
-    const int max_blocks = persistent_grid(reinterpret_cast<const void*>(kernel), a.warps * 32, a.smem, device);
+    // The occupancy query (and the raise of the kernel's shared-memory limit that goes with it) is
+    // remembered per thread for the last few (device, warps, shared memory) combinations of this
+    // instantiation, so that a steady stream of calls pays for it once.
+    struct Slot {
+        int device, warps, blocks;
+        size_t smem;
+    };
+    thread_local Slot slots[4] = {{-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}};
+    thread_local int next_slot = 0;
+    int max_blocks = -1;
+    for (const Slot& s : slots)
+        if (s.device == device && s.warps == a.warps && s.smem == a.smem) max_blocks = s.blocks;
+    if (max_blocks < 0) {
+        max_blocks = persistent_grid(reinterpret_cast<const void*>(kernel), a.warps * 32, a.smem, device);
+        slots[next_slot] = Slot{device, a.warps, max_blocks, a.smem};
+        next_slot = (next_slot + 1) % 4;
+    }
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     constexpr int P = 32 / G;
     const long long ngroups = (a.n + P - 1) / P;

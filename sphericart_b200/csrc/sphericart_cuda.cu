@@ -11,6 +11,7 @@
 #include "sph_launch.hpp"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -30,23 +31,21 @@ void check(cudaError_t status, const char* what) {
     }
 }
 
-// Development knobs, read from the environment once per process (0 = use the built-in choice).
+// Switches for the kernel-variant tests, read from the environment once per process (0 = use the
+// built-in choice). They select code paths the default dispatch reaches only for some inputs, so that
+// every path can be checked against the CPU reference on the same inputs; none is a tuning knob.
 struct Knobs {
-    int band_image_kb;  // per-warp image budget of the band kernel, KiB
     int band_lanes;     // force lanes per point (1..32, power of two)
     int band_warps;     // force warps per CTA of the band kernel (1..4)
     int tile_warps;     // force warps per CTA of the tile kernels (1..8)
     int force_band;     // route every call through the band kernel
     int no_bulk;        // copy tiles out with plain stores instead of TMA bulk stores
     int band_direct;    // 1: force direct global stores in the band kernel, -1: forbid them
-    int band_max_ctas;  // cap on resident CTAs per SM of the band kernel (0 = no cap)
-    int tile_span;      // force the number of 32-point tiles per image of the tile kernels (1..8)
     int tile_iters;     // work items per warp of the forward tile kernels (k > 0), -1: persistent launch
     int vjp_iters;      // the same for the backward tile kernels
     int band_iters;     // the same for the band kernels
     int tile_points;    // force the points per tile of the forward tile kernels (8, 16 or 32)
     int tile_lmax;      // largest l_max served by the tile kernels (default: all they are compiled for)
-    int vjp_buffers;    // force one or two upstream-gradient images per warp in the VJP tile kernel
 };
 
 int env_int(const char* name, int fallback) {
@@ -56,14 +55,12 @@ int env_int(const char* name, int fallback) {
 }
 
 const Knobs& knobs() {
-    static const Knobs k = {env_int("SPH_B200_BAND_IMAGE_KB", 64), env_int("SPH_B200_BAND_LANES", 0),
-                            env_int("SPH_B200_BAND_WARPS", 0),     env_int("SPH_B200_TILE_WARPS", 0),
-                            env_int("SPH_B200_FORCE_BAND", 0),     env_int("SPH_B200_NO_BULK", 0),
-                            env_int("SPH_B200_BAND_DIRECT", 0),    env_int("SPH_B200_BAND_MAX_CTAS", 0),
-                            env_int("SPH_B200_TILE_SPAN", 0),      env_int("SPH_B200_TILE_ITERS", 0),
-                            env_int("SPH_B200_VJP_ITERS", 0),      env_int("SPH_B200_BAND_ITERS", 0),
-                            env_int("SPH_B200_TILE_POINTS", 0),    env_int("SPH_B200_TILE_LMAX", TILE_LMAX),
-                            env_int("SPH_B200_VJP_BUFFERS", 0)};
+    static const Knobs k = {env_int("SPH_B200_BAND_LANES", 0),  env_int("SPH_B200_BAND_WARPS", 0),
+                            env_int("SPH_B200_TILE_WARPS", 0),  env_int("SPH_B200_FORCE_BAND", 0),
+                            env_int("SPH_B200_NO_BULK", 0),     env_int("SPH_B200_BAND_DIRECT", 0),
+                            env_int("SPH_B200_TILE_ITERS", 0),  env_int("SPH_B200_VJP_ITERS", 0),
+                            env_int("SPH_B200_BAND_ITERS", 0),  env_int("SPH_B200_TILE_POINTS", 0),
+                            env_int("SPH_B200_TILE_LMAX", TILE_LMAX)};
     return k;
 }
 
@@ -71,23 +68,25 @@ const Knobs& knobs() {
 int resolve_iters(int knob, int builtin) { return knob < 0 ? 0 : (knob > 0 ? knob : builtin); }
 
 struct DeviceProps {
-    bool known = false;
+    std::atomic<bool> known{false};
     int sm_count = 0;
     size_t smem_optin = 0;
 };
 std::mutex g_props_mutex;
 DeviceProps g_props[MAX_DEVICES];
 
+// Filled once per device; afterwards read without taking the lock.
 const DeviceProps& device_props(int device) {
-    std::lock_guard<std::mutex> lock(g_props_mutex);
     DeviceProps& p = g_props[device];
-    if (!p.known) {
+    if (p.known.load(std::memory_order_acquire)) return p;
+    std::lock_guard<std::mutex> lock(g_props_mutex);
+    if (!p.known.load(std::memory_order_relaxed)) {
         int v = 0;
         check(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
         p.sm_count = v;
         check(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, device), "cudaDeviceGetAttribute");
         p.smem_optin = size_t(v);
-        p.known = true;
+        p.known.store(true, std::memory_order_release);
     }
     return p;
 }
@@ -99,16 +98,23 @@ int device_sm_count(int device) { return device_props(device).sm_count; }
 int persistent_grid(const void* kernel, int block, size_t smem, int device) {
     const DeviceProps& props = device_props(device);
     if (smem > props.smem_optin) return 0;
-    // the limit is only ever raised: one kernel may be launched with several image sizes
-    cudaFuncAttributes attr;
-    if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    if (size_t(attr.maxDynamicSharedSizeBytes) < smem &&
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
+    {
+        // The dynamic shared-memory limit of a kernel is per-process state and one kernel may be
+        // launched with several sizes (calculators of different l_max, different tile widths) from
+        // several threads: the read-compare-raise sequence is serialised and the limit is only ever
+        // raised, so a concurrent launch that needs more never finds it lowered.
+        static std::mutex attribute_mutex;
+        std::lock_guard<std::mutex> lock(attribute_mutex);
+        cudaFuncAttributes attr;
+        if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        if (size_t(attr.maxDynamicSharedSizeBytes) < smem &&
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
     }
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, smem) != cudaSuccess) {
@@ -201,7 +207,7 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
     // Lanes per point. The pair loop is balanced for any G, so G is chosen for occupancy and for
     // amortising the per-group prologue: about four pairs per lane at least, and a warp's images
     // within the budget.
-    const size_t budget = size_t(knobs().band_image_kb) * 1024;
+    const size_t budget = 64 * 1024;
     const int pairs = n_table(L);
     int G = 32;
     while (G > 1 && pairs / G < 4) G /= 2;
@@ -253,16 +259,9 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
         if (table_bytes + 4 * per_warp > smem_limit) plan.warps = warps = 1;
         plan.grid_cap = (warps == 4 ? 2 : 8) * sm_count;
     }
-    if (knobs().band_max_ctas > 0) plan.grid_cap = knobs().band_max_ctas * sm_count;
     while (warps > 1 && table_bytes + warps * per_warp > smem_limit) --warps;  // a forced count may not fit
     plan.warps = warps;
     plan.smem = table_bytes + warps * per_warp;
-    if (knobs().band_max_ctas > 0) {
-        // the cap also holds for launches of short-lived CTAs: ask for so much shared memory that no
-        // more CTAs fit an SM (228 KB per SM, 1 KB reserved per CTA)
-        const size_t floor_bytes = size_t(233472) / (size_t(knobs().band_max_ctas) + 1) - 1024 + 256;
-        if (plan.smem < floor_bytes && floor_bytes <= smem_limit) plan.smem = floor_bytes;
-    }
     if (plan.smem > smem_limit) plan.feasible = false;
     // Short-lived CTAs (see work_grid()); each one rebuilds the tables in shared memory, which a few
     // dozen groups per warp amortise. Measured on a B200: l_max = 16 float32 Hessians 0.78 -> 0.81 of
@@ -454,8 +453,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         // arithmetic) measured slower at every degree: more resident warps hide the load better
         // (l_max = 10 float32: 1.03 against 0.61 of the copy peak, l_max = 4: 1.06 against 0.99).
         const size_t vjp_image = size_t(32) * (n_columns(l_max) + tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T);
-        int vjp_buffers = 1;
-        if (knobs().vjp_buffers == 1 || knobs().vjp_buffers == 2) vjp_buffers = knobs().vjp_buffers;
+        const int vjp_buffers = 1;
         const size_t per_warp = kind == 3 ? vjp_buffers * vjp_image + 16
                                           : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
         if (kind == 3) {
@@ -480,10 +478,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             // tiles per image: small tiles are grouped so that each bulk store moves about 8 KB or more
             // (12 KB for a persistent launch)
             const size_t store_bytes = iters > 0 ? 8 * 1024 : 12 * 1024;
-            int span_tiles = knobs().tile_span;
-            if (span_tiles < 1 || span_tiles > 8) {
-                span_tiles = int(std::min<size_t>(8, std::max<size_t>(1, (store_bytes + per_warp - 1) / per_warp)));
-            }
+            int span_tiles = int(std::min<size_t>(8, std::max<size_t>(1, (store_bytes + per_warp - 1) / per_warp)));
             while (span_tiles > 1 && span_tiles * per_warp > props.smem_optin) --span_tiles;
             int warps = tile_warps(span_tiles * per_warp, props.smem_optin);
             if (iters > 0 && knobs().tile_warps == 0) warps = 1;
@@ -801,8 +796,13 @@ SPH_CAPI_VJP2(solid, _f, float)
 // All calls on one device share the one array, and it keeps what the last call left in it. A call
 // overwrites, on the caller's stream, every byte the kernel will read unless the array already holds
 // the data for the same l_max (nothing in it has to start at zero, nothing is read before it is
-// written). Calls that may overlap on the GPU - different streams with no ordering between them -
-// race on the array; order such calls.
+// written); so besides the first call on a device, every call whose l_max differs from the previous
+// call's enqueues a small host-to-device copy in front of the kernel. The host side of that copy is
+// a table the library keeps for the life of the process. A call made while its stream is being
+// captured always records the copy with the kernel (the recorded work is then complete whatever the
+// array holds when it is replayed), and from then on calls on that device no longer skip the copy.
+// Calls that may overlap on the GPU - different streams with no ordering between them - race on the
+// array; order such calls.
 namespace {
 
 constexpr int NO_ALLOC_MAX_L = 32;
@@ -813,9 +813,13 @@ static __device__ __align__(256) unsigned char g_no_alloc_scratch[NO_ALLOC_SCRAT
 struct NoAllocDevice {
     unsigned char* scratch = nullptr;  // device address of g_no_alloc_scratch on this device
     int resident_l_max = -1;           // whose tables the array holds now
+    bool always_upload = false;        // a recorded (captured) call may rewrite the array at any time
 };
 std::mutex g_no_alloc_mutex;
 NoAllocDevice g_no_alloc_devices[sph_b200::MAX_DEVICES];
+// host tables per degree, built on first use and kept until the process ends: an asynchronous or
+// recorded copy may read them long after the call that enqueued it has returned
+std::vector<double> g_no_alloc_host_tables[NO_ALLOC_MAX_L + 1];
 
 void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_samples, double* sph, double* dsph,
                   void* cuda_stream) {
@@ -833,16 +837,18 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
     DeviceScope scope(xyz);
     const DeviceProps& props = device_props(scope.device);
 
-    // host-side tables and launch plan (host heap only)
-    std::vector<double> tables(2 * size_t(n_table(l_max)));
-    build_tables<double>(l_max, tables.data());
     const BandPlan plan = make_band_plan(l_max, /*kind=*/1, sizeof(double), props.smem_optin, props.sm_count);
-    const size_t table_bytes = tables.size() * sizeof(double);
+    const size_t table_bytes = 2 * size_t(n_table(l_max)) * sizeof(double);
     if (table_bytes > NO_ALLOC_SCRATCH_BYTES || !plan.feasible) {
         throw std::runtime_error("sphericart::cuda: internal tables do not fit the allocation-free array");
     }
 
     std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    std::vector<double>& tables = g_no_alloc_host_tables[l_max];  // host heap only
+    if (tables.empty()) {
+        tables.resize(2 * size_t(n_table(l_max)));
+        build_tables<double>(l_max, tables.data());
+    }
     NoAllocDevice& dev = g_no_alloc_devices[scope.device];
     if (dev.scratch == nullptr) {
         // once per device, with that device current (DeviceScope made it so)
@@ -850,7 +856,11 @@ void no_alloc_run(bool normalized, size_t l_max_, const double* xyz, size_t n_sa
         check(cudaGetSymbolAddress(&address, g_no_alloc_scratch), "cudaGetSymbolAddress(no-alloc array)");
         dev.scratch = static_cast<unsigned char*>(address);
     }
-    if (dev.resident_l_max != l_max) {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    check(cudaStreamIsCapturing(stream, &capture), "cudaStreamIsCapturing");
+    const bool capturing = capture != cudaStreamCaptureStatusNone;
+    if (capturing) dev.always_upload = true;
+    if (capturing || dev.always_upload || dev.resident_l_max != l_max) {
         check(cudaMemcpyAsync(dev.scratch, tables.data(), table_bytes, cudaMemcpyHostToDevice, stream),
               "cudaMemcpyAsync(tables)");
         dev.resident_l_max = l_max;

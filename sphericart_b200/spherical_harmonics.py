@@ -72,6 +72,29 @@ class _BaseHarmonics:
             raise ValueError("xyz tensor must be a `N x 3` array")
         return xyz.detach().contiguous()
 
+    @staticmethod
+    def _validate_out(out, xyz, shapes, names=("sph", "dsph", "ddsph"), require_cuda=True):
+        """Caller-provided output buffers are handed to the kernels as bare pointers, so everything
+        the kernels assume is checked here: one CUDA tensor per requested output, on the device of
+        ``xyz``, of its dtype, contiguous and of exactly the output's shape. Returns the buffers padded
+        with ``None`` to three entries. (``require_cuda=False`` lets the CPU-only tests reach the other checks.)"""
+        if isinstance(out, torch.Tensor):
+            out = (out,)
+        out = tuple(out)
+        if len(out) < len(shapes) or any(t is not None for t in out[len(shapes):]):
+            raise ValueError(f"out must hold exactly {len(shapes)} tensor(s) for this call, got {len(out)}")
+        for name, t, shape in zip(names, out, shapes):
+            if not isinstance(t, torch.Tensor) or (require_cuda and not t.is_cuda):
+                raise ValueError(f"out: {name} must be a CUDA tensor")
+            if t.device != xyz.device or t.dtype != xyz.dtype:
+                raise ValueError(f"out: {name} must be on {xyz.device} with dtype {xyz.dtype}, "
+                                 f"got {t.device} / {t.dtype}")
+            if tuple(t.shape) != tuple(shape):
+                raise ValueError(f"out: {name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+            if not t.is_contiguous():
+                raise ValueError(f"out: {name} must be contiguous")
+        return (out[: len(shapes)] + (None, None))[:3]
+
     def compute_raw(self, dtype, level, xyz_ptr, n_samples, sph_ptr, dsph_ptr=None, ddsph_ptr=None, stream=None):
         """Thin wrapper of ``*_try_compute``: device pointers in, work enqueued on ``stream``."""
         sfx = "" if dtype == torch.float64 else "_f"
@@ -96,7 +119,7 @@ class _BaseHarmonics:
             dsph = torch.empty((n, 3, ny), dtype=xyz.dtype, device=xyz.device) if level >= 1 else None
             ddsph = torch.empty((n, 3, 3, ny), dtype=xyz.dtype, device=xyz.device) if level >= 2 else None
         else:
-            sph, dsph, ddsph = (tuple(out) + (None, None))[:3]
+            sph, dsph, ddsph = self._validate_out(out, xyz, [(n, ny), (n, 3, ny), (n, 3, 3, ny)][: level + 1])
         stream = torch.cuda.current_stream(xyz.device).cuda_stream
         self.compute_raw(xyz.dtype, level, _ptr(xyz), n, _ptr(sph), _ptr(dsph), _ptr(ddsph), stream)
         return sph, dsph, ddsph
@@ -136,7 +159,8 @@ class _BaseHarmonics:
         if sph_grad.shape != (n, ny) or sph_grad.dtype != xyz.dtype or sph_grad.device != xyz.device:
             raise ValueError("sph_grad must match xyz in dtype and device and have shape (n_samples, (l_max+1)^2)")
         sph_grad = sph_grad.detach().contiguous()
-        xyz_grad = torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None else out
+        xyz_grad = (torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None
+                    else self._validate_out(out, xyz, [(n, 3)], names=("xyz_grad",))[0])
         stream = torch.cuda.current_stream(xyz.device).cuda_stream
         self.compute_vjp_raw(xyz.dtype, _ptr(xyz), n, _ptr(sph_grad), _ptr(xyz_grad), stream)
         return xyz_grad
@@ -155,7 +179,8 @@ class _BaseHarmonics:
                 raise ValueError("sph_grad must match xyz in dtype and device and have shape (n_samples, (l_max+1)^2)")
             sph_grad = sph_grad.detach().contiguous()
         dsph_grad = dsph_grad.detach().contiguous()
-        xyz_grad = torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None else out
+        xyz_grad = (torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None
+                    else self._validate_out(out, xyz, [(n, 3)], names=("xyz_grad",))[0])
         stream = torch.cuda.current_stream(xyz.device).cuda_stream
         sfx = "" if xyz.dtype == torch.float64 else "_f"
         status = getattr(self._lib, f"{self._prefix}_try_compute_vjp_with_gradients{sfx}")(

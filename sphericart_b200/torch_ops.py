@@ -178,25 +178,3 @@ def e3nn_spherical_harmonics(l_list, x: torch.Tensor, normalize: bool = False, n
     if normalization != "integral":
         sh = sh * torch.tensor(scales, dtype=sh.dtype, device=sh.device)
     return sh
-
-
-_E3NN_ORIGINAL = None
-
-
-def patch_e3nn(e3nn_module) -> None:
-    """Makes ``e3nn_module.o3.spherical_harmonics`` call :func:`e3nn_spherical_harmonics`
-    (reference: ``e3nn.py:86-103``)."""
-    global _E3NN_ORIGINAL
-    if _E3NN_ORIGINAL is not None:
-        raise RuntimeError("It appears that e3nn has already been patched")
-    _E3NN_ORIGINAL = e3nn_module.o3.spherical_harmonics
-    e3nn_module.o3.spherical_harmonics = e3nn_spherical_harmonics
-
-
-def unpatch_e3nn(e3nn_module) -> None:
-    """Restores the function :func:`patch_e3nn` replaced (reference: ``e3nn.py:106-116``)."""
-    global _E3NN_ORIGINAL
-    if _E3NN_ORIGINAL is None:
-        raise RuntimeError("It appears that e3nn has not been patched")
-    e3nn_module.o3.spherical_harmonics = _E3NN_ORIGINAL
-    _E3NN_ORIGINAL = None

@@ -145,3 +145,35 @@ def test_launch_rules(tmp_path):
     assert serves[(2, 4)] == 5 and serves[(2, 8)] == 4            # Hessians: also bounded by a 100 KB image
     assert serves[(3, 4)] == 20 and serves[(3, 8)] == 20          # VJP: two tiles of upstream rows per SM
     assert serves[(4, 4)] == 5 and serves[(4, 8)] == 5            # second-order VJP
+
+
+def test_out_buffers_are_validated_before_they_reach_a_kernel():
+    """The ``out=`` buffers of the Python front end go to the kernels as bare pointers; a wrong
+    count, device, dtype, shape or a non-contiguous tensor must be refused on the host."""
+    import pytest
+    import torch
+
+    from sphericart_b200.spherical_harmonics import _BaseHarmonics
+
+    check = _BaseHarmonics._validate_out
+    xyz = torch.zeros((5, 3), dtype=torch.float64)
+    shapes = [(5, 9), (5, 3, 9)]
+    good = (torch.empty((5, 9), dtype=torch.float64), torch.empty((5, 3, 9), dtype=torch.float64))
+    assert check(good, xyz, shapes, require_cuda=False) == (good[0], good[1], None)
+    assert check(good + (None,), xyz, shapes, require_cuda=False)[2] is None
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        check(good, xyz, shapes)                                          # CPU tensors never reach a kernel
+    with pytest.raises(ValueError, match="exactly 2"):
+        check(good[:1], xyz, shapes, require_cuda=False)                  # gradients asked for, one buffer given
+    with pytest.raises(ValueError, match="exactly 2"):
+        check(good + (torch.empty(1),), xyz, shapes, require_cuda=False)  # one buffer too many
+    with pytest.raises(ValueError, match="shape"):
+        check((good[0], torch.empty((5, 3, 8), dtype=torch.float64)), xyz, shapes, require_cuda=False)
+    with pytest.raises(ValueError, match="dtype"):
+        check((good[0].float(), good[1]), xyz, shapes, require_cuda=False)
+    with pytest.raises(ValueError, match="contiguous"):
+        check((torch.empty((9, 5), dtype=torch.float64).t(), good[1]), xyz, shapes, require_cuda=False)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        check(([1.0], good[1]), xyz, shapes, require_cuda=False)          # not a tensor at all
+    with pytest.raises(ValueError, match="xyz_grad"):
+        check(torch.empty((5, 4), dtype=torch.float64), xyz, [(5, 3)], names=("xyz_grad",), require_cuda=False)

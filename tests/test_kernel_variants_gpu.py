@@ -39,7 +39,9 @@ for normalized, dt, l_max, level, n in cases:
         worst[dt] = max(worst[dt], err)
     g = rng.standard_normal((n, (l_max + 1) ** 2)).astype(dtype)
     vj = calc.compute_vjp(t[1:], torch.from_numpy(g[1:]).cuda()).cpu().numpy()
-    _, dref, _ = oracle.port_compute(xyz[1:].astype(np.float64), l_max, normalized, 1)
+    x64 = xyz[1:].astype(np.float64)
+    _, dref, _ = oracle.ref_compute(x64, l_max, normalized, 1) if oracle.have_ref() else \
+        oracle.port_compute(x64, l_max, normalized, 1)
     ref = np.einsum("nak,nk->na", dref, g[1:].astype(np.float64))
     scale = np.einsum("nak,nk->na", np.abs(dref), np.abs(g[1:].astype(np.float64))).max(axis=1, keepdims=True)
     worst[dt] = max(worst[dt], float((np.abs(vj - ref) / scale).max()))

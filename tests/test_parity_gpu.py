@@ -384,3 +384,34 @@ def test_cuda_array_interface_inputs(sb):
         assert torch.equal(torch.as_tensor(a, device="cuda"), b)
     with pytest.raises(TypeError):
         calc.compute(xyz.cpu().numpy())
+
+
+def test_out_buffers_of_the_python_front_end(sb, oracle_mod):
+    """Caller-provided output tensors (``out=``): filled in place with the same results, and refused
+    when they do not match the call."""
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(31)
+    xyz_np = rng.standard_normal((100, 3))
+    xyz = torch.from_numpy(xyz_np).to(dev)
+    for cls, normalized in _classes(sb):
+        calc = cls(5)
+        out = (torch.empty((100, 36), dtype=torch.float64, device=dev),
+               torch.empty((100, 3, 36), dtype=torch.float64, device=dev))
+        sph, dsph = calc.compute_with_gradients(xyz, out=out)
+        assert sph.data_ptr() == out[0].data_ptr() and dsph.data_ptr() == out[1].data_ptr()
+        want = _reference(oracle_mod, xyz_np, 5, normalized, 1)
+        _assert_close(oracle_mod, [sph.cpu().numpy(), dsph.cpu().numpy()], want[:2], 5, np.float64, "out=")
+        g = torch.from_numpy(rng.standard_normal((100, 36))).to(dev)
+        buf = torch.empty((100, 3), dtype=torch.float64, device=dev)
+        assert calc.compute_vjp(xyz, g, out=buf).data_ptr() == buf.data_ptr()
+        assert torch.allclose(buf, torch.einsum("nak,nk->na", dsph, g), rtol=1e-11, atol=1e-12)
+        with pytest.raises(ValueError):
+            calc.compute_with_gradients(xyz, out=out[:1])
+        with pytest.raises(ValueError):
+            calc.compute(xyz, out=torch.empty((100, 35), dtype=torch.float64, device=dev))
+        with pytest.raises(ValueError):
+            calc.compute(xyz, out=torch.empty((100, 36), dtype=torch.float32, device=dev))
+        with pytest.raises(ValueError):
+            calc.compute(xyz, out=torch.empty((100, 36), dtype=torch.float64))
+        with pytest.raises(ValueError):
+            calc.compute_vjp(xyz, g, out=torch.empty((3, 100), dtype=torch.float64, device=dev).t())

@@ -182,7 +182,6 @@ def test_e3nn_conventions(ops):
     (reference: sphericart-torch/python/sphericart/torch/e3nn.py:10-80; its test compares with e3nn
     itself, which is not installed here, so the closed forms of l = 0, 1 stand in for it)."""
     import math
-    import types
 
     import sphericart_b200.torch_ops as sbt
 
@@ -202,13 +201,6 @@ def test_e3nn_conventions(ops):
     assert torch.equal(solid, ops.solid_harmonics(x[:, [2, 0, 1]], 2))
     comp.sum().backward()
     assert x.grad is not None and bool(torch.isfinite(x.grad).all())
-    fake = types.SimpleNamespace(o3=types.SimpleNamespace(spherical_harmonics="original"))
-    sbt.patch_e3nn(fake)
-    assert fake.o3.spherical_harmonics is sbt.e3nn_spherical_harmonics
-    with pytest.raises(RuntimeError):
-        sbt.patch_e3nn(fake)
-    sbt.unpatch_e3nn(fake)
-    assert fake.o3.spherical_harmonics == "original"
 
 
 def test_operators_record_into_a_cuda_graph(ops):

@@ -52,6 +52,13 @@ def test_no_alloc_entry_point_matches_regular_entry_point(oracle_mod):
         for a, b in zip(no_alloc, regular):
             err, bad = oracle_mod.scaled_error(a, b, l_max)
             assert bad == 0 and err <= TOL, (cls.__name__, l_max, n, err, bad)
+        # and directly against the CPU checker (the reference's own library where it was built)
+        xyz_np = xyz.cpu().numpy()
+        want = (oracle_mod.ref_compute(xyz_np, l_max, normalized, 1) if oracle_mod.have_ref()
+                else oracle_mod.port_compute(xyz_np, l_max, normalized, 1))
+        for a, b in zip(no_alloc, want[:2]):
+            err, bad = oracle_mod.scaled_error(a, b, l_max)
+            assert bad == 0 and err <= TOL, (cls.__name__, l_max, n, "against the CPU checker", err, bad)
 
 
 def test_no_alloc_entry_point_rejects_what_it_cannot_hold():
