@@ -23,9 +23,22 @@ _port = None
 _ref = None
 
 
+def reference_root():
+    """Where the reference's source tree is: ``$SPHERICART_REF``, else a checkout named
+    ``reference`` beside this repository; ``None`` when neither has the reference's headers (the
+    prebuilt files under ``oracle/_ref`` are then used as they are)."""
+    candidates = [os.environ.get("SPHERICART_REF"),
+                  os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for root in candidates:
+        if root and os.path.exists(os.path.join(root, "sphericart", "include", "templates.hpp")):
+            return os.path.abspath(root)
+    return None
+
+
 def build(quiet=True):
     """Compile the restatement (and the reference library when its sources are reachable)."""
-    out = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    ref = reference_root()
+    out = subprocess.run(["make", "-C", _HERE] + ([f"REF={ref}"] if ref else []), capture_output=True, text=True)
     if out.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + out.stdout + out.stderr)
     if not quiet:

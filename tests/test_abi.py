@@ -11,7 +11,13 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = os.path.join(ROOT, "include", "sphericart_b200.h")
-REFERENCE_HEADER_DIR = os.path.join(os.environ.get("SPHERICART_REF", "/root/reference"), "sphericart", "include")
+
+
+def _reference_header_dir():
+    from oracle import oracle
+
+    root = oracle.reference_root()
+    return None if root is None else os.path.join(root, "sphericart", "include")
 
 
 def _declared_functions():
@@ -57,8 +63,9 @@ def test_cxx_calculator_symbols_are_exported():
 def test_object_layout_matches_the_reference_header(tmp_path):
     """Bindings built against the reference header allocate the calculators themselves, so size and
     alignment must agree. Needs the reference checkout; skipped where it is absent."""
-    if not os.path.exists(os.path.join(REFERENCE_HEADER_DIR, "sphericart_cuda.hpp")):
-        pytest.skip("reference headers not available on this machine")
+    reference_header_dir = _reference_header_dir()
+    if reference_header_dir is None:
+        pytest.skip("reference headers not available on this machine (set SPHERICART_REF)")
     prog = r"""
 #include <cstdio>
 #include "sphericart_cuda.hpp"
@@ -71,7 +78,7 @@ int main() {
     src = tmp_path / "layout.cpp"
     src.write_text(prog)
     results = []
-    for inc in (os.path.join(ROOT, "include"), REFERENCE_HEADER_DIR):
+    for inc in (os.path.join(ROOT, "include"), reference_header_dir):
         exe = tmp_path / ("layout_" + str(len(results)))
         subprocess.run(["g++", "-std=c++17", "-I", inc, str(src), "-o", str(exe)], check=True)
         results.append(subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout)
@@ -147,3 +154,41 @@ def test_torch_operator_library_loads_and_serves_cuda_tensors_only():
         shapes = [tuple(o.shape) for o in t.ops.solid_harmonics_with_hessians(x, 4)]
         assert shapes == [(10, 25), (10, 3, 25), (10, 3, 3, 25)]
         assert tuple(t.ops.spherical_harmonics_vjp(x, torch.empty(10, 25, device="cuda"), 4).shape) == (10, 3)
+
+
+def test_gpulite_stand_in_compiles_and_checks(tmp_path):
+    """``include/gpulite/gpulite.hpp`` is what lets the reference's JAX binding
+    (sphericart-jax/src/sphericart_jax_cuda.cpp:15,83,127,177) compile against this library without
+    the run-time loader it normally uses: the macro passes a successful call through and turns a
+    failing one into an exception that names the error. Needs no GPU: the macro is given status
+    values directly."""
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    if not os.path.exists(os.path.join(cuda_home, "include", "cuda_runtime_api.h")):
+        pytest.skip("CUDA toolkit headers not found")
+    prog = r"""
+#include <gpulite/gpulite.hpp>
+#include <cstdio>
+#include <cstring>
+int main() {
+    cudaStream_t stream = nullptr;             // the types the binding uses come with the header
+    cudaPointerAttributes attributes;
+    (void)stream; (void)attributes;
+    int thrown = 0;
+    try {
+        GPULITE_CUDART_CALL(cudaErrorInvalidValue);   // any expression of type cudaError_t
+    } catch (const std::runtime_error& e) {
+        thrown = std::strstr(e.what(), "cudaErrorInvalidValue") != nullptr;
+    }
+    GPULITE_CUDART_CALL(cudaSuccess);
+    std::printf("%d\n", thrown);
+    return thrown ? 0 : 1;
+}
+"""
+    src = tmp_path / "shim.cpp"
+    src.write_text(prog)
+    exe = tmp_path / "shim"
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda_home, "include"),
+                    str(src), "-L", os.path.join(cuda_home, "lib64"), "-lcudart", "-o", str(exe)], check=True)
+    env = dict(os.environ, LD_LIBRARY_PATH=os.path.join(cuda_home, "lib64") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    out = subprocess.run([str(exe)], capture_output=True, text=True, env=env)
+    assert out.returncode == 0 and out.stdout.strip() == "1", out.stdout + out.stderr
