@@ -132,3 +132,45 @@ def test_device_follows_the_pointer(oracle_mod):
             for got, ref in zip((sph, dsph), want):
                 err, bad = oracle_mod.scaled_error(got.cpu().numpy(), ref, l_max)
                 assert bad == 0 and err <= 1e-12
+
+
+def test_threads_alternating_degrees_on_one_kernel(oracle_mod):
+    """Two calculators whose calls run the same kernel instantiation with different shared-memory
+    sizes (l_max = 12 and 14, float64 gradients), driven from several host threads at once: raising the
+    kernel's shared-memory limit for one must never break a launch of the other."""
+    import threading
+
+    import sphericart_b200 as sb
+
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(3)
+    xyz_np = rng.standard_normal((257, 3))
+    degrees = (12, 14)
+    calcs = {l: sb.SphericalHarmonics(l) for l in degrees}
+    want = {l: oracle_mod.port_compute(xyz_np, l, True, 1) for l in degrees}
+    errors, results = [], {}
+
+    def work(tid):
+        try:
+            torch.cuda.set_device(dev)
+            stream = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(stream):
+                xyz = torch.from_numpy(xyz_np).to(dev)
+                for it in range(20):
+                    l = degrees[(tid + it) % 2]
+                    out = calcs[l].compute_with_gradients(xyz)
+            stream.synchronize()
+            results[tid] = (l, out)
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(6)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for l, out in results.values():
+        for got, ref in zip(out, want[l]):
+            err, bad = oracle_mod.scaled_error(got.cpu().numpy(), ref, l)
+            assert bad == 0 and err <= 1e-12

@@ -1,7 +1,15 @@
-"""The benchmark configurations at their full sizes, checked through properties that need no
-CPU run: the addition theorem, Euler's homogeneity relation, the Laplacian, Hessian symmetry,
-the NaN mask of the origin points, and agreement of the fused VJP with the explicit contraction.
-All calls go through the C ABI."""
+"""The benchmark configurations at their full sizes.
+
+Two kinds of checks, all through the C ABI:
+* against the reference CPU library on every point: the GPU evaluates the configuration in one call,
+  as the benchmark does; the host walks the same points in chunks through the reference's CPU
+  calculator (the CPU restatement where the reference library was not built), each chunk's result is
+  uploaded and compared on the device with the stated tolerance (1e-5 float32 / 1e-12 float64 of the
+  largest |reference| in the same degree block of the same point, NaN positions equal);
+* through properties that need no CPU run: the addition theorem, Euler's homogeneity relation,
+  the Laplacian, Hessian symmetry, the NaN mask of the origin points, and agreement of the fused VJP
+  with the explicit contraction.
+"""
 
 import math
 
@@ -143,3 +151,123 @@ def test_config5_stress_full_size():
     tiny = (xyz.norm(dim=1) < 1e-5) & ~at_origin
     assert int(tiny.sum()) == 10000
     assert _radial_error(xyz[tiny], dsph[tiny], wl.l_max) < 1e-12
+
+
+# ---------------------------------------------------------------------------------------------
+# every point of every configuration against the reference CPU implementation
+
+TOL = {"f32": 1e-5, "f64": 1e-12}
+
+
+def _device_scaled_error(got, want, l_max):
+    """The comparator of the CPU tests (largest |got - want| over the largest |want| of the same
+    point and degree block, all derivative components together; NaN and infinity positions must
+    agree), evaluated on the device. got, want: (n, ..., ny). Returns (error, mismatched positions)."""
+    n, ny = want.shape[0], want.shape[-1]
+    g = got.reshape(n, -1, ny)
+    w = want.reshape(n, -1, ny)
+    bad = int((torch.isnan(g) != torch.isnan(w)).sum())
+    inf_w = torch.isinf(w)
+    bad += int((inf_w & (g != w)).sum()) + int((torch.isinf(g) & ~inf_w).sum())
+    finite = torch.isfinite(g) & torch.isfinite(w)
+    tiny = torch.finfo(want.dtype).tiny
+    worst = 0.0
+    for l in range(l_max + 1):
+        sl = slice(l * l, (l + 1) ** 2)
+        wb, gb, fb = w[:, :, sl].double(), g[:, :, sl].double(), finite[:, :, sl]
+        zero = torch.zeros((), dtype=torch.float64, device=w.device)
+        scale = torch.where(fb, wb.abs(), zero).amax(dim=(1, 2), keepdim=True).clamp_min(tiny)
+        worst = max(worst, float((torch.where(fb, (gb - wb).abs(), zero) / scale).max()))
+    return worst, bad
+
+
+def _cpu_checker(oracle_mod, wl):
+    """compute(xyz_chunk, level) -> (sph, dsph, ddsph) on the host with every core."""
+    oracle_mod.use_all_host_threads()
+    if oracle_mod.have_ref():
+        calc = oracle_mod.RefCalculator(wl.l_max, wl.normalized, wl.np_dtype)
+        return "reference CPU library", lambda xyz, level: calc.compute(xyz, level)
+    return "CPU restatement", lambda xyz, level: oracle_mod.port_compute(xyz, wl.l_max, wl.normalized, level, nthreads=0)
+
+
+def _compare_full_size(oracle_mod, config, chunk):
+    import sphericart_b200 as sb
+    from sphericart_b200 import workloads
+
+    wl, _ = workloads.CONFIGS[config]
+    xyz_host = workloads.make_points(config)
+    n = xyz_host.shape[0]
+    assert n == wl.n_points
+    xyz = torch.from_numpy(xyz_host).to(DEV)
+    calc = (sb.SphericalHarmonics if wl.normalized else sb.SolidHarmonics)(wl.l_max)
+    got = calc._compute_impl(xyz, wl.level)              # one call over the whole configuration
+    torch.cuda.synchronize()
+    kind, cpu = _cpu_checker(oracle_mod, wl)
+    worst = [0.0, 0.0, 0.0]
+    mismatched = 0
+    nan_rows = 0
+    for lo in range(0, n, chunk):
+        hi = min(n, lo + chunk)
+        want = cpu(xyz_host[lo:hi], wl.level)
+        for i in range(wl.level + 1):
+            w = torch.from_numpy(want[i]).to(DEV)
+            err, bad = _device_scaled_error(got[i][lo:hi], w, wl.l_max)
+            worst[i] = max(worst[i], err)
+            mismatched += bad
+            if i == 0:
+                nan_rows += int(torch.isnan(w).any(dim=1).sum())
+            del w
+    print(f"\n[{config}: {n} points against the {kind}] largest scaled error sph {worst[0]:.3e}, "
+          f"dsph {worst[1]:.3e}, ddsph {worst[2]:.3e}; NaN/inf mismatches {mismatched}; rows with NaN {nan_rows}")
+    assert mismatched == 0
+    assert max(worst) <= TOL[wl.dtype], worst
+    return nan_rows
+
+
+def test_config2_every_point_against_the_reference(oracle_mod):
+    _compare_full_size(oracle_mod, "cfg2", 1 << 20)
+
+
+def test_config3_every_point_against_the_reference(oracle_mod):
+    _compare_full_size(oracle_mod, "cfg3", 1 << 16)
+
+
+def test_config5_every_point_against_the_reference(oracle_mod):
+    # 1,000 of the points sit exactly at the origin: their rows are NaN (except Y_00) on both sides
+    assert _compare_full_size(oracle_mod, "cfg5", 1 << 15) == 1000
+
+
+def test_config4_every_point_against_the_reference(oracle_mod):
+    """Forward values and the fused VJP of all 5e7 points. The reference's backward is the gradients
+    call followed by a product and a sum over the (l, m) axis
+    (sphericart-torch/python/sphericart/torch/register.py:98-99); here the reference's float32
+    gradients are contracted on the device in float64, which bounds the reduction-order noise, and the
+    fused result must agree within 1e-5 of sum_k |g_k| |dY_k| (the scale of the terms that are summed)."""
+    import sphericart_b200 as sb
+    from sphericart_b200 import workloads
+
+    wl, _ = workloads.CONFIGS["cfg4"]
+    xyz_host = workloads.make_points("cfg4")
+    g_host = workloads.make_upstream_grad("cfg4")
+    n = xyz_host.shape[0]
+    xyz = torch.from_numpy(xyz_host).to(DEV)
+    g = torch.from_numpy(g_host).to(DEV)
+    calc = sb.SphericalHarmonics(wl.l_max)
+    sph = calc.compute(xyz)
+    fused = calc.compute_vjp(xyz, g)
+    torch.cuda.synchronize()
+    kind, cpu = _cpu_checker(oracle_mod, wl)
+    worst_y, worst_v, mismatched = 0.0, 0.0, 0
+    chunk = 1 << 20
+    for lo in range(0, n, chunk):
+        hi = min(n, lo + chunk)
+        want_sph, want_dsph, _ = cpu(xyz_host[lo:hi], 1)
+        err, bad = _device_scaled_error(sph[lo:hi], torch.from_numpy(want_sph).to(DEV), wl.l_max)
+        worst_y, mismatched = max(worst_y, err), mismatched + bad
+        d = torch.from_numpy(want_dsph).to(DEV).double()
+        gd = g[lo:hi].double()
+        ref = torch.einsum("nak,nk->na", d, gd)
+        scale = torch.einsum("nak,nk->na", d.abs(), gd.abs()).amax(dim=1, keepdim=True).clamp_min(1e-30)
+        worst_v = max(worst_v, float(((fused[lo:hi].double() - ref).abs() / scale).max()))
+    print(f"\n[cfg4: {n} points against the {kind}] largest scaled error sph {worst_y:.3e}, fused VJP {worst_v:.3e}")
+    assert mismatched == 0 and worst_y <= 1e-5 and worst_v <= 1e-5
