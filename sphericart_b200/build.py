@@ -40,6 +40,7 @@ def _units():
             units.append((f"tile_{tname}_l{l}.o", "tile_inst.cu", [f"-DSPH_T={t}", f"-DSPH_LMAX={l}"]))
         for g in (1, 2, 4, 8, 16, 32):
             units.append((f"band_{tname}_g{g}.o", "band_inst.cu", [f"-DSPH_T={t}", f"-DSPH_G={g}"]))
+            units.append((f"panel_{tname}_p{g}.o", "panel_inst.cu", [f"-DSPH_T={t}", f"-DSPH_TP={g}"]))
     return units
 
 

@@ -105,6 +105,26 @@ template <typename T> struct BandLaunchArgs {
     int iters;     // see work_grid()
 };
 
+// Panel kernels, run-time l_max, forward levels only. TP points per CTA, threads / TP slices per point.
+template <typename T> struct PanelLaunchArgs {
+    const T* xyz;
+    long long n;
+    T* sph;
+    T* dsph;
+    T* ddsph;
+    const T* d_tables;   // F then K
+    const void* d_desc;  // the per-pair descriptors (PanelDesc in sph_panel.cuh)
+    int l_max;
+    int bulk;            // 1: TMA bulk copy-out, 0: plain stores
+    int threads;         // threads per CTA (a multiple of TP)
+    size_t smem;
+    int iters;           // panels per CTA, see work_grid()
+};
+
+template <typename T, int TP> struct PanelLaunch {
+    static cudaError_t run(int level, bool normalized, const PanelLaunchArgs<T>& a, int device, cudaStream_t stream);
+};
+
 template <typename T, int G> struct BandLaunch {
     // level 0..2 forward; vjp with level 1: first-order VJP, with level 2: VJP of (values, gradients)
     static cudaError_t run(int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,

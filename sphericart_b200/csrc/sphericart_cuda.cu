@@ -46,6 +46,10 @@ struct Knobs {
     int band_iters;     // the same for the band kernels
     int tile_points;    // force the points per tile of the forward tile kernels (8, 16 or 32)
     int tile_lmax;      // largest l_max served by the tile kernels (default: all they are compiled for)
+    int no_panel;       // route what the panel kernels would serve to the band kernel
+    int panel_points;   // force the points per panel (1, 2, 4, 8, 16 or 32)
+    int panel_threads;  // force the threads per CTA of the panel kernels (a multiple of the points, <= 256)
+    int panel_iters;    // panels per CTA of the panel kernels (k > 0), -1: persistent launch
 };
 
 int env_int(const char* name, int fallback) {
@@ -60,7 +64,9 @@ const Knobs& knobs() {
                             env_int("SPH_B200_NO_BULK", 0),     env_int("SPH_B200_BAND_DIRECT", 0),
                             env_int("SPH_B200_TILE_ITERS", 0),  env_int("SPH_B200_VJP_ITERS", 0),
                             env_int("SPH_B200_BAND_ITERS", 0),  env_int("SPH_B200_TILE_POINTS", 0),
-                            env_int("SPH_B200_TILE_LMAX", TILE_LMAX)};
+                            env_int("SPH_B200_TILE_LMAX", TILE_LMAX), env_int("SPH_B200_NO_PANEL", 0),
+                            env_int("SPH_B200_PANEL_POINTS", 0), env_int("SPH_B200_PANEL_THREADS", 0),
+                            env_int("SPH_B200_PANEL_ITERS", 0)};
     return k;
 }
 
@@ -271,13 +277,120 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
     return plan;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Panel-kernel plan: points per panel (TP), threads per CTA, shared-memory size. The sizes restate
+// panel_const_bytes / panel_state_bytes / panel_image_bytes of sph_panel.cuh for a run-time element size.
+struct PanelPlan {
+    int tp = 0;        // points per panel
+    int threads = 0;   // threads per CTA; threads / tp slices share each point
+    size_t smem = 0;   // dynamic shared memory per CTA
+    int iters = 0;     // panels per CTA (see work_grid() in sph_launch.hpp)
+    bool feasible = false;
+};
+
+constexpr int PANEL_LMAX = 200;  // the descriptors hold l and m in 8 bits and the column in 16
+
+size_t panel_smem_bytes(int l_max, int level, int tp, size_t elem) {
+    const size_t ny = size_t(n_columns(l_max));
+    const size_t nq = size_t(n_table(l_max));
+    const size_t slack = 16 / elem;
+    const size_t consts = band_align16(2 * nq, elem) * elem + nq * 16;
+    const size_t state = band_align16(size_t(tp) * (2 * size_t(l_max + 3) + size_t(4 + (l_max + 1) * l_max / 2 + 5 * (l_max + 1))), elem) * elem;
+    size_t image = band_align16(size_t(tp) * ny, elem) + slack;
+    if (level >= 1) image += band_align16(size_t(tp) * 3 * ny, elem) + slack;
+    if (level >= 2) image += band_align16(size_t(tp) * 9 * ny, elem) + slack;
+    return consts + state + image * elem;
+}
+
+// Chooses the panel shape. What is weighed: warps per SM (latency hiding; beyond about twenty the
+// register file is the limit anyway), how evenly the pairs divide among the slices of a point
+// (a slice evaluates ceil(pairs / slices) pairs), and at least three CTAs per SM so that some compute
+// while the images of others drain through the TMA engine. Ties go to the larger panel (fewer,
+// larger bulk stores).
+PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit) {
+    PanelPlan best;
+    if (l_max > PANEL_LMAX) return best;
+    const int nq = n_table(l_max);
+    const int forced_tp = knobs().panel_points;
+    const int forced_threads = knobs().panel_threads;
+    double best_score = -1.0;
+    for (int tp = 32; tp >= 1; tp /= 2) {
+        if (forced_tp > 0 && tp != forced_tp) continue;
+        const size_t smem = panel_smem_bytes(l_max, level, tp, elem);
+        if (smem > smem_limit) continue;
+        for (int threads = 64; threads <= 256; threads += 32) {
+            if (forced_threads > 0 && threads != forced_threads) continue;
+            if (threads % tp != 0) continue;
+            const int slices = threads / tp;
+            if (slices > nq && forced_threads <= 0) continue;
+            // resident CTAs per SM: shared memory (228 KB, 1 KB reserved per CTA), threads, registers (about 96 per thread)
+            long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
+            ctas = std::min<long long>(ctas, 2048 / threads);
+            ctas = std::min<long long>(ctas, 65536 / (96 * threads));
+            if (ctas < 1) continue;
+            const double warps = double(ctas * threads / 32);
+            const double per_slice = double(nq) / slices;
+            const double balance = per_slice / std::ceil(per_slice);
+            const double overlap = ctas >= 3 ? 1.0 : (ctas == 2 ? 0.85 : 0.5);
+            const double score = std::floor(1000.0 * std::min(warps, 20.0) / 20.0 * balance * overlap);
+            if (score > best_score) {
+                best_score = score;
+                best.tp = tp;
+                best.threads = threads;
+                best.smem = smem;
+                best.feasible = true;
+            }
+        }
+    }
+    // Each CTA stages the tables and descriptors once; a few panels per CTA amortise that.
+    best.iters = resolve_iters(knobs().panel_iters, 4);
+    return best;
+}
+
+// Descriptors of the (l, m >= 0) pairs for the panel kernels (PanelDesc in sph_panel.cuh): element
+// offsets of Q_l^m, Q_{l-1}^m, Q_{l-2}^m in the triangular per-point table (rows -1 and -2 are the
+// block of zeros at offset 0), and column | m << 16 | l << 24.
+void make_panel_desc(int l_max, int* out) {
+    auto row_start = [](int l) { return 4 + l * (l - 1) / 2 + 5 * l; };
+    for (int l = 0; l <= l_max; ++l) {
+        for (int m = 0; m <= l; ++m) {
+            int* d = out + 4 * tri(l, m);
+            d[0] = row_start(l) + m;
+            d[1] = (l >= 1 ? row_start(l - 1) : 0) + m;
+            d[2] = (l >= 2 ? row_start(l - 2) : 0) + m;
+            d[3] = (l * l + l + m) | (m << 16) | (l << 24);
+        }
+    }
+}
+
 // Library-owned state of one calculator, reached through the class's prefactors_cuda slot.
 template <typename T> struct CalculatorState {
     std::mutex mutex;
     BandPlan plans[5];
     bool plan_ready[5] = {false, false, false, false, false};
-    T* tables[MAX_DEVICES] = {};  // device copies of the F and K tables, made on first use per device
+    PanelPlan panel_plans[3];
+    bool panel_plan_ready[3] = {false, false, false};
+    // device copies of the F and K tables followed (from the next 16-byte boundary) by the panel
+    // kernels' pair descriptors, made on first use per device
+    T* tables[MAX_DEVICES] = {};
 };
+
+template <typename T> size_t desc_offset_bytes(int l_max) { return band_align16(2 * size_t(n_table(l_max)), sizeof(T)) * sizeof(T); }
+
+// Uploads the calculator's tables to `device` on first use (under the calculator's mutex).
+template <typename T> const T* device_tables(CalculatorState<T>& st, const T* host_tables, int l_max, int device) {
+    if (st.tables[device] == nullptr) {
+        const size_t nq = size_t(n_table(l_max));
+        const size_t desc_at = desc_offset_bytes<T>(l_max);
+        const bool with_desc = l_max <= PANEL_LMAX;
+        std::vector<unsigned char> staging(desc_at + (with_desc ? nq * 16 : 0), 0);
+        std::memcpy(staging.data(), host_tables, 2 * nq * sizeof(T));
+        if (with_desc) make_panel_desc(l_max, reinterpret_cast<int*>(staging.data() + desc_at));
+        check(cudaMalloc(reinterpret_cast<void**>(&st.tables[device]), staging.size()), "cudaMalloc(prefactors)");
+        check(cudaMemcpy(st.tables[device], staging.data(), staging.size(), cudaMemcpyHostToDevice), "cudaMemcpy(prefactors)");
+    }
+    return st.tables[device];
+}
 
 template <typename T>
 void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int kind, int device, size_t smem_limit,
@@ -287,13 +400,20 @@ void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int
         st.plans[kind] = make_band_plan(l_max, kind, sizeof(T), smem_limit, sm_count);
         st.plan_ready[kind] = true;
     }
-    if (st.tables[device] == nullptr) {
-        const size_t bytes = 2 * size_t(n_table(l_max)) * sizeof(T);
-        check(cudaMalloc(reinterpret_cast<void**>(&st.tables[device]), bytes), "cudaMalloc(prefactors)");
-        check(cudaMemcpy(st.tables[device], host_tables, bytes, cudaMemcpyHostToDevice), "cudaMemcpy(prefactors)");
-    }
     plan = &st.plans[kind];
-    d_tables = st.tables[device];
+    d_tables = device_tables(st, host_tables, l_max, device);
+}
+
+template <typename T>
+void panel_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int level, int device, size_t smem_limit,
+                     const PanelPlan*& plan, const T*& d_tables) {
+    std::lock_guard<std::mutex> lock(st.mutex);
+    if (!st.panel_plan_ready[level]) {
+        st.panel_plans[level] = make_panel_plan(l_max, level, sizeof(T), smem_limit);
+        st.panel_plan_ready[level] = true;
+    }
+    plan = &st.panel_plans[level];
+    d_tables = plan->feasible ? device_tables(st, host_tables, l_max, device) : nullptr;
 }
 
 template <typename T>
@@ -387,6 +507,19 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return flag;
     }
 };
+
+template <typename T>
+cudaError_t panel_dispatch(int tp, int level, bool normalized, const PanelLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    switch (tp) {
+        case 1: return PanelLaunch<T, 1>::run(level, normalized, a, device, stream);
+        case 2: return PanelLaunch<T, 2>::run(level, normalized, a, device, stream);
+        case 4: return PanelLaunch<T, 4>::run(level, normalized, a, device, stream);
+        case 8: return PanelLaunch<T, 8>::run(level, normalized, a, device, stream);
+        case 16: return PanelLaunch<T, 16>::run(level, normalized, a, device, stream);
+        case 32: return PanelLaunch<T, 32>::run(level, normalized, a, device, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
 
 template <typename T>
 cudaError_t band_dispatch(int lanes, int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
@@ -487,6 +620,29 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             check(TileDispatch<T>::forward(l_max, kind, normalized, xyz, n, sph, dsph, ddsph, host_tables, warps,
                                            span_tiles, use_bulk, iters, tile_points, scope.device, stream),
                   "tile kernel launch");
+            return;
+        }
+    }
+
+    if (kind <= 2 && knobs().no_panel == 0 && !force_band) {
+        const PanelPlan* pplan = nullptr;
+        const T* d_tables = nullptr;
+        panel_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, pplan, d_tables);
+        if (pplan->feasible) {
+            PanelLaunchArgs<T> a{};
+            a.xyz = xyz;
+            a.n = n;
+            a.sph = sph;
+            a.dsph = dsph;
+            a.ddsph = ddsph;
+            a.d_tables = d_tables;
+            a.d_desc = reinterpret_cast<const unsigned char*>(d_tables) + desc_offset_bytes<T>(l_max);
+            a.l_max = l_max;
+            a.bulk = knobs().no_bulk != 0 ? 0 : 1;
+            a.threads = pplan->threads;
+            a.smem = pplan->smem;
+            a.iters = pplan->iters;
+            check(panel_dispatch<T>(pplan->tp, kind, normalized, a, scope.device, stream), "panel kernel launch");
             return;
         }
     }

@@ -1,6 +1,7 @@
 """Parity of the kernel variants that the default dispatch does not reach on every input: the
-run-time-degree kernel for low degrees, its plain-store and direct-store copy-out modes, forced
-lane counts, the tile kernels without TMA, and persistent launches against grids of short-lived CTAs. The variants are selected by the library's
+run-time-degree kernels (panel and band) for low degrees, their plain-store and direct-store copy-out
+modes, forced lane counts and panel shapes, the tile kernels without TMA, and persistent launches
+against grids of short-lived CTAs. The variants are selected by the library's
 development environment variables, which are read once per process, so each runs in a child
 process that prints its worst scaled error against the CPU checker."""
 
@@ -68,8 +69,16 @@ VARIANTS = [
     {"SPH_B200_TILE_POINTS": "8"},
     {"SPH_B200_TILE_POINTS": "16", "SPH_B200_TILE_ITERS": "-1"},
     {"SPH_B200_TILE_POINTS": "32"},
-    # the band kernel for every degree the tile kernels would otherwise take above l_max = 2
+    # every degree above l_max = 2 through the run-time-degree kernels: the panel kernels (forward) ...
     {"SPH_B200_TILE_LMAX": "2"},
+    # ... and the band kernel alone
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_NO_PANEL": "1"},
+    {"SPH_B200_NO_PANEL": "1"},
+    # panel shapes the plan picks only for some degrees: one point per CTA (unaligned spans), many points
+    # per CTA, persistent launch, plain-store copy-out
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "1", "SPH_B200_PANEL_THREADS": "96"},
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "32", "SPH_B200_PANEL_THREADS": "64", "SPH_B200_PANEL_ITERS": "-1"},
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "4", "SPH_B200_NO_BULK": "1"},
 ]
 
 
