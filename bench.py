@@ -9,7 +9,10 @@ Workload: the case the headline metric is quoted on - SphericalHarmonics (normal
 float32, values + gradients, 4,194,304 points per GPU drawn iid N(0,1) per coordinate (seed 1000 +
 rank). One step = one pass of the kernel over the rank's points. Points are independent, so ranks
 share nothing: no collective is on the data path (NCCL is used only for the barrier around the
-timed region and to take the maximum time over ranks); scaling is weak.
+timed region and to take the maximum time over ranks). Scaling is weak by default (every rank has the
+workload's full point count); ``--scaling strong`` fixes the total (8 x 4,194,304 points for the
+headline case, the configuration's own size otherwise) and gives rank r the contiguous shard
+``workloads.shard_bounds(total, world, r)``.
 
 Prints ONE JSON line on rank 0.
 """
@@ -43,22 +46,27 @@ def _peaks():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-# DRAM bytes per launch of the timed kernel, from the ncu capture summarised in
-# profiles/sph_tile_kernel_f32_l8_gradients.md: 627.0 MB (dram__bytes_read.sum + dram__bytes_write.sum)
-# for a 524,288-point launch. Traffic grows in proportion to the points; the workload is
-# 4,194,304 points per GPU, i.e. 8x.
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one step's kernel(s), from ncu captures of
+# a launch of `points` points of the same kernel(s); the commands and counters are in the summaries
+# under profiles/. A capture of the full workload would break the profiler's size rule, so the figure
+# for n points is the captured bytes plus the algorithmic bytes of the n - `points` further points:
+# what separates captured from algorithmic bytes is written data still resident in the 126 MB L2 when
+# the kernel ends, a constant that does not grow with the launch.
 NCU_TRAFFIC = {
-    "spherical_l8_f32_grad": {"points": 524288, "dram_bytes": 627.0e6,
-                              "note": "ncu capture of a 524288-point launch scaled by points; about 60 MB of "
-                                      "written data is still in L2 at kernel end, so traffic < algorithmic bytes"},
+    "spherical_l8_f32_grad": {"points": 524288, "dram_bytes": 627.0e6},
+    "solid_l6_f32_grad_n1e6": {"points": 1000000, "dram_bytes": 737.5e6},
+    "spherical_l4_f32_fwd_vjp_n5e7": {"points": 4194304, "dram_bytes": 412.3e6 + 514.0e6},
 }
 
 
-def _recorded_traffic(workload_name, n_points):
-    entry = NCU_TRAFFIC.get(workload_name)
-    if entry is None:
+def _recorded_traffic(wl, n_points, bytes_per_point):
+    entry = NCU_TRAFFIC.get(wl.name)
+    if entry is None or n_points < entry["points"]:
         return None
-    return {"dram_bytes_per_launch": entry["dram_bytes"] * n_points / entry["points"], "note": entry["note"]}
+    return {"dram_bytes_per_launch": entry["dram_bytes"] + bytes_per_point * (n_points - entry["points"]),
+            "note": f"ncu capture of a {entry['points']}-point launch ({entry['dram_bytes'] / 1e6:.1f} MB) plus the "
+                    f"algorithmic bytes of the other {n_points - entry['points']} points; the shortfall against the "
+                    "algorithmic bytes is written data still in L2 at kernel end"}
 
 
 class ClockSampler(threading.Thread):
@@ -155,6 +163,16 @@ def reduce_sum(value, world, device=None):
     return float(t.item())
 
 
+def _cpu_build_flags():
+    """How the reference CPU library under oracle/_ref was compiled (recorded by oracle/Makefile). It
+    travels between machines, so it targets a portable instruction set rather than the host's own."""
+    try:
+        with open(os.path.join(ROOT, "oracle", "_ref", "build_flags.txt")) as f:
+            return f.read().strip()
+    except OSError:
+        return "unknown flags"
+
+
 def cpu_reference_rate(wl, sample_points, seconds_budget=12.0, min_reps=3, max_reps=40):
     """Times the reference's CPU path (or the restatement when the reference library is not
     there) on ``sample_points`` points of the workload with all host threads.
@@ -222,7 +240,7 @@ def run_reference_arm(args):
     elapsed = time.perf_counter() - t0
     value = sample * args.steps / elapsed
     sample_text = (f"{sample} points of the workload per step (seed 1000), reference CPU library via its C API, "
-                   f"OpenMP threads = {cores}" if kind == "reference" else
+                   f"built with `{_cpu_build_flags()}`, OpenMP threads = {cores}" if kind == "reference" else
                    f"{sample} points per step, CPU restatement (reference library not built on this machine)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": args.gpus,
@@ -247,6 +265,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU gets the workload's full point count; strong: the total is fixed "
+                         "(8 x 4,194,304 points for the headline case, the configuration's size otherwise) and sharded")
     ap.add_argument("--config", default="metric", choices=sorted(workloads.CONFIGS),
                     help="metric = the headline case; cfg1..cfg5 = the other benchmark configurations")
     args = ap.parse_args()
@@ -270,10 +291,20 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     wl, _ = workloads.CONFIGS[args.config]
-    n = args.points or wl.n_points
     warmup = max(args.warmup, 3)
     tdtype = torch.float64 if wl.dtype == "f64" else torch.float32
-    xyz_host = torch.from_numpy(workloads.make_points(args.config, n_points=n, seed_offset=rank))
+    strong = args.scaling == "strong"
+    if strong:
+        # one point set of fixed size for any number of GPUs, cut into contiguous shards
+        total = args.points or (8 * wl.n_points if args.config == "metric" else wl.n_points)
+        lo, hi = workloads.shard_bounds(total, world, rank)
+        n = hi - lo
+        if n == 0:
+            raise SystemExit("strong scaling: the point set is too small for this many GPUs")
+        xyz_host = torch.from_numpy(workloads.make_points(args.config, n_points=total)[lo:hi].copy())
+    else:
+        n = args.points or wl.n_points
+        xyz_host = torch.from_numpy(workloads.make_points(args.config, n_points=n, seed_offset=rank))
     xyz = xyz_host.to(device)
     calc = (sphericart_b200.SphericalHarmonics if wl.normalized else sphericart_b200.SolidHarmonics)(wl.l_max)
     ny = wl.ny
@@ -282,7 +313,10 @@ def main():
     ddsph = torch.empty((n, 3, 3, ny), dtype=tdtype, device=device) if wl.level >= 2 else None
     sph_grad = xyz_grad = None
     if wl.vjp:
-        sph_grad = torch.from_numpy(workloads.make_upstream_grad(args.config, n_points=n, seed_offset=rank)).to(device)
+        grad_host = (workloads.make_upstream_grad(args.config, n_points=total)[lo:hi] if strong
+                     else workloads.make_upstream_grad(args.config, n_points=n, seed_offset=rank))
+        sph_grad = torch.from_numpy(grad_host).to(device)
+        del grad_host
         xyz_grad = torch.empty((n, 3), dtype=tdtype, device=device)
     stream = torch.cuda.current_stream(device)
     ptr = lambda t: None if t is None else t.data_ptr()  # noqa: E731
@@ -363,11 +397,28 @@ def main():
             pipe.run(xyz_pin, [sph_pin, dsph_pin])
         e1.record(stream)
         torch.cuda.synchronize(device)
-        e2e_ms = reduce_max(e0.elapsed_time(e1), world, device)
+        my_e2e_ms = e0.elapsed_time(e1)
+        e2e_ms = reduce_max(my_e2e_ms, world, device)
         bi, bo = pipe.bytes_per_point()
+        # the link's own rate, measured here: one large device-to-host copy into the same pinned array
+        # (this rank alone is timed; with several GPUs the ranks copy at the same time, as in the pipeline)
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dsph_pin.copy_(dsph, non_blocking=True)
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        c0.record(stream)
+        dsph_pin.copy_(dsph, non_blocking=True)
+        c1.record(stream)
+        torch.cuda.synchronize(device)
+        d2h_gbs = dsph.numel() * dsph.element_size() / (c0.elapsed_time(c1) * 1e-3) / 1e9
+        my_d2h_gbs = bo * n * e2e_steps / (my_e2e_ms * 1e-3) / 1e9
         e2e = {"value": total_points * e2e_steps / (e2e_ms * 1e-3), "unit": "points/s",
                "h2d_bytes_per_step": int(bi * total_points), "d2h_bytes_per_step": int(bo * total_points),
                "steps": e2e_steps,
+               "d2h_link_gbs": d2h_gbs, "d2h_achieved_gbs": my_d2h_gbs, "pcie_frac": my_d2h_gbs / d2h_gbs,
+               "pcie_note": "rank 0: device-to-host bytes of the pipeline / its time, over the rate of one large "
+                            "pinned device-to-host copy measured in this run; 1.0 = the link is the bound",
                "path": "HostPipeline: pinned host xyz -> H2D -> kernel -> D2H of sph and dsph into pinned host "
                        "arrays, 3 streams, 262144-point chunks; bound by PCIe device-to-host bandwidth"}
         del sph_pin, dsph_pin
@@ -380,14 +431,20 @@ def main():
     peak, peak_kind = _peaks()
     bytes_per_launch = out_bytes
     achieved = bytes_per_launch / (my_ms / args.steps * 1e-3) / 1e9
-    traffic = _recorded_traffic(wl.name, n)
-    kernel = ("sph_tile_kernel" if wl.l_max <= 8 else "sph_band_kernel") + \
-        f"<{'double' if wl.dtype == 'f64' else 'float'}, l_max={wl.l_max}, level={wl.level}>" + \
-        (" + fused VJP kernel" if wl.vjp else "")
+    traffic = _recorded_traffic(wl, n, step_bytes_per_point)
+    # the kernel names come from the library's own dispatch rule, not from a guess made here
+    from sphericart_b200 import _c_lib
+
+    ctype = "double" if wl.dtype == "f64" else "float"
+    kernel = f"{_c_lib.kernel_family(wl.level, wl.l_max, elem)}<{ctype}, l_max={wl.l_max}, level={wl.level}>"
+    if wl.vjp:
+        kernel += f" + {_c_lib.kernel_family(3, wl.l_max, elem)}<{ctype}, l_max={wl.l_max}>"
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": (traffic or {}).get("dram_bytes_per_launch"),
                 "peak_source": f"of {peak_kind}", "kernel": kernel,
                 "algorithmic_bytes_per_launch": bytes_per_launch,
+                "frac_basis": "algorithmic bytes per launch / CUDA-event time per launch, over a copy (read + write) "
+                              "bandwidth: a store-only kernel can read above 1.0",
                 "traffic_note": (traffic or {}).get("note")}
 
     cpu = None
@@ -395,13 +452,15 @@ def main():
         sample = 1 << 21
         rate, kind, cores, reps, sec = cpu_reference_rate(wl, sample)
         cpu = {"value": rate, "unit": "points/s", "cores": cores, "kind": kind,
-               "sample": f"first {sample} points of the workload (seed 1000), median of {reps} passes of "
+               "sample": f"first {sample} points of the workload (seed 1000), {kind} CPU code"
+                         + (f" built with `{_cpu_build_flags()}`" if kind == "reference" else "")
+                         + f", {cores} OpenMP threads, median of {reps} passes of "
                          f"{sec * 1e3:.1f} ms after 2 warm-up passes, preallocated outputs"}
 
     line = {
         "metric": METRIC if args.config == "metric" else f"points/sec, {wl.name}",
         "value": value, "unit": "points/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
         "config": {"workload": wl.name, "class": "SphericalHarmonics" if wl.normalized else "SolidHarmonics",
                    "l_max": wl.l_max,
@@ -412,7 +471,10 @@ def main():
                                  if flush is None else
                                  "small outputs: a 256 MB buffer is rewritten between timed steps to flush L2, "
                                  "each step timed with its own event pair"),
-                   "parallelism": f"points sharded over {world} GPU(s), no collective"},
+                   "total_points": int(total_points),
+                   "parallelism": (f"one point set of {int(total_points)} points cut into {world} contiguous shard(s), "
+                                   "no collective" if strong else
+                                   f"{n} points per GPU on {world} GPU(s), no collective")},
         "roofline": roofline, "cpu_baseline": cpu, "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e,
         "gpu_launches": timed_launches,
     }

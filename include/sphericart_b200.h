@@ -136,6 +136,13 @@ SPHERICART_EXPORT void sphericart_cuda_solid_harmonics_compute_array_with_hessia
  * *_new (empty string if none). The pointer stays valid until the thread's next failing call. */
 SPHERICART_EXPORT const char* sphericart_cuda_last_error(void);
 
+/* No counterpart in the reference. Name of the kernel family that serves a call on a B200:
+ * kind 0, 1, 2 = values, + gradients, + Hessians; 3 = fused VJP; 4 = fused second-order VJP;
+ * elem_bytes 4 (float) or 8 (double). Returns "sph_tile_kernel", "sph_vjp_tile_kernel",
+ * "sph_vjp2_tile_kernel", "sph_panel_kernel" or "sph_band_kernel" (a static string; "" for arguments
+ * out of range). Launches nothing; benchmarks and profiles use it to label what they time. */
+SPHERICART_EXPORT const char* sphericart_cuda_kernel_family(int kind, size_t l_max, int elem_bytes);
+
 /* The kernels' only waits are on their own asynchronous copies and are bounded; a wait that ever
  * gave up records it on the device. Returns 1 if that happened on the current device since the
  * library was loaded, 0 if not, -1 if the flags could not be read. Synchronises the device. */
@@ -260,6 +267,78 @@ SPHERICART_EXPORT void sphericart_cuda_solid_harmonics_compute_vjp_with_gradient
 SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_try_compute_vjp_with_gradients_f(
     sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const float* sph_grad, const float* dsph_grad, float* xyz_grad,
     void* cuda_stream);
+
+/* No counterpart in the reference's C API. Values of selected degree blocks of the spherical (normalised) harmonics
+ * only, packed, scaled and with the input axes permuted, in one pass (what the reference's e3nn adaptor,
+ * sphericart-torch/python/sphericart/torch/e3nn.py:47-80, composes from a full evaluation, a slice, a
+ * permutation and a multiplication). l_list: n_l distinct degrees <= l_max, HOST pointer, in output order;
+ * out: n_samples x sum(2l+1), device pointer; axis_order: 3 HOST ints, the input columns holding x, y, z
+ * (NULL: 0, 1, 2); scales: n_l HOST factors (NULL: 1). Needs l_max <= 20. Returns 0 on success, otherwise
+ * non-zero with the message in sphericart_cuda_last_error(). */
+SPHERICART_EXPORT int sphericart_cuda_spherical_harmonics_compute_selected(
+    sphericart_cuda_spherical_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const double* scales, double* out, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Fused vector-Jacobian product of compute_selected:
+ * out_grad is n_samples x sum(2l+1) in the packed layout, xyz_grad n_samples x 3 in the caller's axis
+ * order (device pointers); gradients of the harmonics are never written to memory. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_spherical_harmonics_compute_selected_vjp(
+    sphericart_cuda_spherical_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const double* scales, const double* out_grad, double* xyz_grad, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Values of selected degree blocks of the spherical (normalised) harmonics
+ * only, packed, scaled and with the input axes permuted, in one pass (what the reference's e3nn adaptor,
+ * sphericart-torch/python/sphericart/torch/e3nn.py:47-80, composes from a full evaluation, a slice, a
+ * permutation and a multiplication). l_list: n_l distinct degrees <= l_max, HOST pointer, in output order;
+ * out: n_samples x sum(2l+1), device pointer; axis_order: 3 HOST ints, the input columns holding x, y, z
+ * (NULL: 0, 1, 2); scales: n_l HOST factors (NULL: 1). Needs l_max <= 20. Returns 0 on success, otherwise
+ * non-zero with the message in sphericart_cuda_last_error(). */
+SPHERICART_EXPORT int sphericart_cuda_spherical_harmonics_compute_selected_f(
+    sphericart_cuda_spherical_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const float* scales, float* out, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Fused vector-Jacobian product of compute_selected_f:
+ * out_grad is n_samples x sum(2l+1) in the packed layout, xyz_grad n_samples x 3 in the caller's axis
+ * order (device pointers); gradients of the harmonics are never written to memory. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_spherical_harmonics_compute_selected_vjp_f(
+    sphericart_cuda_spherical_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const float* scales, const float* out_grad, float* xyz_grad, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Values of selected degree blocks of the solid harmonics
+ * only, packed, scaled and with the input axes permuted, in one pass (what the reference's e3nn adaptor,
+ * sphericart-torch/python/sphericart/torch/e3nn.py:47-80, composes from a full evaluation, a slice, a
+ * permutation and a multiplication). l_list: n_l distinct degrees <= l_max, HOST pointer, in output order;
+ * out: n_samples x sum(2l+1), device pointer; axis_order: 3 HOST ints, the input columns holding x, y, z
+ * (NULL: 0, 1, 2); scales: n_l HOST factors (NULL: 1). Needs l_max <= 20. Returns 0 on success, otherwise
+ * non-zero with the message in sphericart_cuda_last_error(). */
+SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_compute_selected(
+    sphericart_cuda_solid_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const double* scales, double* out, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Fused vector-Jacobian product of compute_selected:
+ * out_grad is n_samples x sum(2l+1) in the packed layout, xyz_grad n_samples x 3 in the caller's axis
+ * order (device pointers); gradients of the harmonics are never written to memory. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_compute_selected_vjp(
+    sphericart_cuda_solid_harmonics_calculator_t* calculator, const double* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const double* scales, const double* out_grad, double* xyz_grad, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Values of selected degree blocks of the solid harmonics
+ * only, packed, scaled and with the input axes permuted, in one pass (what the reference's e3nn adaptor,
+ * sphericart-torch/python/sphericart/torch/e3nn.py:47-80, composes from a full evaluation, a slice, a
+ * permutation and a multiplication). l_list: n_l distinct degrees <= l_max, HOST pointer, in output order;
+ * out: n_samples x sum(2l+1), device pointer; axis_order: 3 HOST ints, the input columns holding x, y, z
+ * (NULL: 0, 1, 2); scales: n_l HOST factors (NULL: 1). Needs l_max <= 20. Returns 0 on success, otherwise
+ * non-zero with the message in sphericart_cuda_last_error(). */
+SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_compute_selected_f(
+    sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const float* scales, float* out, void* cuda_stream);
+
+/* No counterpart in the reference's C API. Fused vector-Jacobian product of compute_selected_f:
+ * out_grad is n_samples x sum(2l+1) in the packed layout, xyz_grad n_samples x 3 in the caller's axis
+ * order (device pointers); gradients of the harmonics are never written to memory. Returns 0 on success. */
+SPHERICART_EXPORT int sphericart_cuda_solid_harmonics_compute_selected_vjp_f(
+    sphericart_cuda_solid_harmonics_calculator_f_t* calculator, const float* xyz, size_t n_samples, const int* l_list, size_t n_l, const int* axis_order,
+    const float* scales, const float* out_grad, float* xyz_grad, void* cuda_stream);
 
 /* No counterpart in the reference. Values and gradients (float64, level 1) for hosts that do not
  * let a plugin allocate device memory of its own - a runtime that reserved the whole device arena

@@ -64,6 +64,27 @@ template <typename T> class SphericalHarmonics {
         void* cuda_stream = nullptr
     );
 
+    /// Values of selected degree blocks only, packed, scaled and with the input axes permuted, in one
+    /// pass (no counterpart in the reference's C++ classes; it serves callers such as the reference's
+    /// e3nn adaptor, sphericart-torch/python/sphericart/torch/e3nn.py:47-80, which evaluates every degree
+    /// and then slices, permutes and rescales). l_list: n_l distinct degrees <= l_max (HOST pointer), in
+    /// the order their blocks appear in the output; out is n_samples x sum(2l+1) (device pointer);
+    /// axis_order: three HOST ints, a permutation of 0, 1, 2 giving the input columns that hold x, y, z
+    /// (null: 0, 1, 2); scales: n_l HOST factors, one per listed degree (null: all 1). Needs
+    /// l_max <= 20 (the compile-time kernels); throws std::runtime_error otherwise.
+    void compute_selected(
+        const T* xyz, const size_t n_samples, const int* l_list, const size_t n_l, const int* axis_order,
+        const T* scales, T* out, void* cuda_stream = nullptr
+    );
+
+    /// Fused vector-Jacobian product of compute_selected: out_grad is n_samples x sum(2l+1) in the
+    /// packed layout, xyz_grad is n_samples x 3 in the caller's axis order; the gradients of the
+    /// harmonics are never written to memory.
+    void compute_selected_vjp(
+        const T* xyz, const size_t n_samples, const int* l_list, const size_t n_l, const int* axis_order,
+        const T* scales, const T* out_grad, T* xyz_grad, void* cuda_stream = nullptr
+    );
+
     template <typename U> friend class SolidHarmonics;
 
   private:

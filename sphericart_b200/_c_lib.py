@@ -18,14 +18,15 @@ _SUFFIXES = ("", "_f")
 
 def exported_names():
     """Every function the C header declares, in declaration-family order."""
-    names = ["sphericart_cuda_last_error", "sphericart_cuda_device_wait_errors",
+    names = ["sphericart_cuda_last_error", "sphericart_cuda_kernel_family", "sphericart_cuda_device_wait_errors",
              "sphericart_cuda_harmonics_with_gradients_no_alloc"]
     for kind in _KINDS:
         for sfx in _SUFFIXES:
             base = f"sphericart_cuda_{kind}_harmonics"
             for fn in ("new", "delete", "compute_array", "compute_array_with_gradients",
                        "compute_array_with_hessians", "compute_vjp", "try_compute", "try_compute_vjp",
-                       "compute_vjp_with_gradients", "try_compute_vjp_with_gradients"):
+                       "compute_vjp_with_gradients", "try_compute_vjp_with_gradients",
+                       "compute_selected", "compute_selected_vjp"):
                 names.append(f"{base}_{fn}{sfx}")
     return names
 
@@ -43,6 +44,8 @@ def get_library():
     vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
     lib.sphericart_cuda_last_error.restype = ctypes.c_char_p
     lib.sphericart_cuda_last_error.argtypes = []
+    lib.sphericart_cuda_kernel_family.restype = ctypes.c_char_p
+    lib.sphericart_cuda_kernel_family.argtypes = [ci, sz, ci]
     lib.sphericart_cuda_device_wait_errors.restype = ci
     lib.sphericart_cuda_device_wait_errors.argtypes = []
     lib.sphericart_cuda_harmonics_with_gradients_no_alloc.restype = ci
@@ -66,6 +69,8 @@ def get_library():
             bind("try_compute_vjp", ci, [vp, vp, sz, vp, vp, vp])
             bind("compute_vjp_with_gradients", None, [vp, vp, sz, vp, vp, vp, vp])
             bind("try_compute_vjp_with_gradients", ci, [vp, vp, sz, vp, vp, vp, vp])
+            bind("compute_selected", ci, [vp, vp, sz, vp, sz, vp, vp, vp, vp])
+            bind("compute_selected_vjp", ci, [vp, vp, sz, vp, sz, vp, vp, vp, vp, vp])
     _lib = lib
     return lib
 
@@ -73,3 +78,8 @@ def get_library():
 def last_error():
     msg = get_library().sphericart_cuda_last_error()
     return msg.decode("utf-8", "replace") if msg else ""
+
+
+def kernel_family(kind, l_max, elem_bytes):
+    """Name of the kernel family that serves a call (kind 0..2 forward level, 3 VJP, 4 second-order VJP)."""
+    return get_library().sphericart_cuda_kernel_family(int(kind), int(l_max), int(elem_bytes)).decode()

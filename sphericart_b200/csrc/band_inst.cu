@@ -18,23 +18,7 @@ namespace {
 template <typename T, int LEVEL, bool NORM, int G, bool VJP, bool DIRECT>
 cudaError_t launch_band(const BandLaunchArgs<T>& a, int device, cudaStream_t stream) {
     auto kernel = sph_band_kernel<T, LEVEL, NORM, G, VJP, DIRECT>;
-    // The occupancy query (and the raise of the kernel's shared-memory limit that goes with it) is
-    // remembered per thread for the last few (device, warps, shared memory) combinations of this
-    // instantiation, so that a steady stream of calls pays for it once.
-    struct Slot {
-        int device, warps, blocks;
-        size_t smem;
-    };
-    thread_local Slot slots[4] = {{-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}};
-    thread_local int next_slot = 0;
-    int max_blocks = -1;
-    for (const Slot& s : slots)
-        if (s.device == device && s.warps == a.warps && s.smem == a.smem) max_blocks = s.blocks;
-    if (max_blocks < 0) {
-        max_blocks = persistent_grid(reinterpret_cast<const void*>(kernel), a.warps * 32, a.smem, device);
-        slots[next_slot] = Slot{device, a.warps, max_blocks, a.smem};
-        next_slot = (next_slot + 1) % 4;
-    }
+    const int max_blocks = memo_grid<sph_band_kernel<T, LEVEL, NORM, G, VJP, DIRECT>>(a.warps * 32, a.smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     constexpr int P = 32 / G;
     const long long ngroups = (a.n + P - 1) / P;

@@ -1,5 +1,5 @@
 // Instantiates the panel kernels for one (type, points-per-panel) pair: compile with
-//   -DSPH_T=float|double -DSPH_TP=1|2|4|8|16|32
+//   -DSPH_T=float|double -DSPH_TP=1|2|4|8|16|32   (points per table batch)
 #include "sph_launch.hpp"
 #include "sph_panel.cuh"
 
@@ -17,26 +17,14 @@ namespace {
 template <typename T, int LEVEL, bool NORM, int TP>
 cudaError_t launch_panel(const PanelLaunchArgs<T>& a, int device, cudaStream_t stream) {
     auto kernel = sph_panel_kernel<T, LEVEL, NORM, TP>;
-    // the occupancy query (which also raises the kernel's shared-memory limit) is remembered per
-    // thread for the last few (device, threads, shared memory) combinations of this instantiation
-    struct Slot {
-        int device, threads, blocks;
-        size_t smem;
-    };
-    thread_local Slot slots[4] = {{-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}};
-    thread_local int next_slot = 0;
-    int max_blocks = -1;
-    for (const Slot& s : slots)
-        if (s.device == device && s.threads == a.threads && s.smem == a.smem) max_blocks = s.blocks;
-    if (max_blocks < 0) {
-        max_blocks = persistent_grid(reinterpret_cast<const void*>(kernel), a.threads, a.smem, device);
-        slots[next_slot] = Slot{device, a.threads, max_blocks, a.smem};
-        next_slot = (next_slot + 1) % 4;
-    }
+    const int max_blocks = memo_grid<sph_panel_kernel<T, LEVEL, NORM, TP>>(a.threads, a.smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
-    if (a.threads % TP != 0 || a.threads > 256) return cudaErrorInvalidValue;
-    const long long npanels = (a.n + TP - 1) / TP;
-    const int grid = work_grid(npanels, max_blocks, a.iters, /*all_or_nothing=*/true);
+    if (a.threads < TP || a.threads > 256 || a.tp < 1 || a.tp > TP || (a.tp & (a.tp - 1)) != 0 || a.slots < 1 ||
+        a.slots > PANEL_MAX_SLOTS) {
+        return cudaErrorInvalidValue;
+    }
+    const long long nbatches = (a.n + TP - 1) / TP;
+    const int grid = work_grid(nbatches, max_blocks, a.iters, /*all_or_nothing=*/true);
     PanelArgs<T> k{};
     k.xyz = a.xyz;
     k.n = a.n;
@@ -47,6 +35,9 @@ cudaError_t launch_panel(const PanelLaunchArgs<T>& a, int device, cudaStream_t s
     k.desc = static_cast<const PanelDesc*>(a.d_desc);
     k.l_max = a.l_max;
     k.bulk = a.bulk;
+    k.tp = a.tp;
+    k.slots = a.slots;
+    k.tables_f64 = a.tables_f64;
     kernel<<<grid, a.threads, a.smem, stream>>>(k);
     return cudaGetLastError();
 }
@@ -68,6 +59,22 @@ cudaError_t PanelLaunch<T, TP>::run(int level, bool normalized, const PanelLaunc
                               : launch_panel<T, 2, false, TP>(a, device, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+template <typename T, int TP> int PanelLaunch<T, TP>::registers(int level, bool normalized) {
+    const void* kernel = nullptr;
+    switch (level) {
+        case 0: kernel = normalized ? (const void*)sph_panel_kernel<T, 0, true, TP> : (const void*)sph_panel_kernel<T, 0, false, TP>; break;
+        case 1: kernel = normalized ? (const void*)sph_panel_kernel<T, 1, true, TP> : (const void*)sph_panel_kernel<T, 1, false, TP>; break;
+        case 2: kernel = normalized ? (const void*)sph_panel_kernel<T, 2, true, TP> : (const void*)sph_panel_kernel<T, 2, false, TP>; break;
+        default: return 0;
+    }
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return attr.numRegs;
 }
 
 template struct PanelLaunch<SPH_T, SPH_TP>;

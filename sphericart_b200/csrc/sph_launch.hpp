@@ -38,6 +38,24 @@ constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
 int persistent_grid(const void* kernel, int block, size_t smem, int device);
 int device_sm_count(int device);
 
+// persistent_grid() for one kernel (a function pointer known at compile time), remembered per host
+// thread for the last few (device, threads, shared memory) combinations, so that a steady stream of
+// calls pays for the occupancy query (and the raise of the shared-memory limit) once.
+template <auto Kernel> int memo_grid(int threads, size_t smem, int device) {
+    struct Slot {
+        int device, threads, blocks;
+        size_t smem;
+    };
+    thread_local Slot slots[4] = {{-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}, {-1, 0, 0, 0}};
+    thread_local int next_slot = 0;
+    for (const Slot& s : slots)
+        if (s.device == device && s.threads == threads && s.smem == smem) return s.blocks;
+    const int blocks = persistent_grid(reinterpret_cast<const void*>(Kernel), threads, smem, device);
+    slots[next_slot] = Slot{device, threads, blocks, smem};
+    next_slot = (next_slot + 1) % 4;
+    return blocks;
+}
+
 // Every kernel walks its work items (spans of tiles, groups of points) with a grid-stride loop, so
 // the grid size alone decides how the work is divided:
 //   iters = 0: persistent launch, `resident` CTAs (one per slot the SMs offer), items dealt
@@ -64,6 +82,16 @@ inline int work_grid(long long ctas_wanted, int resident, int iters, bool all_or
     return int(grid < 1 ? 1 : grid);
 }
 
+// Which degree blocks a "selected" call emits and where (see sph_select.cuh): block l goes to the
+// packed columns dest[l] ... dest[l] + 2l (dest[l] < 0: not emitted) times scale[l]; axis[a] is the
+// input column that holds coordinate a.
+struct Selection {
+    int dest[TILE_LMAX + 1];
+    double scale[TILE_LMAX + 1];
+    int ny_out;
+    int axis[3];
+};
+
 // Tile kernels, l_max = LMAX known at compile time. host_tables = F then K (n_table each).
 template <typename T, int LMAX> struct TileLaunch {
     static size_t smem_per_warp(int level);
@@ -80,6 +108,11 @@ template <typename T, int LMAX> struct TileLaunch {
     // second-order backward: VJP of (values, gradients); sph_grad may be null
     static cudaError_t vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
                             T* xyz_grad, const T* host_tables, int warps, int iters, int device, cudaStream_t stream);
+    // values of selected degree blocks, packed / scaled / axis-permuted, and the matching fused VJP
+    static cudaError_t selected(bool normalized, const T* xyz, long long n, T* out, const T* host_tables,
+                                const Selection& selection, bool use_bulk, int device, cudaStream_t stream);
+    static cudaError_t selected_vjp(bool normalized, const T* xyz, const T* out_grad, long long n, T* xyz_grad,
+                                    const T* host_tables, const Selection& selection, int device, cudaStream_t stream);
     // 1 if a bounded wait inside one of this instantiation's kernels ever gave up on the current
     // device, 0 if not, -1 if the flag could not be read. Synchronises the device.
     static int device_error_flag();
@@ -105,7 +138,8 @@ template <typename T> struct BandLaunchArgs {
     int iters;     // see work_grid()
 };
 
-// Panel kernels, run-time l_max, forward levels only. TP points per CTA, threads / TP slices per point.
+// Panel kernels, run-time l_max, forward levels only. Tables for TPT points at a time, tp points per
+// image (a power of two dividing TPT), threads / tp slices per point, `slots` images per CTA.
 template <typename T> struct PanelLaunchArgs {
     const T* xyz;
     long long n;
@@ -116,13 +150,18 @@ template <typename T> struct PanelLaunchArgs {
     const void* d_desc;  // the per-pair descriptors (PanelDesc in sph_panel.cuh)
     int l_max;
     int bulk;            // 1: TMA bulk copy-out, 0: plain stores
-    int threads;         // threads per CTA (a multiple of TP)
+    int tp;
+    int slots;
+    int tables_f64;      // 1: table recurrences in float64 for float32 outputs too
+    int threads;         // threads per CTA
     size_t smem;
-    int iters;           // panels per CTA, see work_grid()
+    int iters;           // table batches per CTA, see work_grid()
 };
 
-template <typename T, int TP> struct PanelLaunch {
+template <typename T, int TPT> struct PanelLaunch {
     static cudaError_t run(int level, bool normalized, const PanelLaunchArgs<T>& a, int device, cudaStream_t stream);
+    // registers per thread of the kernel that run() would launch (0 if it cannot be queried)
+    static int registers(int level, bool normalized);
 };
 
 template <typename T, int G> struct BandLaunch {

@@ -1,31 +1,40 @@
 // "Panel" kernels: forward evaluation (values, gradients, Hessians) for any maximum degree
-// (run-time l_max) with a whole CTA working on a panel of TP consecutive points (TP = 1 ... 32).
-// They serve the cases with rows too long for the compile-time tile kernels (see panel_serves()
-// in sph_launch.hpp); the fused backward passes of those cases stay with the band kernel.
+// (run-time l_max) with a whole CTA working on a panel of tp consecutive points at a time
+// (tp = 1 ... 32). They serve the cases with rows too long for the compile-time tile kernels (see
+// the dispatch in sphericart_cuda.cu); the fused backward passes of those cases stay with the band
+// kernel.
 //
-// Work split. Thread t of a CTA is (point p = t mod TP, slice s = t / TP); S = blockDim.x / TP
-// slices share each point. Neighbouring lanes therefore hold DIFFERENT POINTS and the SAME (l, m)
-// pair, which makes every shared-memory access of the hot loop conflict-free by construction: the
-// per-point tables are stored point-minor (element e of point p at e * TP + p), the per-pair
-// constants are read at one address by all lanes of a slice, and the image rows of neighbouring
-// points are an odd number of words apart. (The band kernel deals pairs to lanes instead; half of
-// its image stores conflict where a warp straddles two degrees.)
+// Work split. For a panel, thread t of a CTA is (point p = t mod tp, slice s = t / tp);
+// S = blockDim.x / tp slices share each point. Neighbouring lanes therefore hold DIFFERENT POINTS and
+// the SAME (l, m) pair, which makes the shared-memory accesses of the hot loop conflict-free by
+// construction: the per-point tables are stored point-minor (element e of point q at e * TPT + q),
+// the per-pair constants are read at one address by all lanes of a slice, and the image rows of
+// neighbouring points are an odd number of 4-word groups apart. (The band kernel deals pairs to
+// lanes instead; half of its image stores conflict where a warp straddles two degrees.)
 //
-//  A. Tables, once per panel, all threads: c_m + i s_m = (x + i y)^m (slice s builds a block of
-//     consecutive m from one power) and the triangular table Q_l^m with the reference's
-//     downward-in-m recurrence (sphericart/include/templates_core.hpp:123,155,202), rows dealt to
-//     the slices in pairs (l, l_max - l) of constant total length. Carried in float64 for both
-//     element types and rounded once on storing, as in the band kernel. Four zeros follow every
-//     diagonal, a block of zeros stands for the rows -1 and -2, and c, s carry two zeros before
-//     m = 0, so that every "term absent" case of the derivative formulas reads a zero.
-//  B. Pairs. Slice s evaluates the pairs t = s, s + S, ... of the flattened (l, m >= 0) list with
-//     the same per-pair code as the band kernel (band_eval_pair / eval_pair2 and the unit-sphere
-//     chain rule), two pairs in flight, and writes both columns of each pair into the panel's image.
-//  C. Copy-out. The panel's rows are one contiguous span of each output array; the image of each
-//     span, built at the span's own offset modulo 16 bytes, leaves as a TMA 1-D bulk store
-//     (cp.async.bulk.global.shared::cta), the few elements before the first and after the last
-//     16-byte boundary as plain stores. The tables of the next panel are built while the engine
-//     reads the image; only the first image store of the next panel waits for it.
+//  A. Tables, for a batch of TPT points (TPT / tp panels) at once, all threads: c_m + i s_m =
+//     (x + i y)^m (a slice builds a block of consecutive m from one power) and the triangular table
+//     Q_l^m with the reference's downward-in-m recurrence
+//     (sphericart/include/templates_core.hpp:123,155,202), rows dealt to the slices in pairs
+//     (l, l_max - l) of constant total length. The recurrence is a serial chain, so batching several
+//     panels' points gives this phase its parallelism. Carried in float64 for both element types and
+//     rounded once on storing, as in the band kernel. Four zeros follow every diagonal, a block of
+//     zeros stands for the rows -1 and -2, and c, s carry two zeros before m = 0, so that every "term
+//     absent" case of the derivative formulas reads a zero.
+//  B. Pairs, panel by panel. Slice s evaluates the pairs t = s, s + S, ... of the flattened
+//     (l, m >= 0) list with the same per-pair code as the band kernel (band_eval_pair / eval_pair2 and
+//     the unit-sphere chain rule) and writes both columns of each pair into the panel's image.
+//  C. Copy-out. The image leaves through the TMA engine (cp.async.bulk.global.shared::cta).
+//     Odd row lengths (even l_max): the panel's rows are one contiguous span of each output array;
+//     its image is built at the span's own offset modulo 16 bytes and leaves as one bulk store per
+//     array, the few elements before the first and after the last 16-byte boundary as plain stores.
+//     Even row lengths (odd l_max: (l_max+1)^2 is a multiple of 4): every point's row is 16-byte
+//     aligned by itself; rows get 16 bytes of padding where needed to keep neighbouring points an odd
+//     number of 16-byte groups apart, and leave as one bulk store per point and array.
+//     A CTA owns a ring of `slots` images: a panel's image is only waited for when its slot comes
+//     round again, so the engine drains one image while the CTA fills the next. What bounds these
+//     kernels is the number of image bytes an SM keeps in flight towards HBM, which is why the launch
+//     plan fills the shared memory with images first.
 //
 // No communication between CTAs or GPUs, no spin-wait. Replaces spherical_harmonics_kernel
 // (sphericart/src/sphericart_impl.cu:207-615).
@@ -37,13 +46,25 @@
 
 namespace sph_b200 {
 
-constexpr int PANEL_ROW_PAD = 4;  // zeros after the diagonal of every Q row
+constexpr int PANEL_ROW_PAD = 4;    // zeros after the diagonal of every Q row
+constexpr int PANEL_MAX_SLOTS = 4;  // images per CTA
 
-// Element offset (for TP = 1) of row l of the triangular Q table: a block of PANEL_ROW_PAD zeros
+// Element offset (for TPT = 1) of row l of the triangular Q table: a block of PANEL_ROW_PAD zeros
 // (standing for the rows -1 and -2), then row 0, row 1, ... each with its PANEL_ROW_PAD zeros.
 __host__ __device__ constexpr int panel_row_start(int l) { return PANEL_ROW_PAD + l * (l - 1) / 2 + (PANEL_ROW_PAD + 1) * l; }
-// Elements of per-point state: c and s with two leading zeros each, then the Q table.
-__host__ __device__ constexpr int panel_point_state(int l_max) { return 2 * (l_max + 3) + panel_row_start(l_max + 1); }
+// Elements of per-point state: the point itself (x, y, z - normalised where the harmonics are - and
+// 1/r), c and s with two leading zeros each, then the Q table.
+__host__ __device__ constexpr int panel_point_state(int l_max) { return 4 + 2 * (l_max + 3) + panel_row_start(l_max + 1); }
+
+// Elements between the image rows of neighbouring points for an array with `comps` rows of ny
+// columns per point. Odd ny: the rows are packed (the image is the exact picture of global memory).
+// Even ny: 16 bytes of padding where the packed distance would be an even number of 16-byte groups.
+__host__ __device__ constexpr int panel_point_stride(int comps, int ny, int elem_bytes) {
+    const int packed = comps * ny;
+    if (ny % 2 != 0) return packed;
+    const int q = 16 / elem_bytes;
+    return (packed / q) % 2 == 0 ? packed + q : packed;
+}
 
 // One entry per (l, m >= 0) pair, built on the host (see make_panel_desc in sphericart_cuda.cu):
 // element offsets of Q_l^m, Q_{l-1}^m and Q_{l-2}^m in the per-point table, and
@@ -62,12 +83,15 @@ template <typename T> struct PanelArgs {
     const PanelDesc* desc;  // n_table(l_max) entries
     int l_max;
     int bulk;               // 1: TMA bulk copy-out, 0: plain stores
+    int tp;                 // points per panel: a power of two that divides TPT
+    int slots;              // images per CTA, 1 ... PANEL_MAX_SLOTS
+    int tables_f64;         // 1: the table recurrences are carried in float64 whatever the element type
 };
 
-template <typename T, int TP, int LEVEL>
+template <typename T, int TPT, int LEVEL>
 __device__ __forceinline__ PairInputs<T, LEVEL> panel_load_pair(const PanelDesc d, T f, unsigned q_addr, unsigned c_addr,
                                                                 unsigned s_addr) {
-    constexpr unsigned E = unsigned(TP) * unsigned(sizeof(T));  // bytes between consecutive table elements of one point
+    constexpr unsigned E = unsigned(TPT) * unsigned(sizeof(T));  // bytes between consecutive table elements of one point
     PairInputs<T, LEVEL> in;
     const int m = (d.klm >> 16) & 0xff;
     const int l = (d.klm >> 24) & 0xff;
@@ -77,21 +101,21 @@ __device__ __forceinline__ PairInputs<T, LEVEL> panel_load_pair(const PanelDesc 
     const unsigned ac = c_addr + unsigned(m) * E;  // c_{m-2}
     const unsigned as = s_addr + unsigned(m) * E;  // s_{m-2}
     in.q = lds_at<T, 0>(q_addr + unsigned(d.off0));
-    in.cm = lds_at<T, 2 * TP>(ac);
-    in.sm = lds_at<T, 2 * TP>(as);
+    in.cm = lds_at<T, 2 * TPT>(ac);
+    in.sm = lds_at<T, 2 * TPT>(as);
     if constexpr (LEVEL >= 1) {
         const unsigned a1 = q_addr + unsigned(d.off1);
-        in.q1a = lds_at<T, TP>(a1);
+        in.q1a = lds_at<T, TPT>(a1);
         in.q1b = lds_at<T, 0>(a1);
-        in.cm1 = lds_at<T, TP>(ac);
-        in.sm1 = lds_at<T, TP>(as);
+        in.cm1 = lds_at<T, TPT>(ac);
+        in.sm1 = lds_at<T, TPT>(as);
         in.fm = T(m);
         in.flm = T(l + m);
     }
     if constexpr (LEVEL >= 2) {
         const unsigned a2 = q_addr + unsigned(d.off2);
-        in.q2a = lds_at<T, 2 * TP>(a2);
-        in.q2b = lds_at<T, TP>(a2);
+        in.q2a = lds_at<T, 2 * TPT>(a2);
+        in.q2b = lds_at<T, TPT>(a2);
         in.q2c = lds_at<T, 0>(a2);
         in.cm2 = lds_at<T, 0>(ac);
         in.sm2 = lds_at<T, 0>(as);
@@ -101,45 +125,119 @@ __device__ __forceinline__ PairInputs<T, LEVEL> panel_load_pair(const PanelDesc 
     return in;
 }
 
-// Dynamic shared memory of one CTA, in bytes (also used by the host to plan the launch).
-template <typename T> __host__ __device__ constexpr size_t panel_const_bytes(int l_max) {
-    return size_t(align16_elems<T>(2 * n_table(l_max))) * sizeof(T) + size_t(n_table(l_max)) * sizeof(PanelDesc);
-}
-template <typename T> __host__ __device__ constexpr size_t panel_state_bytes(int l_max, int tp) {
-    return size_t(align16_elems<T>(tp * panel_point_state(l_max))) * sizeof(T);
-}
-template <typename T> __host__ __device__ constexpr size_t panel_image_bytes(int l_max, int tp, int level) {
-    const int ny = n_columns(l_max);
-    size_t e = size_t(band_region<T>(tp, 1, ny));
-    if (level >= 1) e += size_t(band_region<T>(tp, 3, ny));
-    if (level >= 2) e += size_t(band_region<T>(tp, 9, ny));
-    return e * sizeof(T);
+// Elements of one image region (one output array of one panel), with the slack the alignment shift needs.
+template <typename T> __host__ __device__ constexpr int panel_region(int tp, int comps, int ny) {
+    return align16_elems<T>(tp * panel_point_stride(comps, ny, int(sizeof(T)))) + 16 / int(sizeof(T));
 }
 
-template <typename T, int LEVEL, bool NORM, int TP>
+// Waits until at most `pending` of this thread's committed bulk stores are still reading shared memory.
+__device__ __forceinline__ void bulk_wait_read_pending(int pending) {
+    switch (pending) {
+        case 0: asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); break;
+    }
+}
+
+// Phase A for one (point, slice): the slice's block of c_m + i s_m = (x + i y)^m (one power by repeated
+// squaring, then one complex product per m) and its rows of the Q table (pairs (j, L - j) of constant
+// total length), with the reference's downward-in-m recurrence
+// (sphericart/include/templates_core.hpp:123,155,202). A is the type the recurrences are carried in:
+// double (rounded once on storing) or the element type itself.
+template <typename T, typename A, int TPT>
+__device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa, int SA, int qa, T* sc, T* ss, T* sQ,
+                                                   const T* sK) {
+    const A xd = A(x), yd = A(y), zd = A(z);
+    const A rhod = xd * xd + yd * yd;
+    const int block = (L + SA) / SA;  // ceil((L + 1) / SA)
+    const int m0 = sa * block;
+    if (m0 <= L) {
+        A pr = A(1), pi = A(0);
+        A wr = xd, wi = yd;
+        for (int bits = m0; bits != 0; bits >>= 1) {
+            if (bits & 1) {
+                const A nr = pr * wr - pi * wi;
+                pi = pr * wi + pi * wr;
+                pr = nr;
+            }
+            const A sr = wr * wr - wi * wi;
+            wi = (wr + wr) * wi;
+            wr = sr;
+        }
+        const int m1 = (m0 + block - 1) < L ? (m0 + block - 1) : L;
+        for (int m = m0; m <= m1; ++m) {
+            sc[(m + 2) * TPT + qa] = T(pr);
+            ss[(m + 2) * TPT + qa] = T(pi);
+            const A nr = pr * xd - pi * yd;
+            pi = pr * yd + pi * xd;
+            pr = nr;
+        }
+    }
+    auto build_row = [&](int l) {
+        T* row = sQ + panel_row_start(l) * TPT + qa;
+        const T* Kl = sK + tri(l, 0);
+        A q2 = A(Kl[l]);  // Q_l^l is tabulated
+        row[l * TPT] = T(q2);
+        if (l >= 1) {
+            A q1 = -zd * q2;  // Q_l^{l-1}
+            row[(l - 1) * TPT] = T(q1);
+            A tm = A(2 * (l - 1));  // 2 (m + 1)
+            for (int m = l - 2; m >= 0; --m) {
+                const A q0 = A(Kl[m]) * (tm * zd * q1 + rhod * q2);
+                row[m * TPT] = T(q0);
+                q2 = q1;
+                q1 = q0;
+                tm -= A(2);
+            }
+        }
+    };
+    for (int j = sa; 2 * j <= L; j += SA) {
+        build_row(L - j);
+        if (L - j != j) build_row(j);
+    }
+}
+
+template <typename T, int LEVEL, bool NORM, int TPT>
 __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ PanelArgs<T> a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int L = a.l_max;
     const int ny = (L + 1) * (L + 1);
     const int nq = (L + 1) * (L + 2) / 2;
     const int tid = threadIdx.x;
-    const int p = tid % TP;  // point of the panel
-    const int s = tid / TP;  // slice of the point's (l, m) pairs
-    const int S = blockDim.x / TP;
+    const int tp = a.tp;
+    const int slots = a.slots;
     const bool bulk = a.bulk != 0;
-    constexpr unsigned E = unsigned(TP) * unsigned(sizeof(T));
+    const bool packed_rows = (ny & 1) != 0;  // odd row length: the image is the exact picture of global memory
+    constexpr unsigned E = unsigned(TPT) * unsigned(sizeof(T));
+    constexpr int Q16 = 16 / int(sizeof(T));
 
-    // carve-up: F | K | descriptors | per-point state (point-minor) | images
+    // phase A: thread = (point of the batch, table slice)
+    const int qa = tid % TPT;
+    const int sa = tid / TPT;
+    const int SA = blockDim.x / TPT;
+    // phase B: thread = (point of the panel, pair slice)
+    const int p = tid & (tp - 1);
+    const int s = tid / tp;
+    const int S = blockDim.x / tp;
+
+    // carve-up: F | K | descriptors | per-point state of a batch (point-minor) | slots x images
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
     PanelDesc* sDesc = reinterpret_cast<PanelDesc*>(sF + align16_elems<T>(2 * nq));
     T* state = reinterpret_cast<T*>(sDesc + nq);
-    T* sc = state;                            // c_m of point p at sc[(m + 2) * TP + p]
-    T* ss = sc + (L + 3) * TP;                // s_m likewise
-    T* sQ = ss + (L + 3) * TP;                // element e of point p at sQ[e * TP + p]
-    T* region0 = state + align16_elems<T>(TP * panel_point_state(L));
-    T* region1 = region0 + band_region<T>(TP, 1, ny);
-    T* region2 = region1 + (LEVEL >= 1 ? band_region<T>(TP, 3, ny) : 0);
+    T* sP = state;              // x, y, z, 1/r of point q at sP[c * TPT + q]
+    T* sc = sP + 4 * TPT;       // c_m of point q at sc[(m + 2) * TPT + q]
+    T* ss = sc + (L + 3) * TPT;  // s_m likewise
+    T* sQ = ss + (L + 3) * TPT;  // element e of point q at sQ[e * TPT + q]
+    T* images = state + align16_elems<T>(TPT * panel_point_state(L));
+    const int st0 = panel_point_stride(1, ny, int(sizeof(T)));
+    const int st1 = panel_point_stride(3, ny, int(sizeof(T)));
+    const int st2 = panel_point_stride(9, ny, int(sizeof(T)));
+    const int reg0 = panel_region<T>(tp, 1, ny);
+    const int reg1 = LEVEL >= 1 ? panel_region<T>(tp, 3, ny) : 0;
+    const int reg2 = LEVEL >= 2 ? panel_region<T>(tp, 9, ny) : 0;
+    const int slot_elems = reg0 + reg1 + reg2;
 
     // ---- once per CTA: constants, and the zeros that never change
     for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
@@ -150,268 +248,262 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
         d.off2 *= int(E);
         sDesc[t] = d;
     }
-    for (int e = tid; e < 2 * TP; e += blockDim.x) {
+    for (int e = tid; e < 2 * TPT; e += blockDim.x) {
         sc[e] = T(0);
         ss[e] = T(0);
     }
-    for (int e = tid; e < PANEL_ROW_PAD * TP; e += blockDim.x) sQ[e] = T(0);
-    for (int e = tid; e < (L + 1) * PANEL_ROW_PAD * TP; e += blockDim.x) {
-        const int l = e / (PANEL_ROW_PAD * TP);
-        const int r = e % (PANEL_ROW_PAD * TP);
-        sQ[(panel_row_start(l) + l + 1) * TP + r] = T(0);
+    for (int e = tid; e < PANEL_ROW_PAD * TPT; e += blockDim.x) sQ[e] = T(0);
+    for (int e = tid; e < (L + 1) * PANEL_ROW_PAD * TPT; e += blockDim.x) {
+        const int l = e / (PANEL_ROW_PAD * TPT);
+        const int r = e % (PANEL_ROW_PAD * TPT);
+        sQ[(panel_row_start(l) + l + 1) * TPT + r] = T(0);
     }
     __syncthreads();
 
-    const unsigned q_addr = static_cast<unsigned>(__cvta_generic_to_shared(sQ + p));
-    const unsigned c_addr = static_cast<unsigned>(__cvta_generic_to_shared(sc + p));
-    const unsigned s_addr = static_cast<unsigned>(__cvta_generic_to_shared(ss + p));
     const unsigned f_addr = static_cast<unsigned>(__cvta_generic_to_shared(sF));
     const unsigned desc_addr = static_cast<unsigned>(__cvta_generic_to_shared(sDesc));
     const unsigned ny_b = unsigned(ny) * unsigned(sizeof(T));
 
-    const long long npanels = (a.n + TP - 1) / TP;
-    bool stores_in_flight = false;  // thread 0 only: committed bulk stores that may still read the images
-    for (long long panel = blockIdx.x; panel < npanels; panel += gridDim.x) {
-        const long long first = panel * TP;
-        const long long i = first + p;
-        const int nvalid = (a.n - first) < TP ? int(a.n - first) : TP;
-
-        // rows past the end evaluate a harmless point; they are never copied out
-        T x = T(1), y = T(0), z = T(0);
-        if (i < a.n) {
-            x = a.xyz[3 * i + 0];
-            y = a.xyz[3 * i + 1];
-            z = a.xyz[3 * i + 2];
+    const long long nbatches = (a.n + TPT - 1) / TPT;
+    // rows past the end evaluate a harmless point; they are never copied out
+    auto fetch_point = [&](long long batch, T& px, T& py, T& pz) {
+        px = T(1);
+        py = T(0);
+        pz = T(0);
+        const long long ip = batch * TPT + qa;
+        if (batch < nbatches && ip < a.n) {
+            px = a.xyz[3 * ip + 0];
+            py = a.xyz[3 * ip + 1];
+            pz = a.xyz[3 * ip + 2];
         }
-        UnitSphere<T> us{x, y, z, T(0), T(0)};
-        if constexpr (NORM) {
-            // IEEE square root and division, as on the CPU (sphericart/include/templates.hpp:392-400)
-            const T ir = T(1) / sqrt(x * x + y * y + z * z);
-            x *= ir;
-            y *= ir;
-            z *= ir;
-            us = UnitSphere<T>{x, y, z, ir, ir * ir};
-        }
-        const T x2 = x * x, y2 = y * y, xy = x * y;
+    };
+    T next_x = T(1), next_y = T(0), next_z = T(0);
+    if (sa < SA) fetch_point(blockIdx.x, next_x, next_y, next_z);
+    int slot = 0;
+    int committed = 0;  // thread 0 only: bulk-store groups committed so far
+    for (long long batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
+        const long long batch_first = batch * TPT;
 
-        // ---- phase A (float64 for both element types, rounded once on storing)
-        {
-            const double xd = double(x), yd = double(y), zd = double(z);
-            const double rhod = xd * xd + yd * yd;
-            // c_m + i s_m for a block of consecutive m: one power, then one complex product per m
-            const int block = (L + S) / S;  // ceil((L + 1) / S)
-            const int m0 = s * block;
-            if (m0 <= L) {
-                double pr = 1.0, pi = 0.0;
-                double wr = xd, wi = yd;
-                for (int bits = m0; bits != 0; bits >>= 1) {
-                    if (bits & 1) {
-                        const double nr = pr * wr - pi * wi;
-                        pi = pr * wi + pi * wr;
-                        pr = nr;
-                    }
-                    const double sr = wr * wr - wi * wi;
-                    wi = (wr + wr) * wi;
-                    wr = sr;
-                }
-                const int m1 = (m0 + block - 1) < L ? (m0 + block - 1) : L;
-                for (int m = m0; m <= m1; ++m) {
-                    sc[(m + 2) * TP + p] = T(pr);
-                    ss[(m + 2) * TP + p] = T(pi);
-                    const double nr = pr * xd - pi * yd;
-                    pi = pr * yd + pi * xd;
-                    pr = nr;
-                }
+        // ---- phase A
+        if (sa < SA) {
+            T x = next_x, y = next_y, z = next_z, ir = T(1);
+            // the next batch's point is fetched now and used an entire batch later: under a saturated
+            // write stream a read from global memory takes microseconds
+            fetch_point(batch + gridDim.x, next_x, next_y, next_z);
+            if constexpr (NORM) {
+                // IEEE square root and division, as on the CPU (sphericart/include/templates.hpp:392-400)
+                ir = T(1) / sqrt(x * x + y * y + z * z);
+                x *= ir;
+                y *= ir;
+                z *= ir;
             }
-            // Q rows, dealt to the slices in pairs (j, L - j) of constant total length
-            auto build_row = [&](int l) {
-                T* row = sQ + panel_row_start(l) * TP + p;
-                const T* Kl = sK + tri(l, 0);
-                double q2 = double(Kl[l]);  // Q_l^l is tabulated
-                row[l * TP] = T(q2);
-                if (l >= 1) {
-                    double q1 = -zd * q2;  // Q_l^{l-1}
-                    row[(l - 1) * TP] = T(q1);
-                    double tm = double(2 * (l - 1));  // 2 (m + 1)
-                    for (int m = l - 2; m >= 0; --m) {
-                        const double q0 = double(Kl[m]) * (tm * zd * q1 + rhod * q2);
-                        row[m * TP] = T(q0);
-                        q2 = q1;
-                        q1 = q0;
-                        tm -= 2.0;
-                    }
-                }
-            };
-            for (int j = s; 2 * j <= L; j += S) {
-                build_row(L - j);
-                if (L - j != j) build_row(j);
+            if (sa == 0) {
+                // phase B reads the point from here
+                sP[0 * TPT + qa] = x;
+                sP[1 * TPT + qa] = y;
+                sP[2 * TPT + qa] = z;
+                sP[3 * TPT + qa] = ir;
             }
-        }
-
-        // where this panel's rows go; images placed so that shared and global addresses agree modulo 16 bytes
-        T* gsph = a.sph + first * ny;
-        T* gd = LEVEL >= 1 ? a.dsph + first * 3 * ny : nullptr;
-        T* gdd = LEVEL >= 2 ? a.ddsph + first * 9 * ny : nullptr;
-        int shift0 = 0, shift1 = 0, shift2 = 0;
-        if (bulk) {
-            shift0 = int((reinterpret_cast<uintptr_t>(gsph) & 15u) / sizeof(T));
-            if constexpr (LEVEL >= 1) shift1 = int((reinterpret_cast<uintptr_t>(gd) & 15u) / sizeof(T));
-            if constexpr (LEVEL >= 2) shift2 = int((reinterpret_cast<uintptr_t>(gdd) & 15u) / sizeof(T));
-        }
-        T* image0 = region0 + shift0;
-        T* image1 = region1 + shift1;
-        T* image2 = region2 + shift2;
-
-        // the engine must be done reading the previous panel's images before phase B overwrites them
-        if (tid == 0 && stores_in_flight) {
-            bulk_wait_read_all();
-            stores_in_flight = false;
-        }
-        __syncthreads();  // tables complete, images free
-
-        const unsigned img0_addr = static_cast<unsigned>(__cvta_generic_to_shared(image0 + p * ny));
-        [[maybe_unused]] const unsigned img1_addr = static_cast<unsigned>(__cvta_generic_to_shared(image1 + p * 3 * ny));
-        [[maybe_unused]] const unsigned img2_addr = static_cast<unsigned>(__cvta_generic_to_shared(image2 + p * 9 * ny));
-
-        auto store_column = [&](int k, const Column<T>& v) {
-            const unsigned k_b = unsigned(k) * unsigned(sizeof(T));
-            sts_to<T>(img0_addr + k_b, v.y);
-            if constexpr (LEVEL >= 1) {
-                unsigned ad = img1_addr + k_b;
-                sts_to<T>(ad, v.gx);
-                ad += ny_b;
-                sts_to<T>(ad, v.gy);
-                ad += ny_b;
-                sts_to<T>(ad, v.gz);
-            }
-            if constexpr (LEVEL >= 2) {
-                unsigned ah = img2_addr + k_b;
-                sts_to<T>(ah, v.hxx);
-                ah += ny_b;
-                sts_to<T>(ah, v.hxy);
-                ah += ny_b;
-                sts_to<T>(ah, v.hxz);
-                ah += ny_b;
-                sts_to<T>(ah, v.hxy);
-                ah += ny_b;
-                sts_to<T>(ah, v.hyy);
-                ah += ny_b;
-                sts_to<T>(ah, v.hyz);
-                ah += ny_b;
-                sts_to<T>(ah, v.hxz);
-                ah += ny_b;
-                sts_to<T>(ah, v.hyz);
-                ah += ny_b;
-                sts_to<T>(ah, v.hzz);
-            }
-        };
-        // float32 with derivatives: the pair's two columns go through the packed two-wide path
-        constexpr bool PACKED = sizeof(T) == 4 && LEVEL >= 1;
-        constexpr bool CHAIN = NORM && LEVEL >= 1;
-        [[maybe_unused]] UnitSphere2 us2{};
-        if constexpr (PACKED && CHAIN) {
-            UnitSphere<float> usf{float(us.x), float(us.y), float(us.z), float(us.ir), float(us.irsq)};
-            us2 = make_unit_sphere2<LEVEL>(usf);
-        }
-        auto finish_pair = [&](const PairInputs<T, LEVEL>& in) {
-            Column<T> vp{}, vm{};
-            if constexpr (PACKED) {
-                PairScalars ps{};
-                ps.f = float(in.f);
-                ps.q = float(in.q);
-                ps.q1a = float(in.q1a);
-                ps.q1b = float(in.q1b);
-                ps.fm = float(in.fm);
-                ps.flm = float(in.flm);
-                F2 cs2 = bc(0.0f);
-                if constexpr (LEVEL >= 2) {
-                    ps.q2a = float(in.q2a);
-                    ps.q2b = float(in.q2b);
-                    ps.q2c = float(in.q2c);
-                    ps.fmm = float(in.fmm);
-                    ps.fz = float(in.fz);
-                    cs2 = f2(float(in.cm2), float(in.sm2));
-                }
-                Column2 v{};
-                eval_pair2<LEVEL>(ps, f2(float(in.cm), float(in.sm)), f2(float(in.cm1), float(in.sm1)), cs2, float(x),
-                                  float(y), float(x2), float(y2), float(xy), v);
-                if constexpr (CHAIN) to_cartesian2<LEVEL>(v, us2);
-                vp.y = T(v.y.v.x);    vm.y = T(v.y.v.y);
-                vp.gx = T(v.gx.v.x);  vm.gx = T(v.gx.v.y);
-                vp.gy = T(v.gy.v.x);  vm.gy = T(v.gy.v.y);
-                vp.gz = T(v.gz.v.x);  vm.gz = T(v.gz.v.y);
-                if constexpr (LEVEL >= 2) {
-                    vp.hxx = T(v.hxx.v.x);  vm.hxx = T(v.hxx.v.y);
-                    vp.hxy = T(v.hxy.v.x);  vm.hxy = T(v.hxy.v.y);
-                    vp.hxz = T(v.hxz.v.x);  vm.hxz = T(v.hxz.v.y);
-                    vp.hyy = T(v.hyy.v.x);  vm.hyy = T(v.hyy.v.y);
-                    vp.hyz = T(v.hyz.v.x);  vm.hyz = T(v.hyz.v.y);
-                    vp.hzz = T(v.hzz.v.x);  vm.hzz = T(v.hzz.v.y);
-                }
+            if (a.tables_f64 != 0) {
+                panel_build_tables<T, double, TPT>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
             } else {
-                band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
-                if constexpr (CHAIN) {
-                    to_cartesian<T, LEVEL>(vp, us);
-                    to_cartesian<T, LEVEL>(vm, us);
-                }
+                panel_build_tables<T, T, TPT>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
             }
-            store_column(in.kp, vp);
-            if (in.m > 0) store_column(in.kp - 2 * in.m, vm);
-        };
-
-        // ---- phase B: pairs t = s, s + S, ..., two in flight per thread
-        auto load = [&](int t) {
-            PanelDesc d;
-            asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(d.off0), "=r"(d.off1), "=r"(d.off2), "=r"(d.klm)
-                         : "r"(desc_addr + unsigned(t) * 16u));
-            const T f = lds_at<T, 0>(f_addr + unsigned(t) * unsigned(sizeof(T)));
-            return panel_load_pair<T, TP, LEVEL>(d, f, q_addr, c_addr, s_addr);
-        };
-        int t = s;
-        for (; t + S < nq; t += 2 * S) {
-            const PairInputs<T, LEVEL> in0 = load(t);
-            const PairInputs<T, LEVEL> in1 = load(t + S);
-            finish_pair(in0);
-            finish_pair(in1);
         }
-        if (t < nq) finish_pair(load(t));
 
-        // ---- copy-out
-        if (bulk) {
-            fence_proxy_async_smem();  // this thread's image writes, visible to the TMA engine
-            __syncthreads();           // images complete; phase B has finished reading the tables
-            if (tid < 32) {
-                constexpr int Q16 = 16 / int(sizeof(T));
-                auto copy_out = [&](T* gdst, const T* img, int shift, int count) {
-                    const int head = shift == 0 ? 0 : (Q16 - shift < count ? Q16 - shift : count);
-                    const int body = (count - head) / Q16 * Q16;
-                    const int tail = count - head - body;
-                    if (tid < head) gdst[tid] = img[tid];
-                    if (tid >= 8 && tid - 8 < tail) gdst[head + body + tid - 8] = img[head + body + tid - 8];
-                    if (tid == 0 && body > 0)
-                        bulk_store_smem_to_global(gdst + head, img + head, unsigned(body) * unsigned(sizeof(T)));
+        // ---- the batch's panels, one image each
+        for (int sub = 0; sub < TPT; sub += tp) {
+            const long long first = batch_first + sub;
+            if (first >= a.n) break;  // the same for every thread
+            const int nvalid = (a.n - first) < tp ? int(a.n - first) : tp;
+
+            // where this panel's rows go; with packed rows the images are placed so that shared and
+            // global addresses agree modulo 16 bytes
+            T* gsph = a.sph + first * ny;
+            T* gd = LEVEL >= 1 ? a.dsph + first * 3 * ny : nullptr;
+            T* gdd = LEVEL >= 2 ? a.ddsph + first * 9 * ny : nullptr;
+            int shift0 = 0, shift1 = 0, shift2 = 0;
+            if (bulk && packed_rows) {
+                shift0 = int((reinterpret_cast<uintptr_t>(gsph) & 15u) / sizeof(T));
+                if constexpr (LEVEL >= 1) shift1 = int((reinterpret_cast<uintptr_t>(gd) & 15u) / sizeof(T));
+                if constexpr (LEVEL >= 2) shift2 = int((reinterpret_cast<uintptr_t>(gdd) & 15u) / sizeof(T));
+            }
+            T* region0 = images + slot * slot_elems;
+            T* image0 = region0 + shift0;
+            T* image1 = region0 + reg0 + shift1;
+            T* image2 = region0 + reg0 + reg1 + shift2;
+
+            // the engine must be done reading this slot's previous image before phase B overwrites it:
+            // of the groups committed so far all but the last slots - 1 must have been read
+            if (tid == 0 && committed >= slots) bulk_wait_read_pending(slots - 1);
+            __syncthreads();  // tables complete, slot free
+
+            if (s < S) {
+                const T x = sP[0 * TPT + sub + p], y = sP[1 * TPT + sub + p], z = sP[2 * TPT + sub + p];
+                [[maybe_unused]] const T ir = sP[3 * TPT + sub + p];
+                const UnitSphere<T> us{x, y, z, ir, ir * ir};
+                const T x2 = x * x, y2 = y * y, xy = x * y;
+                const unsigned q_addr = static_cast<unsigned>(__cvta_generic_to_shared(sQ + sub + p));
+                const unsigned c_addr = static_cast<unsigned>(__cvta_generic_to_shared(sc + sub + p));
+                const unsigned s_addr = static_cast<unsigned>(__cvta_generic_to_shared(ss + sub + p));
+                const unsigned img0_addr = static_cast<unsigned>(__cvta_generic_to_shared(image0 + p * st0));
+                [[maybe_unused]] const unsigned img1_addr = static_cast<unsigned>(__cvta_generic_to_shared(image1 + p * st1));
+                [[maybe_unused]] const unsigned img2_addr = static_cast<unsigned>(__cvta_generic_to_shared(image2 + p * st2));
+
+                auto store_column = [&](int k, const Column<T>& v) {
+                    const unsigned k_b = unsigned(k) * unsigned(sizeof(T));
+                    sts_to<T>(img0_addr + k_b, v.y);
+                    if constexpr (LEVEL >= 1) {
+                        unsigned ad = img1_addr + k_b;
+                        sts_to<T>(ad, v.gx);
+                        ad += ny_b;
+                        sts_to<T>(ad, v.gy);
+                        ad += ny_b;
+                        sts_to<T>(ad, v.gz);
+                    }
+                    if constexpr (LEVEL >= 2) {
+                        unsigned ah = img2_addr + k_b;
+                        sts_to<T>(ah, v.hxx);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hxy);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hxz);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hxy);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hyy);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hyz);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hxz);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hyz);
+                        ah += ny_b;
+                        sts_to<T>(ah, v.hzz);
+                    }
                 };
-                copy_out(gsph, image0, shift0, nvalid * ny);
-                if constexpr (LEVEL >= 1) copy_out(gd, image1, shift1, nvalid * 3 * ny);
-                if constexpr (LEVEL >= 2) copy_out(gdd, image2, shift2, nvalid * 9 * ny);
+                // float32 with derivatives: the pair's two columns go through the packed two-wide path
+                constexpr bool PACKED = sizeof(T) == 4 && LEVEL >= 1;
+                constexpr bool CHAIN = NORM && LEVEL >= 1;
+                [[maybe_unused]] UnitSphere2 us2{};
+                if constexpr (PACKED && CHAIN) {
+                    UnitSphere<float> usf{float(us.x), float(us.y), float(us.z), float(us.ir), float(us.irsq)};
+                    us2 = make_unit_sphere2<LEVEL>(usf);
+                }
+                auto finish_pair = [&](const PairInputs<T, LEVEL>& in) {
+                    Column<T> vp{}, vm{};
+                    if constexpr (PACKED) {
+                        PairScalars ps{};
+                        ps.f = float(in.f);
+                        ps.q = float(in.q);
+                        ps.q1a = float(in.q1a);
+                        ps.q1b = float(in.q1b);
+                        ps.fm = float(in.fm);
+                        ps.flm = float(in.flm);
+                        F2 cs2 = bc(0.0f);
+                        if constexpr (LEVEL >= 2) {
+                            ps.q2a = float(in.q2a);
+                            ps.q2b = float(in.q2b);
+                            ps.q2c = float(in.q2c);
+                            ps.fmm = float(in.fmm);
+                            ps.fz = float(in.fz);
+                            cs2 = f2(float(in.cm2), float(in.sm2));
+                        }
+                        Column2 v{};
+                        eval_pair2<LEVEL>(ps, f2(float(in.cm), float(in.sm)), f2(float(in.cm1), float(in.sm1)), cs2,
+                                          float(x), float(y), float(x2), float(y2), float(xy), v);
+                        if constexpr (CHAIN) to_cartesian2<LEVEL>(v, us2);
+                        vp.y = T(v.y.v.x);    vm.y = T(v.y.v.y);
+                        vp.gx = T(v.gx.v.x);  vm.gx = T(v.gx.v.y);
+                        vp.gy = T(v.gy.v.x);  vm.gy = T(v.gy.v.y);
+                        vp.gz = T(v.gz.v.x);  vm.gz = T(v.gz.v.y);
+                        if constexpr (LEVEL >= 2) {
+                            vp.hxx = T(v.hxx.v.x);  vm.hxx = T(v.hxx.v.y);
+                            vp.hxy = T(v.hxy.v.x);  vm.hxy = T(v.hxy.v.y);
+                            vp.hxz = T(v.hxz.v.x);  vm.hxz = T(v.hxz.v.y);
+                            vp.hyy = T(v.hyy.v.x);  vm.hyy = T(v.hyy.v.y);
+                            vp.hyz = T(v.hyz.v.x);  vm.hyz = T(v.hyz.v.y);
+                            vp.hzz = T(v.hzz.v.x);  vm.hzz = T(v.hzz.v.y);
+                        }
+                    } else {
+                        band_eval_pair<T, LEVEL>(in, x, y, x2, y2, xy, vp, vm);
+                        if constexpr (CHAIN) {
+                            to_cartesian<T, LEVEL>(vp, us);
+                            to_cartesian<T, LEVEL>(vm, us);
+                        }
+                    }
+                    store_column(in.kp, vp);
+                    if (in.m > 0) store_column(in.kp - 2 * in.m, vm);
+                };
+
+                // ---- phase B: pairs t = s, s + S, ...
+                auto load = [&](int t) {
+                    PanelDesc d;
+                    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(d.off0), "=r"(d.off1), "=r"(d.off2), "=r"(d.klm)
+                                 : "r"(desc_addr + unsigned(t) * 16u));
+                    const T f = lds_at<T, 0>(f_addr + unsigned(t) * unsigned(sizeof(T)));
+                    return panel_load_pair<T, TPT, LEVEL>(d, f, q_addr, c_addr, s_addr);
+                };
+                int t = s;
+                // two pairs in flight per thread
+                for (; t + S < nq; t += 2 * S) {
+                    const PairInputs<T, LEVEL> in0 = load(t);
+                    const PairInputs<T, LEVEL> in1 = load(t + S);
+                    finish_pair(in0);
+                    finish_pair(in1);
+                }
+                if (t < nq) finish_pair(load(t));
+            }
+
+            // ---- copy-out
+            if (bulk) {
+                fence_proxy_async_smem();  // this thread's image writes, visible to the TMA engine
+                __syncthreads();           // image complete; phase B has finished reading the tables
+                if (packed_rows) {
+                    if (tid < 32) {
+                        auto copy_out = [&](T* gdst, const T* img, int shift, int count) {
+                            const int head = shift == 0 ? 0 : (Q16 - shift < count ? Q16 - shift : count);
+                            const int body = (count - head) / Q16 * Q16;
+                            const int tail = count - head - body;
+                            if (tid < head) gdst[tid] = img[tid];
+                            if (tid >= 8 && tid - 8 < tail) gdst[head + body + tid - 8] = img[head + body + tid - 8];
+                            if (tid == 0 && body > 0)
+                                bulk_store_smem_to_global(gdst + head, img + head, unsigned(body) * unsigned(sizeof(T)));
+                        };
+                        copy_out(gsph, image0, shift0, nvalid * ny);
+                        if constexpr (LEVEL >= 1) copy_out(gd, image1, shift1, nvalid * 3 * ny);
+                        if constexpr (LEVEL >= 2) copy_out(gdd, image2, shift2, nvalid * 9 * ny);
+                    }
+                } else if (tid == 0) {
+                    // every point's row is 16-byte aligned on both sides: one store per point and array
+                    for (int r = 0; r < nvalid; ++r) {
+                        bulk_store_smem_to_global(gsph + size_t(r) * ny, image0 + r * st0, ny_b);
+                        if constexpr (LEVEL >= 1) bulk_store_smem_to_global(gd + size_t(r) * 3 * ny, image1 + r * st1, 3 * ny_b);
+                        if constexpr (LEVEL >= 2) bulk_store_smem_to_global(gdd + size_t(r) * 9 * ny, image2 + r * st2, 9 * ny_b);
+                    }
+                }
                 if (tid == 0) {
                     bulk_commit();
-                    stores_in_flight = true;
+                    ++committed;
+                }
+            } else {
+                __syncthreads();
+                for (int r = 0; r < nvalid; ++r) {
+                    for (int e = tid; e < ny; e += blockDim.x) gsph[size_t(r) * ny + e] = image0[r * st0 + e];
+                    if constexpr (LEVEL >= 1)
+                        for (int e = tid; e < 3 * ny; e += blockDim.x) gd[size_t(r) * 3 * ny + e] = image1[r * st1 + e];
+                    if constexpr (LEVEL >= 2)
+                        for (int e = tid; e < 9 * ny; e += blockDim.x) gdd[size_t(r) * 9 * ny + e] = image2[r * st2 + e];
                 }
             }
-        } else {
-            __syncthreads();
-            for (int e = tid; e < nvalid * ny; e += blockDim.x) gsph[e] = image0[e];
-            if constexpr (LEVEL >= 1)
-                for (int e = tid; e < nvalid * 3 * ny; e += blockDim.x) gd[e] = image1[e];
-            if constexpr (LEVEL >= 2)
-                for (int e = tid; e < nvalid * 9 * ny; e += blockDim.x) gdd[e] = image2[e];
-            __syncthreads();  // images free for the next panel
+            slot = slot + 1 == slots ? 0 : slot + 1;
         }
+        // (the next batch's tables may be written at once: every thread has passed the barrier that
+        // follows phase B of this batch's last panel)
     }
     // shared memory must outlive the engine's reads
-    if (tid == 0 && stores_in_flight) bulk_wait_read_all();
+    if (tid == 0 && committed > 0) bulk_wait_read_all();
 }
 
 }  // namespace sph_b200

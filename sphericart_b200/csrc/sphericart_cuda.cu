@@ -47,9 +47,12 @@ struct Knobs {
     int tile_points;    // force the points per tile of the forward tile kernels (8, 16 or 32)
     int tile_lmax;      // largest l_max served by the tile kernels (default: all they are compiled for)
     int no_panel;       // route what the panel kernels would serve to the band kernel
-    int panel_points;   // force the points per panel (1, 2, 4, 8, 16 or 32)
-    int panel_threads;  // force the threads per CTA of the panel kernels (a multiple of the points, <= 256)
-    int panel_iters;    // panels per CTA of the panel kernels (k > 0), -1: persistent launch
+    int panel_batch;    // force the points per table batch of the panel kernels (1, 2, 4, 8, 16 or 32)
+    int panel_points;   // force the points per panel image (a power of two dividing the batch)
+    int panel_slots;    // force the images per CTA (1..4)
+    int panel_threads;  // force the threads per CTA of the panel kernels (<= 256)
+    int panel_iters;    // table batches per CTA of the panel kernels (k > 0), -1: persistent launch
+    int panel_tables_f64;  // 1: table recurrences of the panel kernels in float64 for float32 outputs too
 };
 
 int env_int(const char* name, int fallback) {
@@ -65,8 +68,9 @@ const Knobs& knobs() {
                             env_int("SPH_B200_TILE_ITERS", 0),  env_int("SPH_B200_VJP_ITERS", 0),
                             env_int("SPH_B200_BAND_ITERS", 0),  env_int("SPH_B200_TILE_POINTS", 0),
                             env_int("SPH_B200_TILE_LMAX", TILE_LMAX), env_int("SPH_B200_NO_PANEL", 0),
-                            env_int("SPH_B200_PANEL_POINTS", 0), env_int("SPH_B200_PANEL_THREADS", 0),
-                            env_int("SPH_B200_PANEL_ITERS", 0)};
+                            env_int("SPH_B200_PANEL_BATCH", 0), env_int("SPH_B200_PANEL_POINTS", 0),
+                            env_int("SPH_B200_PANEL_SLOTS", 0), env_int("SPH_B200_PANEL_THREADS", 0),
+                            env_int("SPH_B200_PANEL_ITERS", 0), env_int("SPH_B200_PANEL_TABLES_F64", 0)};
     return k;
 }
 
@@ -281,69 +285,105 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
 // Panel-kernel plan: points per panel (TP), threads per CTA, shared-memory size. The sizes restate
 // panel_const_bytes / panel_state_bytes / panel_image_bytes of sph_panel.cuh for a run-time element size.
 struct PanelPlan {
-    int tp = 0;        // points per panel
+    int batch = 0;     // TPT: points whose tables are built at once
+    int tp = 0;        // points per panel (image); a power of two dividing batch
+    int slots = 0;     // images per CTA
     int threads = 0;   // threads per CTA; threads / tp slices share each point
     size_t smem = 0;   // dynamic shared memory per CTA
-    int iters = 0;     // panels per CTA (see work_grid() in sph_launch.hpp)
+    int iters = 0;     // table batches per CTA (see work_grid() in sph_launch.hpp)
     bool feasible = false;
 };
 
 constexpr int PANEL_LMAX = 200;  // the descriptors hold l and m in 8 bits and the column in 16
 
-size_t panel_smem_bytes(int l_max, int level, int tp, size_t elem) {
+// Bytes of one panel image: the regions of sph_panel.cuh (panel_region) for a run-time element size.
+size_t panel_image_bytes(int l_max, int level, int tp, size_t elem) {
     const size_t ny = size_t(n_columns(l_max));
-    const size_t nq = size_t(n_table(l_max));
-    const size_t slack = 16 / elem;
-    const size_t consts = band_align16(2 * nq, elem) * elem + nq * 16;
-    const size_t state = band_align16(size_t(tp) * (2 * size_t(l_max + 3) + size_t(4 + (l_max + 1) * l_max / 2 + 5 * (l_max + 1))), elem) * elem;
-    size_t image = band_align16(size_t(tp) * ny, elem) + slack;
-    if (level >= 1) image += band_align16(size_t(tp) * 3 * ny, elem) + slack;
-    if (level >= 2) image += band_align16(size_t(tp) * 9 * ny, elem) + slack;
-    return consts + state + image * elem;
+    const size_t q = 16 / elem;
+    auto stride = [&](size_t comps) {
+        const size_t packed = comps * ny;
+        if (ny % 2 != 0) return packed;
+        return (packed / q) % 2 == 0 ? packed + q : packed;
+    };
+    size_t image = band_align16(size_t(tp) * stride(1), elem) + q;
+    if (level >= 1) image += band_align16(size_t(tp) * stride(3), elem) + q;
+    if (level >= 2) image += band_align16(size_t(tp) * stride(9), elem) + q;
+    return image * elem;
 }
 
-// Chooses the panel shape. What is weighed: warps per SM (latency hiding; beyond about twenty the
-// register file is the limit anyway), how evenly the pairs divide among the slices of a point
-// (a slice evaluates ceil(pairs / slices) pairs), and at least three CTAs per SM so that some compute
-// while the images of others drain through the TMA engine. Ties go to the larger panel (fewer,
-// larger bulk stores).
-PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit) {
+size_t panel_fixed_bytes(int l_max, int batch, size_t elem) {
+    const size_t nq = size_t(n_table(l_max));
+    const size_t consts = band_align16(2 * nq, elem) * elem + nq * 16;
+    const size_t per_point = 4 + 2 * size_t(l_max + 3) + size_t(4 + (l_max + 1) * l_max / 2 + 5 * (l_max + 1));
+    return consts + band_align16(size_t(batch) * per_point, elem) * elem;
+}
+
+// Chooses the panel shape. These kernels are bound by how many image bytes an SM keeps in flight
+// towards HBM (an image drains for microseconds once the memory system is saturated), so the plan
+// first fills the shared memory with images (CTAs per SM x images per CTA x image size, up to about
+// 160 KB), then weighs the warps per SM (latency hiding, up to sixteen), how evenly the pairs divide
+// among the slices of a point and into whole warps, the pairs per thread and panel (each panel costs
+// two barriers and a copy-out), and the share of the threads that the table phase keeps busy
+// (batch x (l_max + 2) / 2 rows pairs). `regs` = registers per thread of the kernel (occupancy).
+PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, int regs) {
     PanelPlan best;
     if (l_max > PANEL_LMAX) return best;
     const int nq = n_table(l_max);
-    const int forced_tp = knobs().panel_points;
-    const int forced_threads = knobs().panel_threads;
+    const bool even_rows = n_columns(l_max) % 2 == 0;
+    if (regs <= 0) regs = level == 2 ? 176 : 64;
+    const int regs_alloc = (regs + 7) / 8 * 8;
+    const Knobs& k = knobs();
     double best_score = -1.0;
-    for (int tp = 32; tp >= 1; tp /= 2) {
-        if (forced_tp > 0 && tp != forced_tp) continue;
-        const size_t smem = panel_smem_bytes(l_max, level, tp, elem);
-        if (smem > smem_limit) continue;
-        for (int threads = 64; threads <= 256; threads += 32) {
-            if (forced_threads > 0 && threads != forced_threads) continue;
-            if (threads % tp != 0) continue;
-            const int slices = threads / tp;
-            if (slices > nq && forced_threads <= 0) continue;
-            // resident CTAs per SM: shared memory (228 KB, 1 KB reserved per CTA), threads, registers (about 96 per thread)
-            long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
-            ctas = std::min<long long>(ctas, 2048 / threads);
-            ctas = std::min<long long>(ctas, 65536 / (96 * threads));
-            if (ctas < 1) continue;
-            const double warps = double(ctas * threads / 32);
-            const double per_slice = double(nq) / slices;
-            const double balance = per_slice / std::ceil(per_slice);
-            const double overlap = ctas >= 3 ? 1.0 : (ctas == 2 ? 0.85 : 0.5);
-            const double score = std::floor(1000.0 * std::min(warps, 20.0) / 20.0 * balance * overlap);
-            if (score > best_score) {
-                best_score = score;
-                best.tp = tp;
-                best.threads = threads;
-                best.smem = smem;
-                best.feasible = true;
+    for (int batch = 32; batch >= 1; batch /= 2) {
+        if (k.panel_batch > 0 && batch != k.panel_batch) continue;
+        const size_t fixed = panel_fixed_bytes(l_max, batch, elem);
+        for (int tp = batch; tp >= 1; tp /= 2) {
+            if (k.panel_points > 0 && tp != k.panel_points) continue;
+            // rows of even length: neighbouring points sit a multiple of 16 bytes apart, which is
+            // conflict-free for up to eight points side by side
+            if (even_rows && tp > 8 && k.panel_points <= 0) continue;
+            const size_t image = panel_image_bytes(l_max, level, tp, elem);
+            for (int slots = 1; slots <= 4; ++slots) {
+                if (k.panel_slots > 0 && slots != k.panel_slots) continue;
+                const size_t smem = fixed + slots * image;
+                if (smem > smem_limit) break;
+                for (int per_slice = 1; per_slice <= nq; ++per_slice) {
+                    const int slices = (nq + per_slice - 1) / per_slice;
+                    int threads = slices * tp;
+                    if (k.panel_threads > 0) threads = k.panel_threads;
+                    if (threads > 256) continue;
+                    if (threads < 64 && k.panel_threads <= 0) break;
+                    if (threads < batch) continue;
+                    const int warp_threads = (threads + 31) / 32 * 32;
+                    long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
+                    ctas = std::min<long long>(ctas, 2048 / warp_threads);
+                    ctas = std::min<long long>(ctas, 65536 / (regs_alloc * warp_threads));
+                    if (ctas < 1) continue;
+                    const int real_slices = threads / tp;
+                    const int real_per_slice = (nq + real_slices - 1) / real_slices;
+                    const double in_flight = std::min<double>(double(ctas * slots) * double(image), 160.0 * 1024) / (160.0 * 1024);
+                    const double warps = std::min<double>(double(ctas * warp_threads / 32), 16.0) / 16.0;
+                    const double balance = double(nq) / (double(real_slices) * real_per_slice) * threads / warp_threads;
+                    const double panel_cost = real_per_slice / (real_per_slice + 0.5);
+                    const double table_busy = std::min(1.0, double(batch) * ((l_max + 2) / 2) / threads);
+                    const double score = in_flight * warps * balance * panel_cost * (0.7 + 0.3 * table_busy) *
+                                         (ctas >= 2 ? 1.0 : 0.8);
+                    if (score > best_score + 1e-9) {
+                        best_score = score;
+                        best.batch = batch;
+                        best.tp = tp;
+                        best.slots = slots;
+                        best.threads = threads;
+                        best.smem = smem;
+                        best.feasible = true;
+                    }
+                    if (k.panel_threads > 0) break;
+                }
             }
         }
     }
-    // Each CTA stages the tables and descriptors once; a few panels per CTA amortise that.
-    best.iters = resolve_iters(knobs().panel_iters, 4);
+    // Each CTA stages the constants once; a few table batches per CTA amortise that.
+    best.iters = resolve_iters(k.panel_iters, 4);
     return best;
 }
 
@@ -404,12 +444,14 @@ void band_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int
     d_tables = device_tables(st, host_tables, l_max, device);
 }
 
+template <typename T> int panel_registers(int level, bool normalized);
+
 template <typename T>
-void panel_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int level, int device, size_t smem_limit,
-                     const PanelPlan*& plan, const T*& d_tables) {
+void panel_resources(CalculatorState<T>& st, const T* host_tables, int l_max, int level, bool normalized, int device,
+                     size_t smem_limit, const PanelPlan*& plan, const T*& d_tables) {
     std::lock_guard<std::mutex> lock(st.mutex);
     if (!st.panel_plan_ready[level]) {
-        st.panel_plans[level] = make_panel_plan(l_max, level, sizeof(T), smem_limit);
+        st.panel_plans[level] = make_panel_plan(l_max, level, sizeof(T), smem_limit, panel_registers<T>(level, normalized));
         st.panel_plan_ready[level] = true;
     }
     plan = &st.panel_plans[level];
@@ -498,6 +540,26 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
                                                    iters, device, stream);
         return cudaErrorInvalidValue;
     }
+    static cudaError_t selected(int l_max, bool normalized, const T* xyz, long long n, T* out, const T* tables,
+                                const Selection& selection, bool use_bulk, int device, cudaStream_t stream) {
+        if (l_max == LMAX)
+            return TileLaunch<T, LMAX>::selected(normalized, xyz, n, out, tables, selection, use_bulk, device, stream);
+        if constexpr (LMAX > 0)
+            return TileDispatch<T, LMAX - 1>::selected(l_max, normalized, xyz, n, out, tables, selection, use_bulk, device,
+                                                       stream);
+        return cudaErrorInvalidValue;
+    }
+    static cudaError_t selected_vjp(int l_max, bool normalized, const T* xyz, const T* out_grad, long long n,
+                                    T* xyz_grad, const T* tables, const Selection& selection, int device,
+                                    cudaStream_t stream) {
+        if (l_max == LMAX)
+            return TileLaunch<T, LMAX>::selected_vjp(normalized, xyz, out_grad, n, xyz_grad, tables, selection, device,
+                                                     stream);
+        if constexpr (LMAX > 0)
+            return TileDispatch<T, LMAX - 1>::selected_vjp(l_max, normalized, xyz, out_grad, n, xyz_grad, tables,
+                                                           selection, device, stream);
+        return cudaErrorInvalidValue;
+    }
     static int error_flags() {
         int flag = TileLaunch<T, LMAX>::device_error_flag();
         if constexpr (LMAX > 0) {
@@ -507,6 +569,9 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return flag;
     }
 };
+
+// Registers per thread of the panel kernels (they barely depend on the batch size; 8 is queried).
+template <typename T> int panel_registers(int level, bool normalized) { return PanelLaunch<T, 8>::registers(level, normalized); }
 
 template <typename T>
 cudaError_t panel_dispatch(int tp, int level, bool normalized, const PanelLaunchArgs<T>& a, int device, cudaStream_t stream) {
@@ -627,7 +692,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
     if (kind <= 2 && knobs().no_panel == 0 && !force_band) {
         const PanelPlan* pplan = nullptr;
         const T* d_tables = nullptr;
-        panel_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, pplan, d_tables);
+        panel_resources(st, host_tables, l_max, kind, normalized, scope.device, props.smem_optin, pplan, d_tables);
         if (pplan->feasible) {
             PanelLaunchArgs<T> a{};
             a.xyz = xyz;
@@ -638,11 +703,17 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             a.d_tables = d_tables;
             a.d_desc = reinterpret_cast<const unsigned char*>(d_tables) + desc_offset_bytes<T>(l_max);
             a.l_max = l_max;
-            a.bulk = knobs().no_bulk != 0 ? 0 : 1;
+            // bulk copy-out: rows of odd length go out as one span per array from an image placed at the
+            // span's own alignment; rows of even length go out point by point and need 16-byte aligned arrays
+            const bool aligned_out = aligned16(sph) && (kind < 1 || aligned16(dsph)) && (kind < 2 || aligned16(ddsph));
+            a.bulk = (knobs().no_bulk != 0 || (n_columns(l_max) % 2 == 0 && !aligned_out)) ? 0 : 1;
+            a.tp = pplan->tp;
+            a.slots = pplan->slots;
+            a.tables_f64 = knobs().panel_tables_f64;
             a.threads = pplan->threads;
             a.smem = pplan->smem;
             a.iters = pplan->iters;
-            check(panel_dispatch<T>(pplan->tp, kind, normalized, a, scope.device, stream), "panel kernel launch");
+            check(panel_dispatch<T>(pplan->batch, kind, normalized, a, scope.device, stream), "panel kernel launch");
             return;
         }
     }
@@ -657,6 +728,69 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         band_launch_args<T>(*plan, l_max, d_tables, xyz, n, sph, dsph, ddsph, sph_grad, dsph_grad, xyz_grad);
     check(band_dispatch<T>(plan->lanes, kind == 3 ? 1 : (kind == 4 ? 2 : kind), vjp, normalized, a, scope.device, stream),
           "band kernel launch");
+}
+
+// Selected degree blocks (values when out_grad is null, the fused VJP otherwise).
+template <typename T>
+void run_selected(size_t l_max_, bool normalized, const T* host_tables, const T* xyz, size_t n_samples,
+                  const int* l_list, size_t n_l, const int* axis_order, const T* scales, T* out, const T* out_grad,
+                  T* xyz_grad, void* cuda_stream) {
+    const int l_max = int(l_max_);
+    if (l_max > TILE_LMAX) {
+        throw std::runtime_error("sphericart::cuda: selected outputs are served for l_max <= " + std::to_string(TILE_LMAX) +
+                                 "; got l_max = " + std::to_string(l_max));
+    }
+    if (l_list == nullptr || n_l == 0) throw std::runtime_error("sphericart::cuda: l_list is empty");
+    Selection sel{};
+    for (int l = 0; l <= TILE_LMAX; ++l) {
+        sel.dest[l] = -1;
+        sel.scale[l] = 1.0;
+    }
+    int column = 0;
+    for (size_t j = 0; j < n_l; ++j) {
+        const int l = l_list[j];
+        if (l < 0 || l > l_max) {
+            throw std::runtime_error("sphericart::cuda: l_list holds " + std::to_string(l) +
+                                     ", outside 0 ... l_max = " + std::to_string(l_max));
+        }
+        if (sel.dest[l] >= 0) throw std::runtime_error("sphericart::cuda: l_list holds " + std::to_string(l) + " twice");
+        sel.dest[l] = column;
+        sel.scale[l] = scales != nullptr ? double(scales[j]) : 1.0;
+        column += 2 * l + 1;
+    }
+    sel.ny_out = column;
+    for (int a = 0; a < 3; ++a) sel.axis[a] = axis_order != nullptr ? axis_order[a] : a;
+    const bool permutation = ((1 << sel.axis[0]) | (1 << sel.axis[1]) | (1 << sel.axis[2])) == 7 && sel.axis[0] >= 0 &&
+                             sel.axis[1] >= 0 && sel.axis[2] >= 0 && sel.axis[0] <= 2 && sel.axis[1] <= 2 && sel.axis[2] <= 2;
+    if (!permutation) throw std::runtime_error("sphericart::cuda: axis_order must be a permutation of 0, 1, 2");
+    if (n_samples == 0) return;
+    if (xyz == nullptr) throw std::runtime_error("sphericart::cuda: xyz is a null pointer");
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    DeviceScope scope(xyz);
+    if (out_grad == nullptr) {
+        if (out == nullptr) throw std::runtime_error("sphericart::cuda: out is a null pointer");
+        check(TileDispatch<T>::selected(l_max, normalized, xyz, (long long)n_samples, out, host_tables, sel,
+                                        aligned16(out) && knobs().no_bulk == 0, scope.device, stream),
+              "selected kernel launch");
+    } else {
+        if (xyz_grad == nullptr) throw std::runtime_error("sphericart::cuda: xyz_grad is a null pointer");
+        check(TileDispatch<T>::selected_vjp(l_max, normalized, xyz, out_grad, (long long)n_samples, xyz_grad, host_tables,
+                                            sel, scope.device, stream),
+              "selected VJP kernel launch");
+    }
+}
+
+// The kernel family run() picks for a call of this kind; mirrors the order of the tests in run().
+const char* kernel_family(int kind, int l_max, int elem_bytes, size_t smem_limit) {
+    const bool force_band = knobs().force_band != 0;
+    if (tile_serves(kind, l_max, elem_bytes) && l_max <= knobs().tile_lmax && !force_band) {
+        return kind == 3 ? "sph_vjp_tile_kernel" : (kind == 4 ? "sph_vjp2_tile_kernel" : "sph_tile_kernel");
+    }
+    if (kind <= 2 && knobs().no_panel == 0 && !force_band &&
+        make_panel_plan(l_max, kind, size_t(elem_bytes), smem_limit, 0).feasible) {
+        return "sph_panel_kernel";
+    }
+    return "sph_band_kernel";
 }
 
 }  // namespace sph_b200
@@ -762,6 +896,25 @@ void SphericalHarmonics<T>::compute_vjp_with_gradients(
                      n_samples, nullptr, nullptr, nullptr, sph_grad, dsph_grad, xyz_grad, cuda_stream);
 }
 
+template <typename T>
+void SphericalHarmonics<T>::compute_selected(
+    const T* xyz, const size_t n_samples, const int* l_list, const size_t n_l, const int* axis_order, const T* scales,
+    T* out, void* cuda_stream
+) {
+    sph_b200::run_selected<T>(this->l_max, this->normalized, this->prefactors_cpu, xyz, n_samples, l_list, n_l, axis_order,
+                              scales, out, nullptr, nullptr, cuda_stream);
+}
+
+template <typename T>
+void SphericalHarmonics<T>::compute_selected_vjp(
+    const T* xyz, const size_t n_samples, const int* l_list, const size_t n_l, const int* axis_order, const T* scales,
+    const T* out_grad, T* xyz_grad, void* cuda_stream
+) {
+    if (n_samples != 0 && out_grad == nullptr) throw std::runtime_error("sphericart::cuda: out_grad is a null pointer");
+    sph_b200::run_selected<T>(this->l_max, this->normalized, this->prefactors_cpu, xyz, n_samples, l_list, n_l, axis_order,
+                              scales, nullptr, out_grad, xyz_grad, cuda_stream);
+}
+
 template <typename T> SolidHarmonics<T>::SolidHarmonics(size_t l_max) : SphericalHarmonics<T>(l_max) {
     this->normalized = false;
 }
@@ -855,6 +1008,12 @@ void vjp_call(Calculator* c, const T* xyz, size_t n, const T* sph_grad, T* xyz_g
 
 extern "C" const char* sphericart_cuda_last_error(void) { return g_last_error.c_str(); }
 
+extern "C" const char* sphericart_cuda_kernel_family(int kind, size_t l_max, int elem_bytes) {
+    if (kind < 0 || kind > 4 || (elem_bytes != 4 && elem_bytes != 8)) return "";
+    // the largest dynamic shared memory a CTA may ask for on sm_100 (227 KB); the planning rule needs it
+    return sph_b200::kernel_family(kind, int(l_max), elem_bytes, size_t(232448));
+}
+
 extern "C" int sphericart_cuda_device_wait_errors(void) {
     const int f = sph_b200::TileDispatch<float>::error_flags();
     const int d = sph_b200::TileDispatch<double>::error_flags();
@@ -912,6 +1071,32 @@ extern "C" int sphericart_cuda_device_wait_errors(void) {
         const T* sph_grad, const T* dsph_grad, T* xyz_grad, void* cuda_stream) {                                    \
         return capi_try([&] { vjp2_call(calculator, xyz, n_samples, sph_grad, dsph_grad, xyz_grad, cuda_stream); }); \
     }
+
+#define SPH_CAPI_SELECTED(KIND, SFX, T)                                                                              \
+    extern "C" int sphericart_cuda_##KIND##_harmonics_compute_selected##SFX(                                        \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples,         \
+        const int* l_list, size_t n_l, const int* axis_order, const T* scales, T* out, void* cuda_stream) {         \
+        return capi_try([&] {                                                                                       \
+            if (calculator == nullptr) throw std::runtime_error("sphericart::cuda: calculator is a null pointer");  \
+            calculator->compute_selected(xyz, n_samples, l_list, n_l, axis_order, scales, out, cuda_stream);        \
+        });                                                                                                         \
+    }                                                                                                               \
+    extern "C" int sphericart_cuda_##KIND##_harmonics_compute_selected_vjp##SFX(                                    \
+        sphericart_cuda_##KIND##_harmonics_calculator##SFX##_t* calculator, const T* xyz, size_t n_samples,         \
+        const int* l_list, size_t n_l, const int* axis_order, const T* scales, const T* out_grad, T* xyz_grad,      \
+        void* cuda_stream) {                                                                                        \
+        return capi_try([&] {                                                                                       \
+            if (calculator == nullptr) throw std::runtime_error("sphericart::cuda: calculator is a null pointer");  \
+            calculator->compute_selected_vjp(xyz, n_samples, l_list, n_l, axis_order, scales, out_grad, xyz_grad,   \
+                                             cuda_stream);                                                          \
+        });                                                                                                         \
+    }
+
+SPH_CAPI_SELECTED(spherical, , double)
+SPH_CAPI_SELECTED(spherical, _f, float)
+SPH_CAPI_SELECTED(solid, , double)
+SPH_CAPI_SELECTED(solid, _f, float)
+#undef SPH_CAPI_SELECTED
 
 SPH_CAPI_FAMILY(spherical, , double)
 SPH_CAPI_FAMILY(spherical, _f, float)

@@ -1,6 +1,7 @@
 // Instantiates the tile kernels for one (type, l_max) pair: compile with
 //   -DSPH_T=float|double -DSPH_LMAX=0..20
 #include "sph_launch.hpp"
+#include "sph_select.cuh"
 #include "sph_tile.cuh"
 
 #include <atomic>
@@ -129,6 +130,58 @@ cudaError_t launch_vjp2(const T* xyz, const T* sph_grad, const T* dsph_grad, lon
     return cudaGetLastError();
 }
 
+template <typename T, int LMAX> SelectMap<T, LMAX> make_select_map(const Selection& selection) {
+    SelectMap<T, LMAX> map;
+    for (int l = 0; l <= LMAX; ++l) {
+        map.dest[l] = selection.dest[l];
+        map.scale[l] = T(selection.scale[l]);
+    }
+    map.ny_out = selection.ny_out;
+    for (int a = 0; a < 3; ++a) map.axis[a] = selection.axis[a];
+    return map;
+}
+
+// Warps per CTA of the selected kernels: up to four, fewer when the packed images are large.
+template <typename T> int select_warps(int ny_out, int device, size_t& smem_per_warp) {
+    smem_per_warp = size_t(TILE_POINTS) * select_row_stride(ny_out) * sizeof(T);
+    int warps = 4;
+    while (warps > 1 && warps * smem_per_warp > size_t(100) * 1024) --warps;
+    (void)device;
+    return warps;
+}
+
+template <typename T, int LMAX, bool NORM>
+cudaError_t launch_selected(const T* xyz, long long n, T* out, const T* host_tables, const Selection& selection,
+                            bool use_bulk, int device, cudaStream_t stream) {
+    auto kernel = sph_select_kernel<T, LMAX, NORM>;
+    size_t per_warp = 0;
+    const int warps = select_warps<T>(selection.ny_out, device, per_warp);
+    const size_t smem = warps * per_warp;
+    const int max_blocks = memo_grid<sph_select_kernel<T, LMAX, NORM>>(warps * 32, smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const int grid = work_grid((ntiles + warps - 1) / warps, max_blocks, /*iters=*/2);
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, n, out, make_tables<T, LMAX>(host_tables),
+                                               make_select_map<T, LMAX>(selection), use_bulk ? 1 : 0);
+    return cudaGetLastError();
+}
+
+template <typename T, int LMAX, bool NORM>
+cudaError_t launch_selected_vjp(const T* xyz, const T* out_grad, long long n, T* xyz_grad, const T* host_tables,
+                                const Selection& selection, int device, cudaStream_t stream) {
+    auto kernel = sph_select_vjp_kernel<T, LMAX, NORM>;
+    size_t per_warp = 0;
+    const int warps = select_warps<T>(selection.ny_out, device, per_warp);
+    const size_t smem = warps * per_warp;
+    const int max_blocks = memo_grid<sph_select_vjp_kernel<T, LMAX, NORM>>(warps * 32, smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const int grid = work_grid((ntiles + warps - 1) / warps, max_blocks, /*iters=*/1);
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, out_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables),
+                                               make_select_map<T, LMAX>(selection));
+    return cudaGetLastError();
+}
+
 template <typename T, int LMAX, int LEVEL> constexpr bool tile_fits() { return tile_serves(LEVEL, LMAX, int(sizeof(T))); }
 
 }  // namespace
@@ -187,6 +240,22 @@ cudaError_t TileLaunch<T, LMAX>::vjp2(bool normalized, const T* xyz, const T* sp
     } else {
         return cudaErrorInvalidConfiguration;
     }
+}
+
+template <typename T, int LMAX>
+cudaError_t TileLaunch<T, LMAX>::selected(bool normalized, const T* xyz, long long n, T* out, const T* host_tables,
+                                          const Selection& selection, bool use_bulk, int device, cudaStream_t stream) {
+    return normalized ? launch_selected<T, LMAX, true>(xyz, n, out, host_tables, selection, use_bulk, device, stream)
+                      : launch_selected<T, LMAX, false>(xyz, n, out, host_tables, selection, use_bulk, device, stream);
+}
+
+template <typename T, int LMAX>
+cudaError_t TileLaunch<T, LMAX>::selected_vjp(bool normalized, const T* xyz, const T* out_grad, long long n, T* xyz_grad,
+                                              const T* host_tables, const Selection& selection, int device,
+                                              cudaStream_t stream) {
+    return normalized
+               ? launch_selected_vjp<T, LMAX, true>(xyz, out_grad, n, xyz_grad, host_tables, selection, device, stream)
+               : launch_selected_vjp<T, LMAX, false>(xyz, out_grad, n, xyz_grad, host_tables, selection, device, stream);
 }
 
 template <typename T, int LMAX> int TileLaunch<T, LMAX>::device_error_flag() {

@@ -189,6 +189,65 @@ class _BaseHarmonics:
             raise RuntimeError(_c_lib.last_error())
         return xyz_grad
 
+    def _selection_args(self, l_list, axis_order, scales, dtype):
+        import ctypes
+
+        degrees = [int(l) for l in l_list]
+        if not degrees:
+            raise ValueError("l_list must name at least one degree")
+        if len(set(degrees)) != len(degrees) or min(degrees) < 0 or max(degrees) > self._l_max:
+            raise ValueError(f"l_list must hold distinct degrees between 0 and l_max = {self._l_max}, got {degrees}")
+        axis = [0, 1, 2] if axis_order is None else [int(a) for a in axis_order]
+        if sorted(axis) != [0, 1, 2]:
+            raise ValueError("axis_order must be a permutation of (0, 1, 2)")
+        ctype = ctypes.c_double if dtype == torch.float64 else ctypes.c_float
+        c_scales = None
+        if scales is not None:
+            if len(scales) != len(degrees):
+                raise ValueError("scales must hold one factor per listed degree")
+            c_scales = (ctype * len(degrees))(*[float(v) for v in scales])
+        c_l = (ctypes.c_int * len(degrees))(*degrees)
+        c_axis = (ctypes.c_int * 3)(*axis)
+        return degrees, c_l, c_axis, c_scales, sum(2 * l + 1 for l in degrees)
+
+    def compute_selected(self, xyz, l_list, axis_order=None, scales=None, out=None) -> torch.Tensor:
+        """Values of the listed degree blocks only, ``(n_samples, sum(2l+1))``, in one kernel: block ``l`` of
+        the output is ``scales[j] * Y_l`` for ``l = l_list[j]``, evaluated at points whose columns
+        ``axis_order`` hold (x, y, z). What the reference's e3nn adaptor composes from a full evaluation, a
+        slice, a permutation and a multiplication (``sphericart-torch/python/sphericart/torch/e3nn.py:47-80``).
+        Needs ``l_max <= 20``."""
+        xyz = self._validate_xyz(xyz)
+        n = xyz.shape[0]
+        _, c_l, c_axis, c_scales, ny_out = self._selection_args(l_list, axis_order, scales, xyz.dtype)
+        res = (torch.empty((n, ny_out), dtype=xyz.dtype, device=xyz.device) if out is None
+               else self._validate_out(out, xyz, [(n, ny_out)], names=("out",))[0])
+        stream = torch.cuda.current_stream(xyz.device).cuda_stream
+        sfx = "" if xyz.dtype == torch.float64 else "_f"
+        status = getattr(self._lib, f"{self._prefix}_compute_selected{sfx}")(
+            self._calculator(xyz.dtype), _ptr(xyz), n, c_l, len(c_l), c_axis, c_scales, _ptr(res), stream)
+        if status != 0:
+            raise RuntimeError(_c_lib.last_error())
+        return res
+
+    def compute_selected_vjp(self, xyz, out_grad, l_list, axis_order=None, scales=None, out=None) -> torch.Tensor:
+        """Fused backward of :meth:`compute_selected`: ``out_grad`` is ``(n_samples, sum(2l+1))`` in the packed
+        layout; returns ``(n_samples, 3)`` in the caller's axis order."""
+        xyz = self._validate_xyz(xyz)
+        n = xyz.shape[0]
+        _, c_l, c_axis, c_scales, ny_out = self._selection_args(l_list, axis_order, scales, xyz.dtype)
+        if out_grad.shape != (n, ny_out) or out_grad.dtype != xyz.dtype or out_grad.device != xyz.device:
+            raise ValueError("out_grad must match xyz in dtype and device and have shape (n_samples, sum(2l+1))")
+        out_grad = out_grad.detach().contiguous()
+        res = (torch.empty((n, 3), dtype=xyz.dtype, device=xyz.device) if out is None
+               else self._validate_out(out, xyz, [(n, 3)], names=("xyz_grad",))[0])
+        stream = torch.cuda.current_stream(xyz.device).cuda_stream
+        sfx = "" if xyz.dtype == torch.float64 else "_f"
+        status = getattr(self._lib, f"{self._prefix}_compute_selected_vjp{sfx}")(
+            self._calculator(xyz.dtype), _ptr(xyz), n, c_l, len(c_l), c_axis, c_scales, _ptr(out_grad), _ptr(res), stream)
+        if status != 0:
+            raise RuntimeError(_c_lib.last_error())
+        return res
+
     def forward(self, xyz) -> torch.Tensor:
         """Values with autograd support: the backward pass is the fused VJP kernel."""
         return _HarmonicsFunction.apply(xyz, self)

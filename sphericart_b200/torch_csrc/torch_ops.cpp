@@ -8,6 +8,10 @@
 //   {spherical,solid}_harmonics_with_hessians(Tensor xyz, int l_max) -> (Tensor, Tensor, Tensor)
 //   {spherical,solid}_harmonics_vjp(Tensor xyz, Tensor sph_grad, int l_max) -> Tensor
 //   {spherical,solid}_harmonics_vjp_with_gradients(Tensor xyz, Tensor? sph_grad, Tensor dsph_grad, int l_max) -> Tensor
+//   {spherical,solid}_harmonics_selected(Tensor xyz, int[] l_list, int[] axis_order, float[] scales) -> Tensor
+//   {spherical,solid}_harmonics_selected_vjp(Tensor xyz, Tensor out_grad, int[] l_list, int[] axis_order, float[] scales) -> Tensor
+//     (chosen degree blocks only, packed, scaled, input axes permuted: what the reference's e3nn adaptor,
+//      sphericart-torch/python/sphericart/torch/e3nn.py:47-80, composes from four tensor expressions)
 //
 // Differences from the reference's operator layer (sphericart-torch/src/torch.cpp:117-143,340-349):
 //  * only the CUDA dispatch key is implemented; a CPU tensor finds no kernel and the dispatcher
@@ -38,6 +42,7 @@
 #include <memory>
 #include <mutex>
 #include <tuple>
+#include <vector>
 
 #include "sphericart_cuda.hpp"
 
@@ -142,6 +147,64 @@ at::Tensor vjp_with_gradients(const at::Tensor& xyz_in, const c10::optional<at::
             dsph_grad.data_ptr<scalar_t>(), out.data_ptr<scalar_t>(), stream);
     });
     return out;
+}
+
+// Selected degree blocks: l_max of the calculator = the largest listed degree.
+struct SelectionArgs {
+    std::vector<int> degrees;
+    int axis[3];
+    int64_t l_max = 0, ny_out = 0;
+};
+
+SelectionArgs checked_selection(at::IntArrayRef l_list, at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    SelectionArgs sel;
+    TORCH_CHECK(!l_list.empty(), "l_list must name at least one degree");
+    TORCH_CHECK(scales.empty() || scales.size() == l_list.size(), "scales must hold one factor per listed degree");
+    TORCH_CHECK(axis_order.size() == 3, "axis_order must hold three entries");
+    for (int64_t l : l_list) {
+        TORCH_CHECK(l >= 0, "degrees must not be negative, got ", l);
+        sel.degrees.push_back(int(l));
+        sel.l_max = std::max<int64_t>(sel.l_max, l);
+        sel.ny_out += 2 * l + 1;
+    }
+    for (int a = 0; a < 3; ++a) sel.axis[a] = int(axis_order[a]);
+    return sel;
+}
+
+template <bool NORMALIZED>
+at::Tensor selected(const at::Tensor& xyz_in, at::IntArrayRef l_list, at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    const SelectionArgs sel = checked_selection(l_list, axis_order, scales);
+    const at::Tensor xyz = checked_points(xyz_in, sel.l_max);
+    const int64_t n = xyz.size(0);
+    const c10::cuda::CUDAGuard guard(xyz.device());
+    void* stream = c10::cuda::getCurrentCUDAStream(xyz.device().index()).stream();
+    at::Tensor out = at::empty({n, sel.ny_out}, xyz.options());
+    AT_DISPATCH_FLOATING_TYPES(xyz.scalar_type(), "sphericart_b200_selected", [&] {
+        std::vector<scalar_t> factors(scales.begin(), scales.end());
+        calculator<Calculator<NORMALIZED, scalar_t>>(sel.l_max).compute_selected(
+            xyz.data_ptr<scalar_t>(), size_t(n), sel.degrees.data(), sel.degrees.size(), sel.axis,
+            factors.empty() ? nullptr : factors.data(), out.data_ptr<scalar_t>(), stream);
+    });
+    return out;
+}
+
+template <bool NORMALIZED>
+at::Tensor selected_vjp(const at::Tensor& xyz_in, const at::Tensor& out_grad_in, at::IntArrayRef l_list,
+                        at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    const SelectionArgs sel = checked_selection(l_list, axis_order, scales);
+    const at::Tensor xyz = checked_points(xyz_in, sel.l_max);
+    const int64_t n = xyz.size(0);
+    const at::Tensor out_grad = checked_like(out_grad_in, xyz, {n, sel.ny_out}, "out_grad");
+    const c10::cuda::CUDAGuard guard(xyz.device());
+    void* stream = c10::cuda::getCurrentCUDAStream(xyz.device().index()).stream();
+    at::Tensor xyz_grad = at::empty({n, 3}, xyz.options());
+    AT_DISPATCH_FLOATING_TYPES(xyz.scalar_type(), "sphericart_b200_selected_vjp", [&] {
+        std::vector<scalar_t> factors(scales.begin(), scales.end());
+        calculator<Calculator<NORMALIZED, scalar_t>>(sel.l_max).compute_selected_vjp(
+            xyz.data_ptr<scalar_t>(), size_t(n), sel.degrees.data(), sel.degrees.size(), sel.axis,
+            factors.empty() ? nullptr : factors.data(), out_grad.data_ptr<scalar_t>(), xyz_grad.data_ptr<scalar_t>(), stream);
+    });
+    return xyz_grad;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -274,6 +337,49 @@ template <bool NORMALIZED> struct HessiansFunction : torch::autograd::Function<H
     }
 };
 
+template <bool NORMALIZED>
+at::Tensor call_selected(const at::Tensor& xyz, at::IntArrayRef l_list, at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    static auto op = c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("_selected").c_str(), "")
+                         .template typed<at::Tensor(const at::Tensor&, at::IntArrayRef, at::IntArrayRef, at::ArrayRef<double>)>();
+    return op.call(xyz, l_list, axis_order, scales);
+}
+template <bool NORMALIZED>
+at::Tensor call_selected_vjp(const at::Tensor& xyz, const at::Tensor& out_grad, at::IntArrayRef l_list,
+                             at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    static auto op =
+        c10::Dispatcher::singleton().findSchemaOrThrow(op_name<NORMALIZED>("_selected_vjp").c_str(), "")
+            .template typed<at::Tensor(const at::Tensor&, const at::Tensor&, at::IntArrayRef, at::IntArrayRef, at::ArrayRef<double>)>();
+    return op.call(xyz, out_grad, l_list, axis_order, scales);
+}
+
+// selected values -> the fused selected VJP (first order only: the VJP operator itself is not differentiable)
+template <bool NORMALIZED> struct SelectedFunction : torch::autograd::Function<SelectedFunction<NORMALIZED>> {
+    static at::Tensor forward(AutogradContext* ctx, const at::Tensor& xyz, at::IntArrayRef l_list,
+                              at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        ctx->save_for_backward({xyz});
+        ctx->saved_data["l_list"] = l_list.vec();
+        ctx->saved_data["axis_order"] = axis_order.vec();
+        ctx->saved_data["scales"] = scales.vec();
+        ctx->set_materialize_grads(false);
+        return call_selected<NORMALIZED>(xyz, l_list, axis_order, scales);
+    }
+    static variable_list backward(AutogradContext* ctx, variable_list grads) {
+        if (!grads[0].defined()) return {at::Tensor(), at::Tensor(), at::Tensor(), at::Tensor()};
+        const auto saved = ctx->get_saved_variables();
+        const std::vector<int64_t> l_list = ctx->saved_data["l_list"].toIntVector();
+        const std::vector<int64_t> axis_order = ctx->saved_data["axis_order"].toIntVector();
+        const std::vector<double> scales = ctx->saved_data["scales"].toDoubleVector();
+        return {call_selected_vjp<NORMALIZED>(saved[0], grads[0].contiguous(), l_list, axis_order, scales), at::Tensor(),
+                at::Tensor(), at::Tensor()};
+    }
+};
+
+template <bool NORMALIZED>
+at::Tensor selected_autograd(const at::Tensor& xyz, at::IntArrayRef l_list, at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    return SelectedFunction<NORMALIZED>::apply(xyz, l_list, axis_order, scales);
+}
+
 template <bool NORMALIZED> at::Tensor values_autograd(const at::Tensor& xyz, int64_t l_max) {
     return ValuesFunction<NORMALIZED>::apply(xyz, l_max);
 }
@@ -300,6 +406,8 @@ TORCH_LIBRARY(sphericart_b200, m) {
         m.def((p + "_with_hessians(Tensor xyz, int l_max) -> (Tensor, Tensor, Tensor)").c_str());
         m.def((p + "_vjp(Tensor xyz, Tensor sph_grad, int l_max) -> Tensor").c_str());
         m.def((p + "_vjp_with_gradients(Tensor xyz, Tensor? sph_grad, Tensor dsph_grad, int l_max) -> Tensor").c_str());
+        m.def((p + "_selected(Tensor xyz, int[] l_list, int[] axis_order, float[] scales) -> Tensor").c_str());
+        m.def((p + "_selected_vjp(Tensor xyz, Tensor out_grad, int[] l_list, int[] axis_order, float[] scales) -> Tensor").c_str());
     }
 }
 
@@ -309,6 +417,10 @@ TORCH_LIBRARY_IMPL(sphericart_b200, CUDA, m) {
     m.impl("spherical_harmonics_with_hessians", &with_hessians<true>);
     m.impl("spherical_harmonics_vjp", &vjp<true>);
     m.impl("spherical_harmonics_vjp_with_gradients", &vjp_with_gradients<true>);
+    m.impl("spherical_harmonics_selected", &selected<true>);
+    m.impl("spherical_harmonics_selected_vjp", &selected_vjp<true>);
+    m.impl("solid_harmonics_selected", &selected<false>);
+    m.impl("solid_harmonics_selected_vjp", &selected_vjp<false>);
     m.impl("solid_harmonics", &values<false>);
     m.impl("solid_harmonics_with_gradients", &with_gradients<false>);
     m.impl("solid_harmonics_with_hessians", &with_hessians<false>);
@@ -322,6 +434,10 @@ TORCH_LIBRARY_IMPL(sphericart_b200, Autograd, m) {
     m.impl("spherical_harmonics_with_hessians", &with_hessians_autograd<true>);
     m.impl("spherical_harmonics_vjp", &vjp_autograd<true>);
     m.impl("spherical_harmonics_vjp_with_gradients", torch::autograd::autogradNotImplementedFallback());
+    m.impl("spherical_harmonics_selected", &selected_autograd<true>);
+    m.impl("spherical_harmonics_selected_vjp", torch::autograd::autogradNotImplementedFallback());
+    m.impl("solid_harmonics_selected", &selected_autograd<false>);
+    m.impl("solid_harmonics_selected_vjp", torch::autograd::autogradNotImplementedFallback());
     m.impl("solid_harmonics", &values_autograd<false>);
     m.impl("solid_harmonics_with_gradients", &with_gradients_autograd<false>);
     m.impl("solid_harmonics_with_hessians", &with_hessians_autograd<false>);

@@ -66,6 +66,14 @@ def _register_fakes(prefix):
     def _(xyz, sph_grad, dsph_grad, l_max):
         return xyz.new_empty((xyz.shape[0], 3))
 
+    @torch.library.register_fake(f"{_NS}::{prefix}_selected")
+    def _(xyz, l_list, axis_order, scales):
+        return xyz.new_empty((xyz.shape[0], sum(2 * l + 1 for l in l_list)))
+
+    @torch.library.register_fake(f"{_NS}::{prefix}_selected_vjp")
+    def _(xyz, out_grad, l_list, axis_order, scales):
+        return xyz.new_empty((xyz.shape[0], 3))
+
 
 def _register_vmap(prefix):
     # a function of one point, vmapped over the points: the batch is the operator's own first axis
@@ -146,35 +154,43 @@ class SolidHarmonics(torch.nn.Module):
         return self._l_max
 
 
+# largest degree the compile-time kernels behind the `*_selected` operators cover
+_SELECTED_LMAX = 20
+
+
 def e3nn_spherical_harmonics(l_list, x: torch.Tensor, normalize: bool = False, normalization: str = "integral"):
     """Harmonics in the conventions of ``e3nn.o3.spherical_harmonics``: the function the reference
     offers in ``sphericart-torch/python/sphericart/torch/e3nn.py:10-80``, for CUDA tensors.
 
-    ``l_list``: one degree or a list of degrees (everything up to the largest is evaluated, the
-    listed blocks are returned in the listed order); ``x``: ``(n, 3)`` points with e3nn's axis order
-    (y, z, x in this library's terms); ``normalize``: spherical (True) or solid (False) harmonics;
-    ``normalization``: "integral" (this library's), "component" (times sqrt(4 pi)) or "norm" (times
-    sqrt(4 pi / (2 l + 1))). Axis permutation, scaling and block selection are one gather of the
-    input and one indexed multiply of the output; autograd flows through the operators."""
+    ``l_list``: one degree or a list of degrees, returned in the listed order; ``x``: ``(n, 3)`` points
+    with e3nn's axis order (y, z, x in this library's terms); ``normalize``: spherical (True) or solid
+    (False) harmonics; ``normalization``: "integral" (this library's), "component" (times sqrt(4 pi)) or
+    "norm" (times sqrt(4 pi / (2 l + 1))).
+
+    One kernel writes the listed blocks, scaled, from the points as they are (the axis permutation is
+    part of the kernel's load); its backward pass is one fused kernel as well. The reference evaluates
+    every degree and then slices, permutes and rescales. Lists the kernel does not serve (a degree
+    above 20, a repeated degree) take that composed route here too, as does second-order autograd."""
     import math
 
     degrees = [int(v) for v in l_list] if hasattr(l_list, "__len__") else [int(l_list)]
     if normalization not in ("integral", "norm", "component"):
         raise ValueError('normalization must be "integral", "norm" or "component"')
-    l_max = max(degrees)
-    xyz = x[:, [2, 0, 1]]
-    op = ops.spherical_harmonics if normalize else ops.solid_harmonics
-    sh = op(xyz, l_max)
-    columns, scales = [], []
+    scales = []
     for l in degrees:
         scale = 1.0 if normalization == "integral" else math.sqrt(4 * math.pi)
         if normalization == "norm":
             scale /= math.sqrt(2 * l + 1)
+        scales.append(scale)
+    if max(degrees) <= _SELECTED_LMAX and len(set(degrees)) == len(degrees):
+        op = ops.spherical_harmonics_selected if normalize else ops.solid_harmonics_selected
+        return op(x, degrees, [2, 0, 1], scales)
+    l_max = max(degrees)
+    op = ops.spherical_harmonics if normalize else ops.solid_harmonics
+    sh = op(x[:, [2, 0, 1]], l_max)
+    columns, factors = [], []
+    for l, scale in zip(degrees, scales):
         columns.extend(range(l * l, (l + 1) * (l + 1)))
-        scales.extend([scale] * (2 * l + 1))
-    whole = columns == list(range((l_max + 1) ** 2))
-    if not whole:
-        sh = sh[:, torch.tensor(columns, dtype=torch.long, device=sh.device)]
-    if normalization != "integral":
-        sh = sh * torch.tensor(scales, dtype=sh.dtype, device=sh.device)
-    return sh
+        factors.extend([scale] * (2 * l + 1))
+    sh = sh[:, torch.tensor(columns, dtype=torch.long, device=sh.device)]
+    return sh * torch.tensor(factors, dtype=sh.dtype, device=sh.device)

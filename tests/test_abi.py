@@ -31,7 +31,7 @@ def test_library_exports_every_declared_function():
 
     lib = _c_lib.get_library()
     declared = _declared_functions()
-    assert len(declared) == 43, declared
+    assert len(declared) == 52, declared
     for name in declared:
         assert getattr(lib, name) is not None
     assert sorted(declared) == sorted(_c_lib.exported_names())

@@ -79,6 +79,8 @@ VARIANTS = [
     {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "1", "SPH_B200_PANEL_THREADS": "96"},
     {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "32", "SPH_B200_PANEL_THREADS": "64", "SPH_B200_PANEL_ITERS": "-1"},
     {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "4", "SPH_B200_NO_BULK": "1"},
+    # several panels per table batch and a ring of three images per CTA
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_BATCH": "8", "SPH_B200_PANEL_POINTS": "2", "SPH_B200_PANEL_SLOTS": "3"},
 ]
 
 
