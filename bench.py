@@ -269,7 +269,8 @@ def main():
                     help="weak: every GPU gets the workload's full point count; strong: the total is fixed "
                          "(8 x 4,194,304 points for the headline case, the configuration's size otherwise) and sharded")
     ap.add_argument("--config", default="metric", choices=sorted(workloads.CONFIGS),
-                    help="metric = the headline case; cfg1..cfg5 = the other benchmark configurations")
+                    help="metric = the headline case; cfg1..cfg5 = the other benchmark configurations; "
+                         "aux_* = backward-kernel cases captured by the profiles")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -311,7 +312,12 @@ def main():
     sph = torch.empty((n, ny), dtype=tdtype, device=device)
     dsph = torch.empty((n, 3, ny), dtype=tdtype, device=device) if wl.level >= 1 else None
     ddsph = torch.empty((n, 3, 3, ny), dtype=tdtype, device=device) if wl.level >= 2 else None
-    sph_grad = xyz_grad = None
+    sph_grad = dsph_grad = xyz_grad = None
+    if wl.vjp2:
+        sph_grad = torch.from_numpy(workloads.make_upstream_grad(args.config, n_points=n, seed_offset=rank)).to(device)
+        dsph_grad = torch.from_numpy(
+            workloads.make_upstream_gradient_of_gradients(args.config, n_points=n, seed_offset=rank)).to(device)
+        xyz_grad = torch.empty((n, 3), dtype=tdtype, device=device)
     if wl.vjp:
         grad_host = (workloads.make_upstream_grad(args.config, n_points=total)[lo:hi] if strong
                      else workloads.make_upstream_grad(args.config, n_points=n, seed_offset=rank))
@@ -330,11 +336,15 @@ def main():
         if wl.vjp:
             calc.compute_vjp_raw(tdtype, xyz.data_ptr(), n, sph_grad.data_ptr(), xyz_grad.data_ptr(), stream.cuda_stream)
             launches += 1
+        if wl.vjp2:
+            calc.compute_vjp_with_gradients(xyz, sph_grad, dsph_grad, out=xyz_grad)
+            launches += 1
 
     # bytes one step moves by the algorithm's own count (forward, plus the fused backward where the
     # configuration has one)
     elem = 8 if wl.dtype == "f64" else 4
-    step_bytes_per_point = elem * (3 + ny * (1, 4, 13)[wl.level]) + (elem * (3 + ny + 3) if wl.vjp else 0)
+    step_bytes_per_point = (elem * (3 + ny * (1, 4, 13)[wl.level]) + (elem * (3 + ny + 3) if wl.vjp else 0) +
+                            (elem * (3 + 4 * ny + 3) if wl.vjp2 else 0))
     out_bytes = step_bytes_per_point * n
     # outputs smaller than a few L2 sizes would stay cached between steps: flush L2 between timed steps
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if out_bytes < (512 << 20) else None
@@ -439,6 +449,8 @@ def main():
     kernel = f"{_c_lib.kernel_family(wl.level, wl.l_max, elem)}<{ctype}, l_max={wl.l_max}, level={wl.level}>"
     if wl.vjp:
         kernel += f" + {_c_lib.kernel_family(3, wl.l_max, elem)}<{ctype}, l_max={wl.l_max}>"
+    if wl.vjp2:
+        kernel += f" + {_c_lib.kernel_family(4, wl.l_max, elem)}<{ctype}, l_max={wl.l_max}, second order>"
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": (traffic or {}).get("dram_bytes_per_launch"),
                 "peak_source": f"of {peak_kind}", "kernel": kernel,
@@ -465,7 +477,7 @@ def main():
         "config": {"workload": wl.name, "class": "SphericalHarmonics" if wl.normalized else "SolidHarmonics",
                    "l_max": wl.l_max,
                    "level": ("values", "values+gradients", "values+gradients+hessians")[wl.level] +
-                            (" then fused VJP" if wl.vjp else ""),
+                            (" then fused VJP" if wl.vjp else "") + (" then fused second-order VJP" if wl.vjp2 else ""),
                    "points_per_gpu": n, "bytes_per_point": step_bytes_per_point,
                    "l2_policy": (f"{out_bytes / 1e9:.2f} GB written per step per GPU, far larger than L2: no flush"
                                  if flush is None else

@@ -282,9 +282,9 @@ __device__ __forceinline__ void bulk_load_global_to_smem(void* sdst, const void*
 
 // Waits for the phase with the given parity, giving up after a bounded number of polls (each
 // poll already blocks for a hardware-defined interval). Returns false on give-up.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity, int max_tries = 1 << 22) {
     const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(bar));
-    for (int tries = 0; tries < (1 << 22); ++tries) {
+    for (int tries = 0; tries < max_tries; ++tries) {
         unsigned done;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"

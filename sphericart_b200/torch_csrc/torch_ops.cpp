@@ -49,11 +49,18 @@
 namespace {
 
 template <typename Calc> Calc& calculator(int64_t l_max) {
+    // the calculators live for the whole process, so each thread may remember the one it used last
+    // and skip the lock and the map on a steady stream of calls with one l_max
+    thread_local int64_t last_l_max = -1;
+    thread_local Calc* last = nullptr;
+    if (last != nullptr && last_l_max == l_max) return *last;
     static std::mutex mutex;
     static std::map<int64_t, std::unique_ptr<Calc>> cache;
     std::lock_guard<std::mutex> lock(mutex);
     auto& slot = cache[l_max];
     if (!slot) slot = std::make_unique<Calc>(static_cast<size_t>(l_max));
+    last = slot.get();
+    last_l_max = l_max;
     return *slot;
 }
 
@@ -212,6 +219,9 @@ at::Tensor selected_vjp(const at::Tensor& xyz_in, const at::Tensor& out_grad_in,
 // pass computes is recorded when a graph of it is asked for (create_graph).
 using torch::autograd::AutogradContext;
 using torch::autograd::variable_list;
+
+// No graph is recorded when nothing asks for one: the operator then goes straight to the kernel.
+inline bool wants_graph(const at::Tensor& t) { return at::GradMode::is_enabled() && t.defined() && t.requires_grad(); }
 
 template <bool NORMALIZED> std::string op_name(const char* suffix) {
     return std::string("sphericart_b200::") + (NORMALIZED ? "spherical" : "solid") + "_harmonics" + suffix;
@@ -377,21 +387,41 @@ template <bool NORMALIZED> struct SelectedFunction : torch::autograd::Function<S
 
 template <bool NORMALIZED>
 at::Tensor selected_autograd(const at::Tensor& xyz, at::IntArrayRef l_list, at::IntArrayRef axis_order, at::ArrayRef<double> scales) {
+    if (!wants_graph(xyz)) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return call_selected<NORMALIZED>(xyz, l_list, axis_order, scales);
+    }
     return SelectedFunction<NORMALIZED>::apply(xyz, l_list, axis_order, scales);
 }
 
 template <bool NORMALIZED> at::Tensor values_autograd(const at::Tensor& xyz, int64_t l_max) {
+    if (!wants_graph(xyz)) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return call_values<NORMALIZED>(xyz, l_max);
+    }
     return ValuesFunction<NORMALIZED>::apply(xyz, l_max);
 }
 template <bool NORMALIZED> at::Tensor vjp_autograd(const at::Tensor& xyz, const at::Tensor& sph_grad, int64_t l_max) {
+    if (!wants_graph(xyz) && !wants_graph(sph_grad)) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return call_vjp<NORMALIZED>(xyz, sph_grad, l_max);
+    }
     return VjpFunction<NORMALIZED>::apply(xyz, sph_grad, l_max);
 }
 template <bool NORMALIZED> std::tuple<at::Tensor, at::Tensor> with_gradients_autograd(const at::Tensor& xyz, int64_t l_max) {
+    if (!wants_graph(xyz)) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return call_with_gradients<NORMALIZED>(xyz, l_max);
+    }
     auto r = GradientsFunction<NORMALIZED>::apply(xyz, l_max);
     return {r[0], r[1]};
 }
 template <bool NORMALIZED>
 std::tuple<at::Tensor, at::Tensor, at::Tensor> with_hessians_autograd(const at::Tensor& xyz, int64_t l_max) {
+    if (!wants_graph(xyz)) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return call_with_hessians<NORMALIZED>(xyz, l_max);
+    }
     auto r = HessiansFunction<NORMALIZED>::apply(xyz, l_max);
     return {r[0], r[1], r[2]};
 }

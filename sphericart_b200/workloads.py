@@ -20,7 +20,8 @@ class Workload:
     dtype: str             # "f32" / "f64"
     n_points: int
     seed: int
-    vjp: bool = False
+    vjp: bool = False      # the step also runs the fused VJP of the values
+    vjp2: bool = False     # the step also runs the fused second-order VJP (of values and gradients)
 
     @property
     def np_dtype(self):
@@ -35,6 +36,8 @@ class Workload:
         size = 8 if self.dtype == "f64" else 4
         if self.vjp:
             return size * (3 + self.ny + 3)
+        if self.vjp2:
+            return size * (3 + 4 * self.ny + 3)
         return size * (3 + self.ny * (1, 4, 13)[self.level])
 
 
@@ -92,6 +95,11 @@ CONFIGS = {
     "cfg3": (Workload("spherical_l16_f32_hess_n2e6", True, 16, 2, "f32", 2_000_000, 1003), "shell"),
     "cfg4": (Workload("spherical_l4_f32_fwd_vjp_n5e7", True, 4, 0, "f32", 50_000_000, 1004, vjp=True), "var2"),
     "cfg5": (Workload("spherical_l32_f64_grad_n1e6", True, 32, 1, "f64", 1_000_000, 1005), "stress"),
+    # Not benchmark configurations: cases of the backward kernels that the profiles under profiles/
+    # capture (forward values, then the fused first- or second-order VJP).
+    "aux_vjp_l16": (Workload("spherical_l16_f32_fwd_vjp", True, 16, 0, "f32", 1_048_576, 1016, vjp=True), "var2"),
+    "aux_vjp2_l4": (Workload("spherical_l4_f32_fwd_vjp2", True, 4, 0, "f32", 4_194_304, 1024, vjp2=True), "var2"),
+    "aux_vjp2_l16": (Workload("spherical_l16_f32_fwd_vjp2", True, 16, 0, "f32", 262_144, 1026, vjp2=True), "var2"),
 }
 
 
@@ -113,6 +121,14 @@ def make_upstream_grad(config, n_points=None, seed_offset=0):
     n = wl.n_points if n_points is None else int(n_points)
     rng = np.random.default_rng(wl.seed + 100 + seed_offset)
     return rng.standard_normal((n, wl.ny), dtype=np.float32).astype(wl.np_dtype)
+
+
+def make_upstream_gradient_of_gradients(config, n_points=None, seed_offset=0):
+    """Upstream gradient dL/d(dY) for the second-order VJP cases: iid N(0,1), shape (n, 3, ny)."""
+    wl, _ = CONFIGS[config]
+    n = wl.n_points if n_points is None else int(n_points)
+    rng = np.random.default_rng(wl.seed + 200 + seed_offset)
+    return rng.standard_normal((n, 3, wl.ny), dtype=np.float32).astype(wl.np_dtype)
 
 
 def shard_bounds(n_points, world_size, rank, multiple=32):
