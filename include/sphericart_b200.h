@@ -143,9 +143,8 @@ SPHERICART_EXPORT const char* sphericart_cuda_last_error(void);
  * out of range). Launches nothing; benchmarks and profiles use it to label what they time. */
 SPHERICART_EXPORT const char* sphericart_cuda_kernel_family(int kind, size_t l_max, int elem_bytes);
 
-/* The kernels only wait on their own asynchronous copies and, inside one CTA, on the hand-over of
- * shared-memory buffers between its warps; every such wait is bounded, and a wait that ever gave up
- * records it on the device. Returns 1 if that happened on the current device since the
+/* The kernels' only waits are on their own asynchronous copies and are bounded; a wait that ever
+ * gave up records it on the device. Returns 1 if that happened on the current device since the
  * library was loaded, 0 if not, -1 if the flags could not be read. Synchronises the device. */
 SPHERICART_EXPORT int sphericart_cuda_device_wait_errors(void);
 

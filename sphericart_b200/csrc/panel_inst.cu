@@ -19,9 +19,8 @@ cudaError_t launch_panel(const PanelLaunchArgs<T>& a, int device, cudaStream_t s
     auto kernel = sph_panel_kernel<T, LEVEL, NORM, TP>;
     const int max_blocks = memo_grid<sph_panel_kernel<T, LEVEL, NORM, TP>>(a.threads, a.smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
-    const int consumers = a.threads / 32 - a.producers - 1;
-    if (a.threads % 32 != 0 || a.threads > 384 || a.producers < 1 || 32 * a.producers < TP || consumers < 1 || a.tp < 1 ||
-        a.tp > TP || (a.tp & (a.tp - 1)) != 0 || a.slots < 1 || a.slots > PANEL_MAX_SLOTS) {
+    if (a.threads < TP || a.threads > 256 || a.tp < 1 || a.tp > TP || (a.tp & (a.tp - 1)) != 0 || a.slots < 1 ||
+        a.slots > PANEL_MAX_SLOTS) {
         return cudaErrorInvalidValue;
     }
     const long long nbatches = (a.n + TP - 1) / TP;
@@ -39,7 +38,6 @@ cudaError_t launch_panel(const PanelLaunchArgs<T>& a, int device, cudaStream_t s
     k.tp = a.tp;
     k.slots = a.slots;
     k.tables_f64 = a.tables_f64;
-    k.producers = a.producers;
     kernel<<<grid, a.threads, a.smem, stream>>>(k);
     return cudaGetLastError();
 }
@@ -77,15 +75,6 @@ template <typename T, int TP> int PanelLaunch<T, TP>::registers(int level, bool 
         return 0;
     }
     return attr.numRegs;
-}
-
-template <typename T, int TP> int PanelLaunch<T, TP>::device_error_flag() {
-    int flag = 0;
-    if (cudaMemcpyFromSymbol(&flag, g_panel_wait_gave_up, sizeof(int)) != cudaSuccess) {
-        cudaGetLastError();
-        return -1;
-    }
-    return flag;
 }
 
 template struct PanelLaunch<SPH_T, SPH_TP>;

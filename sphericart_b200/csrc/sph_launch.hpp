@@ -138,9 +138,8 @@ template <typename T> struct BandLaunchArgs {
     int iters;     // see work_grid()
 };
 
-// Panel kernels, run-time l_max, forward levels only: a pipeline of `producers` table-building warps,
-// one store warp and `consumers` evaluating warps per CTA. Tables for TPT points at a time, tp points per
-// image (a power of two dividing TPT), `slots` images per CTA.
+// Panel kernels, run-time l_max, forward levels only. Tables for TPT points at a time, tp points per
+// image (a power of two dividing TPT), threads / tp slices per point, `slots` images per CTA.
 template <typename T> struct PanelLaunchArgs {
     const T* xyz;
     long long n;
@@ -154,8 +153,7 @@ template <typename T> struct PanelLaunchArgs {
     int tp;
     int slots;
     int tables_f64;      // 1: table recurrences in float64 for float32 outputs too
-    int producers;       // table-building warps per CTA (32 * producers >= TPT)
-    int threads;         // threads per CTA = 32 * (producers + 1 + consumers)
+    int threads;         // threads per CTA
     size_t smem;
     int iters;           // table batches per CTA, see work_grid()
 };
@@ -164,9 +162,6 @@ template <typename T, int TPT> struct PanelLaunch {
     static cudaError_t run(int level, bool normalized, const PanelLaunchArgs<T>& a, int device, cudaStream_t stream);
     // registers per thread of the kernel that run() would launch (0 if it cannot be queried)
     static int registers(int level, bool normalized);
-    // 1 if a bounded wait inside one of this instantiation's kernels ever gave up on the current
-    // device, 0 if not, -1 if the flag could not be read. Synchronises the device.
-    static int device_error_flag();
 };
 
 template <typename T, int G> struct BandLaunch {

@@ -50,8 +50,7 @@ struct Knobs {
     int panel_batch;    // force the points per table batch of the panel kernels (1, 2, 4, 8, 16 or 32)
     int panel_points;   // force the points per panel image (a power of two dividing the batch)
     int panel_slots;    // force the images per CTA (1..4)
-    int panel_threads;  // force the threads per CTA of the panel kernels (32 x (producers + 1 + consumers) <= 384)
-    int panel_producers;  // force the table-building warps per CTA (1 or 2)
+    int panel_threads;  // force the threads per CTA of the panel kernels (<= 256)
     int panel_iters;    // table batches per CTA of the panel kernels (k > 0), -1: persistent launch
     int panel_tables_f64;  // 1: table recurrences of the panel kernels in float64 for float32 outputs too
 };
@@ -71,7 +70,6 @@ const Knobs& knobs() {
                             env_int("SPH_B200_TILE_LMAX", TILE_LMAX), env_int("SPH_B200_NO_PANEL", 0),
                             env_int("SPH_B200_PANEL_BATCH", 0), env_int("SPH_B200_PANEL_POINTS", 0),
                             env_int("SPH_B200_PANEL_SLOTS", 0), env_int("SPH_B200_PANEL_THREADS", 0),
-                            env_int("SPH_B200_PANEL_PRODUCERS", 0),
                             env_int("SPH_B200_PANEL_ITERS", 0), env_int("SPH_B200_PANEL_TABLES_F64", 0)};
     return k;
 }
@@ -287,15 +285,13 @@ BandPlan make_band_plan(int l_max, int kind, size_t elem, size_t smem_limit, int
 // Panel-kernel plan: points per panel (TP), threads per CTA, shared-memory size. The sizes restate
 // panel_const_bytes / panel_state_bytes / panel_image_bytes of sph_panel.cuh for a run-time element size.
 struct PanelPlan {
-    int batch = 0;      // TPT: points whose tables are built at once
-    int tp = 0;         // points per panel (image); a power of two dividing batch
-    int slots = 0;      // images per CTA (ring)
-    int producers = 0;  // table-building warps per CTA
-    int consumers = 0;  // pair-evaluating warps per CTA
-    size_t smem = 0;    // dynamic shared memory per CTA
-    int iters = 0;      // table batches per CTA (see work_grid() in sph_launch.hpp)
+    int batch = 0;     // TPT: points whose tables are built at once
+    int tp = 0;        // points per panel (image); a power of two dividing batch
+    int slots = 0;     // images per CTA
+    int threads = 0;   // threads per CTA; threads / tp slices share each point
+    size_t smem = 0;   // dynamic shared memory per CTA
+    int iters = 0;     // table batches per CTA (see work_grid() in sph_launch.hpp)
     bool feasible = false;
-    int threads() const { return 32 * (producers + 1 + consumers); }
 };
 
 constexpr int PANEL_LMAX = 200;  // the descriptors hold l and m in 8 bits and the column in 16
@@ -315,85 +311,81 @@ size_t panel_image_bytes(int l_max, int level, int tp, size_t elem) {
     return image * elem;
 }
 
-// Constants, the two table buffers and the mbarriers (PANEL_BARRIER_BYTES in sph_panel.cuh).
 size_t panel_fixed_bytes(int l_max, int batch, size_t elem) {
     const size_t nq = size_t(n_table(l_max));
     const size_t consts = band_align16(2 * nq, elem) * elem + nq * 16;
     const size_t per_point = 4 + 2 * size_t(l_max + 3) + size_t(4 + (l_max + 1) * l_max / 2 + 5 * (l_max + 1));
-    return consts + 2 * band_align16(size_t(batch) * per_point, elem) * elem + 8 * (4 + 2 * 4);
+    return consts + band_align16(size_t(batch) * per_point, elem) * elem;
 }
 
-// Chooses the shape of the pipeline. What is weighed, in this order of importance: the consumer
-// warps an SM holds (they are the only warps that issue most of the time; about twenty saturate the
-// schedulers), how many chunks of a panel each consumer gets (a consumer pays a fixed set-up per
-// panel it touches: the point, the chain-rule constants, the image addresses), the lanes a chunk
-// leaves idle, whether the producers keep up with the consumers, and two or more CTAs per SM.
-// A ring of two images per CTA is enough: the store warp returns a slot as soon as the engine has
-// read it. `regs` = registers per thread of the kernel (occupancy).
+// Chooses the panel shape. Measured on a B200 over a few hundred forced shapes, what counts is: enough
+// image bytes per SM on their way to HBM (CTAs per SM x image size, up to about 160 KB - an image
+// drains for microseconds once the memory system is saturated), warps per SM (up to about twenty),
+// how evenly the pairs divide among the slices of a point and into whole warps, MANY pairs per
+// thread and panel (each panel costs two barriers, a copy-out and the wait for the previous image),
+// and a table batch large enough to keep the threads busy during the table phase. A whole warp of
+// points per panel (tp = 32: all lanes of a warp read the same per-pair constants) measured better
+// than its score otherwise says, hence the bonus. One image per CTA: a ring of two halves the
+// panel that fits and was slower in every case measured. `regs` = registers per thread (occupancy).
 PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, int regs) {
     PanelPlan best;
     if (l_max > PANEL_LMAX) return best;
     const int nq = n_table(l_max);
     const bool even_rows = n_columns(l_max) % 2 == 0;
-    if (regs <= 0) regs = level == 2 ? (elem == 8 ? 168 : 80) : (level == 1 ? 74 : 40);
+    if (regs <= 0) regs = level == 2 ? 176 : 64;
     const int regs_alloc = (regs + 7) / 8 * 8;
-    const double pair_cost = level == 0 ? 20.0 : (level == 1 ? 65.0 : 250.0);  // instructions per pair, roughly
-    const double panel_setup = 70.0;                                          // per consumer and panel
     const Knobs& k = knobs();
     double best_score = -1.0;
-    for (int batch = 32; batch >= 8; batch /= 2) {
+    for (int batch = 32; batch >= 1; batch /= 2) {
         if (k.panel_batch > 0 && batch != k.panel_batch) continue;
-        for (int producers = 1; producers <= 2; ++producers) {
-            if (k.panel_producers > 0 && producers != k.panel_producers) continue;
-            const size_t fixed = panel_fixed_bytes(l_max, batch, elem);
-            for (int tp = batch; tp >= 1; tp /= 2) {
-                if (k.panel_points > 0 && tp != k.panel_points) continue;
-                // rows of even length: neighbouring points sit a multiple of 16 bytes apart, which is
-                // conflict-free for up to eight points side by side
-                if (even_rows && tp > 8 && k.panel_points <= 0) continue;
-                const size_t image = panel_image_bytes(l_max, level, tp, elem);
-                const int pairs_per_chunk = 32 / tp;
-                const int nchunks = (nq + pairs_per_chunk - 1) / pairs_per_chunk;
-                for (int slots = 2; slots <= 3; ++slots) {
-                    if (k.panel_slots > 0 && slots != k.panel_slots) continue;
-                    const size_t smem = fixed + slots * image;
-                    if (smem > smem_limit) break;
-                    for (int consumers = 2; consumers <= 9; ++consumers) {
-                        const int threads = 32 * (producers + 1 + consumers);
-                        if (k.panel_threads > 0 && threads != k.panel_threads) continue;
-                        if (threads > 384) break;
-                        long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
-                        ctas = std::min<long long>(ctas, 2048 / threads);
-                        ctas = std::min<long long>(ctas, 65536 / (regs_alloc * threads));
-                        if (ctas < 1) continue;
-                        const double consumer_warps = std::min<double>(double(ctas * consumers), 20.0) / 20.0;
-                        const double chunks_each = double(nchunks) / consumers;
-                        const double setup = chunks_each * pair_cost / (chunks_each * pair_cost + panel_setup);
-                        const double lanes = double(nq) / (double(nchunks) * pairs_per_chunk);
-                        // producers: rows pairs per lane x a serial chain of about l_max steps of ~15 cycles;
-                        // consumers: their instructions for a batch at about four cycles per instruction
-                        const int table_lanes = std::max(1, 32 * producers / batch);
-                        const double produce = double(((l_max + 2) / 2 + table_lanes - 1) / table_lanes) * l_max * 15.0 + 400.0;
-                        const double consume = double(batch / tp) * chunks_each * pair_cost * 4.0;
-                        const double keeps_up = produce < 0.7 * consume ? 1.0 : std::max(0.3, 0.7 * consume / produce);
-                        const double score = consumer_warps * setup * lanes * keeps_up * (ctas >= 2 ? 1.0 : 0.85) *
-                                             (slots == 2 ? 1.0 : 0.98);
-                        if (score > best_score + 1e-9) {
-                            best_score = score;
-                            best.batch = batch;
-                            best.tp = tp;
-                            best.slots = slots;
-                            best.producers = producers;
-                            best.consumers = consumers;
-                            best.smem = smem;
-                            best.feasible = true;
-                        }
+        const size_t fixed = panel_fixed_bytes(l_max, batch, elem);
+        for (int tp = batch; tp >= 1; tp /= 2) {
+            if (k.panel_points > 0 && tp != k.panel_points) continue;
+            // rows of even length: neighbouring points sit a multiple of 16 bytes apart, which is
+            // conflict-free for up to eight points side by side
+            if (even_rows && tp > 8 && k.panel_points <= 0) continue;
+            const size_t image = panel_image_bytes(l_max, level, tp, elem);
+            for (int slots = 1; slots <= 4; ++slots) {
+                if (k.panel_slots > 0 ? slots != k.panel_slots : slots != 1) continue;
+                const size_t smem = fixed + slots * image;
+                if (smem > smem_limit) break;
+                for (int per_slice = 1; per_slice <= nq; ++per_slice) {
+                    const int slices = (nq + per_slice - 1) / per_slice;
+                    int threads = slices * tp;
+                    if (k.panel_threads > 0) threads = k.panel_threads;
+                    if (threads > 256) continue;
+                    if (threads < 64 && k.panel_threads <= 0) break;
+                    if (threads < batch) continue;
+                    const int warp_threads = (threads + 31) / 32 * 32;
+                    long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
+                    ctas = std::min<long long>(ctas, 2048 / warp_threads);
+                    ctas = std::min<long long>(ctas, 65536 / (regs_alloc * warp_threads));
+                    if (ctas < 1) continue;
+                    const int real_slices = threads / tp;
+                    const int real_per_slice = (nq + real_slices - 1) / real_slices;
+                    const double in_flight = std::min<double>(double(ctas * slots) * double(image), 160.0 * 1024) / (160.0 * 1024);
+                    const double warps = std::min<double>(double(ctas * warp_threads / 32), 20.0) / 20.0;
+                    const double balance = double(nq) / (double(real_slices) * real_per_slice) * threads / warp_threads;
+                    const double panel_cost = real_per_slice / (real_per_slice + 1.0);
+                    const double table_busy = std::min(1.0, double(batch) * ((l_max + 2) / 2) / threads);
+                    const double score = in_flight * warps * balance * panel_cost * (0.7 + 0.3 * table_busy) *
+                                         (ctas >= 2 ? 1.0 : 0.8) * (tp == 32 ? 1.15 : 1.0);
+                    if (score > best_score + 1e-9) {
+                        best_score = score;
+                        best.batch = batch;
+                        best.tp = tp;
+                        best.slots = slots;
+                        best.threads = threads;
+                        best.smem = smem;
+                        best.feasible = true;
                     }
+                    if (k.panel_threads > 0) break;
                 }
             }
         }
     }
-    // Each CTA stages the constants once; several table batches per CTA amortise that.
+    // Each CTA stages the constants once; several table batches per CTA amortise that (measured: 8
+    // batches per CTA 3 - 10 % faster than 4, 15 - 25 % faster than 1).
     best.iters = resolve_iters(k.panel_iters, 8);
     return best;
 }
@@ -581,18 +573,6 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
     }
 };
 
-template <typename T> int panel_error_flags() {
-    const int flags[] = {PanelLaunch<T, 1>::device_error_flag(),  PanelLaunch<T, 2>::device_error_flag(),
-                         PanelLaunch<T, 4>::device_error_flag(),  PanelLaunch<T, 8>::device_error_flag(),
-                         PanelLaunch<T, 16>::device_error_flag(), PanelLaunch<T, 32>::device_error_flag()};
-    int all = 0;
-    for (int f : flags) {
-        if (f < 0) return -1;
-        all |= f;
-    }
-    return all;
-}
-
 // Registers per thread of the panel kernels (they barely depend on the batch size; 8 is queried).
 template <typename T> int panel_registers(int level, bool normalized) { return PanelLaunch<T, 8>::registers(level, normalized); }
 
@@ -733,8 +713,7 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             a.tp = pplan->tp;
             a.slots = pplan->slots;
             a.tables_f64 = knobs().panel_tables_f64;
-            a.producers = pplan->producers;
-            a.threads = pplan->threads();
+            a.threads = pplan->threads;
             a.smem = pplan->smem;
             a.iters = pplan->iters;
             check(panel_dispatch<T>(pplan->batch, kind, normalized, a, scope.device, stream), "panel kernel launch");
@@ -1039,14 +1018,9 @@ extern "C" const char* sphericart_cuda_kernel_family(int kind, size_t l_max, int
 }
 
 extern "C" int sphericart_cuda_device_wait_errors(void) {
-    int flags[] = {sph_b200::TileDispatch<float>::error_flags(), sph_b200::TileDispatch<double>::error_flags(),
-                   sph_b200::panel_error_flags<float>(), sph_b200::panel_error_flags<double>()};
-    int all = 0;
-    for (int f : flags) {
-        if (f < 0) return -1;
-        all |= f;
-    }
-    return all;
+    const int f = sph_b200::TileDispatch<float>::error_flags();
+    const int d = sph_b200::TileDispatch<double>::error_flags();
+    return (f < 0 || d < 0) ? -1 : (f | d);
 }
 
 #define SPH_CAPI_FAMILY(KIND, SFX, T)                                                                               \

@@ -22,6 +22,11 @@ import numpy as np, torch
 import sphericart_b200 as sb
 from oracle import oracle
 cases = eval(sys.argv[2])
+import os
+if os.environ.get("EXPECT_PANEL"):
+    # the forced shape must be one the library accepts: otherwise the calls would quietly go elsewhere
+    from sphericart_b200 import _c_lib
+    assert _c_lib.kernel_family(1, 12, 4) == "sph_panel_kernel"
 rng = np.random.default_rng(11)
 worst = {"f32": 0.0, "f64": 0.0}
 for normalized, dt, l_max, level, n in cases:
@@ -74,17 +79,20 @@ VARIANTS = [
     # ... and the band kernel alone
     {"SPH_B200_TILE_LMAX": "2", "SPH_B200_NO_PANEL": "1"},
     {"SPH_B200_NO_PANEL": "1"},
-    # panel shapes the plan picks only for some degrees: one point per CTA (unaligned spans), many points
-    # per CTA, persistent launch, plain-store copy-out
-    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "1", "SPH_B200_PANEL_THREADS": "96"},
-    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "32", "SPH_B200_PANEL_THREADS": "64", "SPH_B200_PANEL_ITERS": "-1"},
-    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "4", "SPH_B200_NO_BULK": "1"},
-    # several panels per table batch and a ring of three images per CTA
-    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_BATCH": "8", "SPH_B200_PANEL_POINTS": "2", "SPH_B200_PANEL_SLOTS": "3"},
+    # panel shapes that the plan picks only for some degrees: one point per image (spans at any
+    # alignment), whole-warp panels with a persistent launch, plain-store copy-out, several panels per
+    # table batch with a ring of three images, table recurrences in float64
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "1", "SPH_B200_PANEL_THREADS": "96", "EXPECT_PANEL": "1"},
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "32", "SPH_B200_PANEL_THREADS": "64",
+     "SPH_B200_PANEL_ITERS": "-1", "EXPECT_PANEL": "1"},
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_POINTS": "4", "SPH_B200_NO_BULK": "1", "EXPECT_PANEL": "1"},
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_BATCH": "8", "SPH_B200_PANEL_POINTS": "2", "SPH_B200_PANEL_SLOTS": "3",
+     "EXPECT_PANEL": "1"},
+    {"SPH_B200_TILE_LMAX": "2", "SPH_B200_PANEL_BATCH": "16", "SPH_B200_PANEL_TABLES_F64": "1", "EXPECT_PANEL": "1"},
 ]
 
 
-@pytest.mark.parametrize("variant", VARIANTS, ids=lambda v: ",".join(f"{k[9:]}={x}" for k, x in v.items()) or "default")
+@pytest.mark.parametrize("variant", VARIANTS, ids=lambda v: ",".join(f"{k[9:]}={x}" for k, x in v.items() if k.startswith("SPH_B200_")) or "default")
 def test_variant_parity(variant, tmp_path):
     script = tmp_path / "child.py"
     script.write_text(CHILD)
