@@ -12,20 +12,23 @@ namespace sph_b200 {
 constexpr int TILE_LMAX = 20;       // compile-time tile kernels cover l_max 0..20
 constexpr int MAX_DEVICES = 64;
 
-// Which cases the tile kernels (compile-time l_max, one lane per point) serve; the rest go to the
-// band kernel (run-time l_max, lanes share a point). kind 0..2: forward level, 3: VJP of the values,
-// 4: VJP of (values, gradients). The crossovers were measured on a B200 for both element types
-// (fraction of the copy peak, tile / band):
-//   values        l = 9..12: 1.01 / 0.22-0.44          -> tile wherever compiled
-//   gradients     l = 10: 0.70-0.76 / 0.54-0.56, l = 11: 0.58-0.63 / 0.61-0.67   -> tile up to 10
-//   Hessians      float32 l = 5: 0.59 / 0.47, l = 6: 0.48 / 0.71 (the Hessian columns need many registers
-//                 and the rows few images per SM)      -> tile up to 5 and a 100 KB image
-//   VJP           l = 9..20: 0.57-1.03 / 0.15-0.25     -> tile wherever compiled
-//   2nd-order VJP l = 5: 1.2-2.1 / 0.7-1.8 Gpoints/s, l = 6: 0.6-1.1 / 0.6-1.7   -> tile up to 5
+// Which cases the tile kernels (compile-time l_max, one lane per point) serve; the other forward
+// calls go to the panel kernels (run-time l_max, a CTA per panel of points), the other backward
+// calls to the band kernel (run-time l_max, lanes share a point). kind 0..2: forward level, 3: VJP
+// of the values, 4: VJP of (values, gradients). The crossovers were measured on a B200 for both
+// element types (fraction of the copy peak, tile / panel or band):
+//   values        l = 9..20: 1.00-1.04 / 0.29-0.57              -> tile wherever compiled
+//   gradients     float32 l = 9: 0.89 / 0.69, l = 10: 0.76 / 0.76, l = 11: 0.60 / 0.82;
+//                 float64 l = 8: 1.02 / 0.92, l = 9: 0.68 / 0.87, l = 10: 0.70 / 0.89
+//                                                               -> tile up to 10 (float32), 8 (float64)
+//   Hessians      float32 l = 4: 0.88 / 0.86, l = 5: 0.57 / 0.67; float64 l = 4: 0.84 / 0.53, l = 5: 0.57 / 0.57
+//                                                               -> tile up to 4
+//   VJP           l = 9..20: 0.57-1.03 / 0.15-0.25 (band)       -> tile wherever compiled
+//   2nd-order VJP l = 5: 1.2-2.1 / 0.7-1.8 Gpoints/s, l = 6: 0.6-1.1 / 0.6-1.7 (band)   -> tile up to 5
 constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
     if (l_max > TILE_LMAX) return false;
-    if (kind == 1) return l_max <= 10;
-    if (kind == 2) return l_max <= 5 && size_t(32) * (l_max + 1) * (l_max + 1) * 13 * elem_bytes <= 100 * 1024;
+    if (kind == 1) return l_max <= (elem_bytes == 4 ? 10 : 8);
+    if (kind == 2) return l_max <= 4;
     if (kind == 4) return l_max <= 5;
     // the VJP kernel keeps a tile's upstream rows in shared memory: at least two tiles per SM
     if (kind == 3) return size_t(32) * (l_max + 1) * (l_max + 1) * elem_bytes <= 113 * 1024;

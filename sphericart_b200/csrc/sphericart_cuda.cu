@@ -320,9 +320,11 @@ size_t panel_fixed_bytes(int l_max, int batch, size_t elem) {
 
 // Chooses the panel shape. Measured on a B200 over a few hundred forced shapes, what counts is: enough
 // image bytes per SM on their way to HBM (CTAs per SM x image size, up to about 160 KB - an image
-// drains for microseconds once the memory system is saturated), warps per SM (up to about twenty),
-// how evenly the pairs divide among the slices of a point and into whole warps, MANY pairs per
-// thread and panel (each panel costs two barriers, a copy-out and the wait for the previous image),
+// drains for microseconds once the memory system is saturated), warps per SM (beyond about twelve
+// more did not help), how evenly the pairs divide among the slices of a point and into whole warps,
+// MANY pairs per thread and panel (each panel costs two barriers, a copy-out and the wait for the
+// previous image: l_max = 16 float32 Hessians, 2e6 points, four points per panel: 3 / 4 / 5 pairs per
+// thread -> 0.87 / 0.86 / 0.93 of the copy peak with 21 / 15 / 12 warps per SM),
 // and a table batch large enough to keep the threads busy during the table phase. A whole warp of
 // points per panel (tp = 32: all lanes of a warp read the same per-pair constants) measured better
 // than its score otherwise says, hence the bonus. One image per CTA: a ring of two halves the
@@ -330,6 +332,12 @@ size_t panel_fixed_bytes(int l_max, int batch, size_t elem) {
 PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, int regs) {
     PanelPlan best;
     if (l_max > PANEL_LMAX) return best;
+    // Rows so long that even one point's image leaves room for a single small CTA per SM stay with the
+    // band kernel and its direct stores (measured, panel / band: float64 gradients l_max = 40, 54 KB per
+    // point: 0.65 / 0.78; float64 Hessians l_max = 32, 113 KB per point: 0.37 / 0.49; below these sizes the
+    // panel kernels win, e.g. float64 Hessians l_max = 24, 65 KB per point: 0.66 / 0.47).
+    const size_t one_point = panel_image_bytes(l_max, level, 1, elem);
+    if (knobs().panel_points <= 0 && ((level == 1 && one_point > 44 * 1024) || (level == 2 && one_point > 100 * 1024))) return best;
     const int nq = n_table(l_max);
     const bool even_rows = n_columns(l_max) % 2 == 0;
     if (regs <= 0) regs = level == 2 ? 176 : 64;
@@ -364,9 +372,9 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                     const int real_slices = threads / tp;
                     const int real_per_slice = (nq + real_slices - 1) / real_slices;
                     const double in_flight = std::min<double>(double(ctas * slots) * double(image), 160.0 * 1024) / (160.0 * 1024);
-                    const double warps = std::min<double>(double(ctas * warp_threads / 32), 20.0) / 20.0;
+                    const double warps = std::min<double>(double(ctas * warp_threads / 32), 12.0) / 12.0;
                     const double balance = double(nq) / (double(real_slices) * real_per_slice) * threads / warp_threads;
-                    const double panel_cost = real_per_slice / (real_per_slice + 1.0);
+                    const double panel_cost = real_per_slice / (real_per_slice + 2.0);
                     const double table_busy = std::min(1.0, double(batch) * ((l_max + 2) / 2) / threads);
                     const double score = in_flight * warps * balance * panel_cost * (0.7 + 0.3 * table_busy) *
                                          (ctas >= 2 ? 1.0 : 0.8) * (tp == 32 ? 1.15 : 1.0);
@@ -384,9 +392,10 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
             }
         }
     }
-    // Each CTA stages the constants once; several table batches per CTA amortise that (measured: 8
-    // batches per CTA 3 - 10 % faster than 4, 15 - 25 % faster than 1).
-    best.iters = resolve_iters(k.panel_iters, 8);
+    // Each CTA stages the constants once; enough table batches per CTA amortise that: at least eight,
+    // and at least 256 points (measured: 8 batches per CTA 3 - 10 % faster than 4 and 15 - 25 % faster
+    // than 1; l_max = 32 float64 gradients with batches of four points: 32 / 64 batches -> 0.73 / 0.80).
+    best.iters = resolve_iters(k.panel_iters, std::max(8, best.batch > 0 ? (256 + best.batch - 1) / best.batch : 8));
     return best;
 }
 
