@@ -53,6 +53,7 @@ struct Knobs {
     int panel_threads;  // force the threads per CTA of the panel kernels (<= 256)
     int panel_iters;    // table batches per CTA of the panel kernels (k > 0), -1: persistent launch
     int panel_tables_f64;  // 1: table recurrences of the panel kernels in float64 for float32 outputs too
+    int vjp_split;      // -1: the one-warp-per-tile VJP kernel also where the shared-tile one is compiled
 };
 
 int env_int(const char* name, int fallback) {
@@ -70,7 +71,8 @@ const Knobs& knobs() {
                             env_int("SPH_B200_TILE_LMAX", TILE_LMAX), env_int("SPH_B200_NO_PANEL", 0),
                             env_int("SPH_B200_PANEL_BATCH", 0), env_int("SPH_B200_PANEL_POINTS", 0),
                             env_int("SPH_B200_PANEL_SLOTS", 0), env_int("SPH_B200_PANEL_THREADS", 0),
-                            env_int("SPH_B200_PANEL_ITERS", 0), env_int("SPH_B200_PANEL_TABLES_F64", 0)};
+                            env_int("SPH_B200_PANEL_ITERS", 0), env_int("SPH_B200_PANEL_TABLES_F64", 0),
+                            env_int("SPH_B200_VJP_SPLIT", 0)};
     return k;
 }
 
@@ -542,14 +544,25 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
                                                   buffers, iters, device, stream);
         return cudaErrorInvalidValue;
     }
+    static cudaError_t vjp_split(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
+                                 const T* tables, bool use_bulk, int iters, int device, cudaStream_t stream) {
+        if (l_max == LMAX)
+            return TileLaunch<T, LMAX>::vjp_split(normalized, xyz, sph_grad, n, xyz_grad, tables, use_bulk, iters, device,
+                                                  stream);
+        if constexpr (LMAX > 0)
+            return TileDispatch<T, LMAX - 1>::vjp_split(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, use_bulk,
+                                                        iters, device, stream);
+        return cudaErrorInvalidValue;
+    }
     static cudaError_t vjp2(int l_max, bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
-                            T* xyz_grad, const T* tables, int warps, int iters, int device, cudaStream_t stream) {
+                            T* xyz_grad, const T* tables, int warps, int iters, bool use_bulk, int device,
+                            cudaStream_t stream) {
         if (l_max == LMAX)
             return TileLaunch<T, LMAX>::vjp2(normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps, iters,
-                                             device, stream);
+                                             use_bulk, device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, tables, warps,
-                                                   iters, device, stream);
+                                                   iters, use_bulk, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t selected(int l_max, bool normalized, const T* xyz, long long n, T* out, const T* tables,
@@ -652,10 +665,11 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
     if (tile_serves(kind, l_max, int(sizeof(T))) && l_max <= knobs().tile_lmax && !force_band) {
         if (kind == 4) {
             const size_t vjp2_per_warp =
-                size_t(32) * (4 * n_columns(l_max) + 2 * tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T);
+                size_t(32) * (4 * n_columns(l_max) + 2 * tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T) + 16;
+            const bool use_bulk = knobs().no_bulk == 0 && aligned16(dsph_grad) && (sph_grad == nullptr || aligned16(sph_grad));
             check(TileDispatch<T>::vjp2(l_max, normalized, xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables,
                                         tile_warps(vjp2_per_warp, props.smem_optin), resolve_iters(knobs().vjp_iters, 4),
-                                        scope.device, stream),
+                                        use_bulk, scope.device, stream),
                   "tile second-order VJP kernel launch");
             return;
         }
@@ -666,6 +680,14 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         const int vjp_buffers = 1;
         const size_t per_warp = kind == 3 ? vjp_buffers * vjp_image + 16
                                           : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
+        if (kind == 3 && knobs().vjp_split >= 0 && vjp_split_compiled(l_max, int(sizeof(T)))) {
+            // long rows: the warps of a CTA share the tile's upstream rows and split its degrees
+            const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
+            check(TileDispatch<T>::vjp_split(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, use_bulk,
+                                             resolve_iters(knobs().vjp_iters, 2), scope.device, stream),
+                  "tile VJP kernel launch (shared tile)");
+            return;
+        }
         if (kind == 3) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
             // short-lived CTAs of four warps; one tile per warp with a single image (nothing to overlap a

@@ -3,6 +3,7 @@
 #include "sph_launch.hpp"
 #include "sph_select.cuh"
 #include "sph_tile.cuh"
+#include "sph_vjp_split.cuh"
 
 #include <atomic>
 
@@ -116,17 +117,33 @@ cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad
 }
 
 template <typename T, int LMAX, bool NORM>
+cudaError_t launch_vjp_split(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, bool use_bulk,
+                             int iters, int device, cudaStream_t stream) {
+    constexpr int W = vjp_split_warps(LMAX, int(sizeof(T)));
+    const size_t smem = vjp_split_smem_bytes<T, LMAX, W>();
+    const int max_blocks = memo_grid<sph_vjp_split_kernel<T, LMAX, NORM, W>>(32 * W, smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
+    const int grid = work_grid(ntiles, max_blocks, iters);
+    sph_vjp_split_kernel<T, LMAX, NORM, W><<<grid, 32 * W, smem, stream>>>(xyz, sph_grad, n, xyz_grad,
+                                                                          make_tables<T, LMAX>(host_tables), use_bulk ? 1 : 0);
+    return cudaGetLastError();
+}
+
+template <typename T, int LMAX, bool NORM>
 cudaError_t launch_vjp2(const T* xyz, const T* sph_grad, const T* dsph_grad, long long n, T* xyz_grad,
-                        const T* host_tables, int warps, int iters, int device, cudaStream_t stream) {
+                        const T* host_tables, int warps, int iters, bool use_bulk, int device, cudaStream_t stream) {
     static GridCache cache{};
     auto kernel = sph_vjp2_tile_kernel<T, LMAX, NORM>;
-    const size_t smem = size_t(warps) * vjp2_tile_smem_bytes<T, LMAX>();
+    // the warps' images, then one mbarrier slot (16 bytes) per warp
+    const size_t smem = size_t(warps) * (vjp2_tile_smem_bytes<T, LMAX>() + 16);
     const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long want = (ntiles + warps - 1) / warps;
     const int grid = work_grid(want, max_blocks, iters);
-    kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, dsph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables));
+    kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, dsph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables),
+                                               use_bulk ? 1 : 0);
     return cudaGetLastError();
 }
 
@@ -229,14 +246,26 @@ cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph
 }
 
 template <typename T, int LMAX>
+cudaError_t TileLaunch<T, LMAX>::vjp_split(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
+                                           const T* host_tables, bool use_bulk, int iters, int device, cudaStream_t stream) {
+    if constexpr (vjp_split_compiled(LMAX, int(sizeof(T)))) {
+        return normalized
+                   ? launch_vjp_split<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, use_bulk, iters, device, stream)
+                   : launch_vjp_split<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, use_bulk, iters, device, stream);
+    } else {
+        return cudaErrorInvalidConfiguration;
+    }
+}
+
+template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
-                                      T* xyz_grad, const T* host_tables, int warps, int iters, int device,
+                                      T* xyz_grad, const T* host_tables, int warps, int iters, bool use_bulk, int device,
                                       cudaStream_t stream) {
     if constexpr (tile_serves(4, LMAX, int(sizeof(T)))) {
         return normalized ? launch_vjp2<T, LMAX, true>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters,
-                                                       device, stream)
+                                                       use_bulk, device, stream)
                           : launch_vjp2<T, LMAX, false>(xyz, sph_grad, dsph_grad, n, xyz_grad, host_tables, warps, iters,
-                                                        device, stream);
+                                                        use_bulk, device, stream);
     } else {
         return cudaErrorInvalidConfiguration;
     }
