@@ -29,20 +29,11 @@ constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
     if (l_max > TILE_LMAX) return false;
     if (kind == 1) return l_max <= (elem_bytes == 4 ? 10 : 8);
     if (kind == 2) return l_max <= 4;
-    if (kind == 4) return l_max <= 5;
+    if (kind == 4) return l_max <= (elem_bytes == 4 ? 10 : 8);
     // the VJP kernel keeps a tile's upstream rows in shared memory: at least two tiles per SM
     if (kind == 3) return size_t(32) * (l_max + 1) * (l_max + 1) * elem_bytes <= 113 * 1024;
     return true;
 }
-
-// The VJP kernel whose warps share a tile (sph_vjp_split.cuh) exists for the degrees where one warp's
-// image of upstream rows exceeds 16 KB (float32: l_max >= 11, float64: l_max >= 8), as long as the
-// image fits at all. Warps per tile: four, eight from 40 KB on.
-constexpr size_t vjp_tile_image_bytes(int l_max, int elem_bytes) { return size_t(32) * (l_max + 1) * (l_max + 1) * elem_bytes; }
-constexpr bool vjp_split_compiled(int l_max, int elem_bytes) {
-    return l_max <= TILE_LMAX && vjp_tile_image_bytes(l_max, elem_bytes) > 16 * 1024 && tile_serves(3, l_max, elem_bytes);
-}
-constexpr int vjp_split_warps(int l_max, int elem_bytes) { return vjp_tile_image_bytes(l_max, elem_bytes) > 40 * 1024 ? 8 : 4; }
 
 // Number of CTAs that keep every SM of `device` full for a persistent launch of `kernel` with
 // the given block size and dynamic shared memory (also raises the kernel's dynamic shared
@@ -113,14 +104,9 @@ template <typename T, int LMAX> struct TileLaunch {
     static cudaError_t forward(int level, bool normalized, const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
                                const T* host_tables, int warps, int span_tiles, bool use_bulk, int iters,
                                int tile_points, int device, cudaStream_t stream);
-    // buffers: 2 = the next tile's upstream rows stream in during the arithmetic, 1 = half the shared memory
     static cudaError_t vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* host_tables, int warps, bool use_bulk, int buffers, int iters, int device,
+                           const T* host_tables, int warps, bool use_bulk, int iters, int device,
                            cudaStream_t stream);
-    // the same product with the warps of a CTA sharing a tile and splitting its degrees (sph_vjp_split.cuh);
-    // compiled for the degrees vjp_split_compiled() lists
-    static cudaError_t vjp_split(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                 const T* host_tables, bool use_bulk, int iters, int device, cudaStream_t stream);
     // second-order backward: VJP of (values, gradients); sph_grad may be null; use_bulk: the upstream
     // gradients are 16-byte aligned and may be fetched by the TMA engine
     static cudaError_t vjp2(bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,

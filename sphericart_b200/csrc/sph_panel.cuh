@@ -145,7 +145,7 @@ __device__ __forceinline__ void bulk_wait_read_pending(int pending) {
 // total length), with the reference's downward-in-m recurrence
 // (sphericart/include/templates_core.hpp:123,155,202). A is the type the recurrences are carried in:
 // double (rounded once on storing) or the element type itself.
-template <typename T, typename A, int TPT>
+template <typename T, typename A, int TPT, bool WITH_Q = true>
 __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa, int SA, int qa, T* sc, T* ss, T* sQ,
                                                    const T* sK) {
     const A xd = A(x), yd = A(y), zd = A(z);
@@ -174,6 +174,7 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
             pr = nr;
         }
     }
+    if constexpr (!WITH_Q) return;  // values only: the rows are evaluated in registers as they are emitted
     auto build_row = [&](int l) {
         T* row = sQ + panel_row_start(l) * TPT + qa;
         const T* Kl = sK + tri(l, 0);
@@ -305,9 +306,9 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                 sP[3 * TPT + qa] = ir;
             }
             if (a.tables_f64 != 0) {
-                panel_build_tables<T, double, TPT>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
+                panel_build_tables<T, double, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
             } else {
-                panel_build_tables<T, T, TPT>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
+                panel_build_tables<T, T, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
             }
         }
 
@@ -445,15 +446,59 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     const T f = lds_at<T, 0>(f_addr + unsigned(t) * unsigned(sizeof(T)));
                     return panel_load_pair<T, TPT, LEVEL>(d, f, q_addr, c_addr, s_addr);
                 };
-                int t = s;
-                // two pairs in flight per thread
-                for (; t + S < nq; t += 2 * S) {
-                    const PairInputs<T, LEVEL> in0 = load(t);
-                    const PairInputs<T, LEVEL> in1 = load(t + S);
-                    finish_pair(in0);
-                    finish_pair(in1);
+                if constexpr (LEVEL >= 1) {
+                    int t = s;
+                    // two pairs in flight per thread
+                    for (; t + S < nq; t += 2 * S) {
+                        const PairInputs<T, LEVEL> in0 = load(t);
+                        const PairInputs<T, LEVEL> in1 = load(t + S);
+                        finish_pair(in0);
+                        finish_pair(in1);
+                    }
+                    if (t < nq) finish_pair(load(t));
+                } else {
+                    // Values only: no Q table. A slice takes whole rows, in pairs (j, l_max - j) of constant
+                    // total length, carries each row's recurrence in registers (the reference's own scheme,
+                    // sphericart/include/templates_core.hpp:123,155,202, in the element type) and writes the
+                    // two values of every m as it goes: Y_{l,+m} = F Q_l^m c_m, Y_{l,-m} = F Q_l^m s_m.
+                    const T rho = x2 + y2;
+                    const T* cp = sc + sub + p + 2 * TPT;  // c_m at cp[m * TPT]
+                    const T* sp = ss + sub + p + 2 * TPT;
+                    T* out = image0 + p * st0;
+                    auto row_values = [&](int l) {
+                        const T* Kl = sK + tri(l, 0);
+                        const T* Fl = sF + tri(l, 0);
+                        T* mid = out + l * l + l;
+                        T q2 = Kl[l];  // Q_l^l is tabulated
+                        {
+                            const T pq = q2 * Fl[l];
+                            mid[l] = pq * cp[l * TPT];
+                            if (l > 0) mid[-l] = pq * sp[l * TPT];
+                        }
+                        if (l >= 1) {
+                            T q1 = -z * q2;  // Q_l^{l-1}
+                            {
+                                const T pq = q1 * Fl[l - 1];
+                                mid[l - 1] = pq * cp[(l - 1) * TPT];
+                                if (l > 1) mid[1 - l] = pq * sp[(l - 1) * TPT];
+                            }
+                            T tm = T(2 * (l - 1));  // 2 (m + 1)
+                            for (int m = l - 2; m >= 0; --m) {
+                                const T q0 = Kl[m] * (tm * z * q1 + rho * q2);
+                                const T pq = q0 * Fl[m];
+                                mid[m] = pq * cp[m * TPT];
+                                if (m > 0) mid[-m] = pq * sp[m * TPT];
+                                q2 = q1;
+                                q1 = q0;
+                                tm -= T(2);
+                            }
+                        }
+                    };
+                    for (int j = s; 2 * j <= L; j += S) {
+                        row_values(L - j);
+                        if (L - j != j) row_values(j);
+                    }
                 }
-                if (t < nq) finish_pair(load(t));
             }
 
             // ---- copy-out

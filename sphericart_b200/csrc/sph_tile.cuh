@@ -300,23 +300,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 // translation unit, read by TileLaunch::device_error_flag().
 static __device__ int g_tile_wait_gave_up = 0;
 
-// Per warp: one or two images of the tile's sph_grad rows followed by two mbarriers. Two images
-// (a double buffer) let the next tile stream in during the arithmetic; for long rows one image
-// leaves room for twice the warps per SM, which hides the latency better.
-template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_smem_bytes(int buffers) {
-    return size_t(buffers) * TILE_POINTS * (n_columns(LMAX) + tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T) + 16;
+// Per warp: one image of the tile's sph_grad rows followed by its mbarrier (16 bytes reserved). One
+// image, not two: a double buffer that fetched one tile ahead halves the warps an SM holds and
+// measured slower at every degree (l_max = 10 float32: 0.61 against 1.03 of the copy peak).
+template <typename T, int LMAX> __host__ __device__ constexpr size_t vjp_tile_smem_bytes() {
+    return size_t(TILE_POINTS) * (n_columns(LMAX) + tile_row_pad(n_columns(LMAX), int(sizeof(T)))) * sizeof(T) + 16;
 }
 
 // use_bulk != 0: the rows of sph_grad are fetched by the TMA engine (1-D bulk load, completion on
-// an mbarrier), so the warp spends no issue slots on the staging copy; with buffers == 2 the next
-// tile is fetched one tile ahead of the arithmetic, with buffers == 1 (the default: half the
-// shared memory, twice the warps per SM) the other resident warps cover the wait. Requires a
-// 16-byte aligned sph_grad; otherwise, and for the ragged last tile, the warp stages the rows
-// itself with coalesced loads.
+// an mbarrier), so the warp spends no issue slots on the staging copy; the next tile is requested
+// as soon as the current one has been consumed and the other resident warps cover the wait.
+// Requires a 16-byte aligned sph_grad; otherwise, and for the ragged last tile, the warp stages
+// the rows itself with coalesced loads.
 template <typename T, int LMAX, bool NORM>
 __global__ void __launch_bounds__(256)
 sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, long long n,
-                    T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk, int buffers) {
+                    T* __restrict__ xyz_grad, const __grid_constant__ Tables<T, LMAX> tab, int use_bulk) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int NY = n_columns(LMAX);
     constexpr unsigned TILE_BYTES = unsigned(TILE_POINTS * NY * sizeof(T));
@@ -328,10 +327,9 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
     if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    unsigned char* mine = smem_raw + size_t(warp) * vjp_tile_smem_bytes<T, LMAX>(buffers);
-    T* img[2] = {reinterpret_cast<T*>(mine), reinterpret_cast<T*>(mine) + (buffers == 2 ? TILE_POINTS * S : 0)};
-    unsigned long long* bar =
-        reinterpret_cast<unsigned long long*>(mine + size_t(buffers) * TILE_POINTS * S * sizeof(T));
+    unsigned char* mine = smem_raw + size_t(warp) * vjp_tile_smem_bytes<T, LMAX>();
+    T* img = reinterpret_cast<T*>(mine);
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(mine + size_t(TILE_POINTS) * S * sizeof(T));
 
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long stride = (long long)gridDim.x * nwarps;
@@ -339,34 +337,32 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
 
     // a tile can come through the engine when it is full (its byte count is then a multiple of 16)
     auto engine_tile = [&](long long tile) { return use_bulk && (tile + 1) * TILE_POINTS <= n; };
-    auto issue = [&](long long tile, int buf) {
+    auto issue = [&](long long tile) {
         if (tile < ntiles && engine_tile(tile)) {  // the same for every lane
             if constexpr (PAD == 0) {
                 if (lane == 0) {
-                    mbar_expect_tx(&bar[buf], TILE_BYTES);
-                    bulk_load_global_to_smem(img[buf], sph_grad + tile * TILE_POINTS * NY, TILE_BYTES, &bar[buf]);
+                    mbar_expect_tx(bar, TILE_BYTES);
+                    bulk_load_global_to_smem(img, sph_grad + tile * TILE_POINTS * NY, TILE_BYTES, bar);
                 }
             } else {
-                if (lane == 0) mbar_expect_tx(&bar[buf], TILE_BYTES);
+                if (lane == 0) mbar_expect_tx(bar, TILE_BYTES);
                 __syncwarp();
-                bulk_load_global_to_smem(img[buf] + lane * S, sph_grad + (tile * TILE_POINTS + lane) * NY,
-                                         unsigned(NY * sizeof(T)), &bar[buf]);
+                bulk_load_global_to_smem(img + lane * S, sph_grad + (tile * TILE_POINTS + lane) * NY, unsigned(NY * sizeof(T)),
+                                         bar);
             }
         }
     };
 
     if (use_bulk) {
         if (lane == 0) {
-            mbar_init(&bar[0], 1);
-            mbar_init(&bar[1], 1);
+            mbar_init(bar, 1);
             mbar_init_fence();
         }
         __syncwarp();
-        issue(tile0, 0);
+        issue(tile0);
     }
 
-    unsigned phase[2] = {0u, 0u};
-    int cur = 0;
+    unsigned phase = 0u;
     for (long long tile = tile0; tile < ntiles; tile += stride) {
         const long long first = tile * TILE_POINTS;
         const long long i = first + lane;
@@ -377,34 +373,27 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             y = xyz[3 * i + 1];
             z = xyz[3 * i + 2];
         }
-        // every lane finished reading the other buffer in the previous iteration (barrier at its
-        // end), so the next tile may stream into it while this one is being processed
-        if (buffers == 2) issue(tile + stride, cur ^ 1);
 
         if (engine_tile(tile)) {
-            if (!mbar_wait_bounded(&bar[cur], phase[cur])) {
+            if (!mbar_wait_bounded(bar, phase)) {
                 g_tile_wait_gave_up = 1;
-                // do not leave with a copy in flight towards this CTA's shared memory
-                if (buffers == 2 && tile + stride < ntiles && engine_tile(tile + stride))
-                    mbar_wait_bounded(&bar[cur ^ 1], phase[cur ^ 1]);
-                return;
+                return;  // nothing else of this warp is in flight: the next tile is only requested below
             }
-            phase[cur] ^= 1u;
+            phase ^= 1u;
         } else {
             const T* gsrc = sph_grad + first * NY;
             if (PAD != 0 && aligned16_in) {
                 // rows past the end of the input keep whatever they hold: their lanes write no result
-                copy_rows_in_16<T, NY, S, TILE_POINTS>(img[cur], gsrc, npts, lane);
+                copy_rows_in_16<T, NY, S, TILE_POINTS>(img, gsrc, npts, lane);
             } else {
-                for (int e = lane; e < TILE_POINTS * NY; e += 32)
-                    img[cur][e + PAD * (e / NY)] = (e < npts * NY) ? gsrc[e] : T(0);
+                for (int e = lane; e < TILE_POINTS * NY; e += 32) img[e + PAD * (e / NY)] = (e < npts * NY) ? gsrc[e] : T(0);
             }
             __syncwarp();
         }
 
         // The chain rule through r -> r/|r| is linear in the gradient, so it is applied once to the
         // accumulated sum of raw gradients instead of to each of the (l_max+1)^2 columns.
-        VjpSink<T, NY> sink{img[cur] + lane * S, T(0), T(0), T(0)};
+        VjpSink<T, NY> sink{img + lane * S, T(0), T(0), T(0)};
         eval_point<T, LMAX, 1, NORM, VjpSink<T, NY>, true>(x, y, z, tab, sink);
         if constexpr (NORM) {
             const T ir = T(1) / sqrt(x * x + y * y + z * z);
@@ -419,15 +408,11 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
             xyz_grad[3 * i + 1] = sink.ay;
             xyz_grad[3 * i + 2] = sink.az;
         }
-        // this buffer is written next by the TMA engine (async proxy) after having been read through
-        // ordinary loads: order the two
+        // the image is written next by the TMA engine (async proxy) after having been read through
+        // ordinary loads: order the two, then ask for the next tile
         fence_proxy_async_smem();
-        __syncwarp();  // all lanes are done with img[cur]
-        if (buffers == 2) {
-            cur ^= 1;
-        } else {
-            issue(tile + stride, 0);  // single image: the next tile can only come in now
-        }
+        __syncwarp();  // all lanes are done with the image
+        issue(tile + stride);
     }
 }
 
@@ -532,7 +517,9 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
     const int nwarps = blockDim.x >> 5;
     constexpr int PAD = tile_row_pad(NY, int(sizeof(T)));
     constexpr int S0 = NY + PAD, S1 = 3 * NY + PAD;
-    if constexpr (PAD != 0) use_bulk = 0;  // padded rows are not an image of global memory
+    // padded rows (see tile_row_pad) arrive as one bulk load per row and array, issued by the row's
+    // lane; worthwhile from 256-byte rows on, shorter padded rows are staged by the warp
+    if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     T* img_s = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * (S0 + S1);
     T* img_d = img_s + TILE_POINTS * S0;
     unsigned long long* bar =
@@ -547,10 +534,18 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
     // a tile can come through the engine when it is full (the same answer for every lane)
     auto engine_tile = [&](long long tile) { return use_bulk && tile < ntiles && (tile + 1) * TILE_POINTS <= n; };
     auto issue = [&](long long tile) {
-        if (engine_tile(tile) && lane == 0) {
-            mbar_expect_tx(bar, (has_value_grad ? BYTES_S : 0u) + BYTES_D);
-            if (has_value_grad) bulk_load_global_to_smem(img_s, sph_grad + tile * TILE_POINTS * NY, BYTES_S, bar);
-            bulk_load_global_to_smem(img_d, dsph_grad + tile * TILE_POINTS * 3 * NY, BYTES_D, bar);
+        if (!engine_tile(tile)) return;
+        if (lane == 0) mbar_expect_tx(bar, (has_value_grad ? BYTES_S : 0u) + BYTES_D);
+        if constexpr (PAD == 0) {
+            if (lane == 0) {
+                if (has_value_grad) bulk_load_global_to_smem(img_s, sph_grad + tile * TILE_POINTS * NY, BYTES_S, bar);
+                bulk_load_global_to_smem(img_d, dsph_grad + tile * TILE_POINTS * 3 * NY, BYTES_D, bar);
+            }
+        } else {
+            __syncwarp();  // the expected byte count is set before any lane's copy can complete
+            const long long row = tile * TILE_POINTS + lane;
+            if (has_value_grad) bulk_load_global_to_smem(img_s + lane * S0, sph_grad + row * NY, unsigned(NY * sizeof(T)), bar);
+            bulk_load_global_to_smem(img_d + lane * S1, dsph_grad + row * 3 * NY, unsigned(3 * NY * sizeof(T)), bar);
         }
     };
     if (use_bulk) {

@@ -53,7 +53,6 @@ struct Knobs {
     int panel_threads;  // force the threads per CTA of the panel kernels (<= 256)
     int panel_iters;    // table batches per CTA of the panel kernels (k > 0), -1: persistent launch
     int panel_tables_f64;  // 1: table recurrences of the panel kernels in float64 for float32 outputs too
-    int vjp_split;      // -1: the one-warp-per-tile VJP kernel also where the shared-tile one is compiled
 };
 
 int env_int(const char* name, int fallback) {
@@ -71,8 +70,7 @@ const Knobs& knobs() {
                             env_int("SPH_B200_TILE_LMAX", TILE_LMAX), env_int("SPH_B200_NO_PANEL", 0),
                             env_int("SPH_B200_PANEL_BATCH", 0), env_int("SPH_B200_PANEL_POINTS", 0),
                             env_int("SPH_B200_PANEL_SLOTS", 0), env_int("SPH_B200_PANEL_THREADS", 0),
-                            env_int("SPH_B200_PANEL_ITERS", 0), env_int("SPH_B200_PANEL_TABLES_F64", 0),
-                            env_int("SPH_B200_VJP_SPLIT", 0)};
+                            env_int("SPH_B200_PANEL_ITERS", 0), env_int("SPH_B200_PANEL_TABLES_F64", 0)};
     return k;
 }
 
@@ -351,6 +349,9 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
         const size_t fixed = panel_fixed_bytes(l_max, batch, elem);
         for (int tp = batch; tp >= 1; tp /= 2) {
             if (k.panel_points > 0 && tp != k.panel_points) continue;
+            // table batches of 32 points only for whole-warp panels (measured, l_max = 16 float32 gradients,
+            // 16 points per panel: batches of 16 / 32 points -> 0.86 / 0.79)
+            if (batch == 32 && tp < 32 && k.panel_batch <= 0) continue;
             // rows of even length: neighbouring points sit a multiple of 16 bytes apart, which is
             // conflict-free for up to eight points side by side
             if (even_rows && tp > 8 && k.panel_points <= 0) continue;
@@ -359,8 +360,10 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                 if (k.panel_slots > 0 ? slots != k.panel_slots : slots != 1) continue;
                 const size_t smem = fixed + slots * image;
                 if (smem > smem_limit) break;
-                for (int per_slice = 1; per_slice <= nq; ++per_slice) {
-                    const int slices = (nq + per_slice - 1) / per_slice;
+                // the work a slice divides: (l, m) pairs, or - values only - pairs of rows (j, l_max - j)
+                const int items = level == 0 ? l_max / 2 + 1 : nq;
+                for (int per_slice = 1; per_slice <= items; ++per_slice) {
+                    const int slices = (items + per_slice - 1) / per_slice;
                     int threads = slices * tp;
                     if (k.panel_threads > 0) threads = k.panel_threads;
                     if (threads > 256) continue;
@@ -372,11 +375,13 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                     ctas = std::min<long long>(ctas, 65536 / (regs_alloc * warp_threads));
                     if (ctas < 1) continue;
                     const int real_slices = threads / tp;
-                    const int real_per_slice = (nq + real_slices - 1) / real_slices;
+                    const int real_per_slice = (items + real_slices - 1) / real_slices;
                     const double in_flight = std::min<double>(double(ctas * slots) * double(image), 160.0 * 1024) / (160.0 * 1024);
                     const double warps = std::min<double>(double(ctas * warp_threads / 32), 12.0) / 12.0;
-                    const double balance = double(nq) / (double(real_slices) * real_per_slice) * threads / warp_threads;
-                    const double panel_cost = real_per_slice / (real_per_slice + 2.0);
+                    const double balance = double(items) / (double(real_slices) * real_per_slice) * threads / warp_threads;
+                    // (a pair of rows is l_max + 2 steps of the recurrence, each writing a pair)
+                    const double pairs_each = level == 0 ? double(real_per_slice) * (l_max + 2) : double(real_per_slice);
+                    const double panel_cost = pairs_each / (pairs_each + 2.0);
                     const double table_busy = std::min(1.0, double(batch) * ((l_max + 2) / 2) / threads);
                     const double score = in_flight * warps * balance * panel_cost * (0.7 + 0.3 * table_busy) *
                                          (ctas >= 2 ? 1.0 : 0.8) * (tp == 32 ? 1.15 : 1.0);
@@ -534,24 +539,14 @@ template <typename T, int LMAX = TILE_LMAX> struct TileDispatch {
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                           const T* tables, int warps, bool use_bulk, int buffers, int iters, int device,
+                           const T* tables, int warps, bool use_bulk, int iters, int device,
                            cudaStream_t stream) {
         if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, buffers, iters,
+            return TileLaunch<T, LMAX>::vjp(normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk, iters,
                                             device, stream);
         if constexpr (LMAX > 0)
             return TileDispatch<T, LMAX - 1>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, warps, use_bulk,
-                                                  buffers, iters, device, stream);
-        return cudaErrorInvalidValue;
-    }
-    static cudaError_t vjp_split(int l_max, bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                 const T* tables, bool use_bulk, int iters, int device, cudaStream_t stream) {
-        if (l_max == LMAX)
-            return TileLaunch<T, LMAX>::vjp_split(normalized, xyz, sph_grad, n, xyz_grad, tables, use_bulk, iters, device,
-                                                  stream);
-        if constexpr (LMAX > 0)
-            return TileDispatch<T, LMAX - 1>::vjp_split(l_max, normalized, xyz, sph_grad, n, xyz_grad, tables, use_bulk,
-                                                        iters, device, stream);
+                                                  iters, device, stream);
         return cudaErrorInvalidValue;
     }
     static cudaError_t vjp2(int l_max, bool normalized, const T* xyz, const T* sph_grad, const T* dsph_grad, long long n,
@@ -673,30 +668,31 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
                   "tile second-order VJP kernel launch");
             return;
         }
-        // VJP: one image of upstream rows per warp. A second one (the next tile streaming in during the
-        // arithmetic) measured slower at every degree: more resident warps hide the load better
-        // (l_max = 10 float32: 1.03 against 0.61 of the copy peak, l_max = 4: 1.06 against 0.99).
+        // VJP: one image of upstream rows per warp (plus its mbarrier)
         const size_t vjp_image = size_t(32) * (n_columns(l_max) + tile_row_pad(n_columns(l_max), int(sizeof(T)))) * sizeof(T);
-        const int vjp_buffers = 1;
-        const size_t per_warp = kind == 3 ? vjp_buffers * vjp_image + 16
-                                          : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
-        if (kind == 3 && knobs().vjp_split >= 0 && vjp_split_compiled(l_max, int(sizeof(T)))) {
-            // long rows: the warps of a CTA share the tile's upstream rows and split its degrees
-            const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
-            check(TileDispatch<T>::vjp_split(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, use_bulk,
-                                             resolve_iters(knobs().vjp_iters, 2), scope.device, stream),
-                  "tile VJP kernel launch (shared tile)");
-            return;
-        }
+        const size_t per_warp = kind == 3 ? vjp_image + 16 : TileDispatch<T>::smem_per_warp(l_max, kind < 3 ? kind : 2);
         if (kind == 3) {
             const bool use_bulk = aligned16(sph_grad) && knobs().no_bulk == 0;
-            // short-lived CTAs of four warps; one tile per warp with a single image (nothing to overlap a
-            // second tile with), four with the double buffer
-            const int iters = resolve_iters(knobs().vjp_iters, vjp_buffers == 1 ? 1 : 4);
+            // short-lived CTAs of four warps, one tile per warp
+            const int iters = resolve_iters(knobs().vjp_iters, 1);
             int warps = tile_warps(per_warp, props.smem_optin);
-            if (iters > 0 && knobs().tile_warps == 0) warps = int(std::min<size_t>(4, std::max<size_t>(1, props.smem_optin / per_warp)));
+            if (iters > 0 && knobs().tile_warps == 0) {
+                // short-lived CTAs of up to four warps: the count that lets an SM hold the most warps (an
+                // SM has 228 KB of shared memory, 1 KB reserved per CTA), the larger CTA on a tie. With long
+                // rows this matters: at l_max = 16 float32 (37 KB per warp) CTAs of four warps fit once per
+                // SM, CTAs of three or two warps give six warps per SM.
+                size_t best = 0;
+                for (int w = 1; w <= 4; ++w) {
+                    if (w * per_warp > props.smem_optin) break;
+                    const size_t resident = std::min<size_t>(32, size_t(233472) / (w * per_warp + 1024)) * w;
+                    if (resident >= best) {
+                        best = resident;
+                        warps = w;
+                    }
+                }
+            }
             check(TileDispatch<T>::vjp(l_max, normalized, xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk,
-                                       vjp_buffers, iters, scope.device, stream),
+                                       iters, scope.device, stream),
                   "tile VJP kernel launch");
             return;
         }

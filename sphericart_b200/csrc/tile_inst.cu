@@ -3,7 +3,6 @@
 #include "sph_launch.hpp"
 #include "sph_select.cuh"
 #include "sph_tile.cuh"
-#include "sph_vjp_split.cuh"
 
 #include <atomic>
 
@@ -101,32 +100,17 @@ cudaError_t launch_forward(const T* xyz, long long n, T* sph, T* dsph, T* ddsph,
 
 template <typename T, int LMAX, bool NORM>
 cudaError_t launch_vjp(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, int warps,
-                       bool use_bulk, int buffers, int iters, int device, cudaStream_t stream) {
-    static GridCache cache[2] = {};
-    if (buffers != 1 && buffers != 2) return cudaErrorInvalidValue;
+                       bool use_bulk, int iters, int device, cudaStream_t stream) {
+    static GridCache cache{};
     auto kernel = sph_vjp_tile_kernel<T, LMAX, NORM>;
-    const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>(buffers);
-    const int max_blocks = cached_grid(cache[buffers - 1], kernel, warps, smem, device);
+    const size_t smem = size_t(warps) * vjp_tile_smem_bytes<T, LMAX>();
+    const int max_blocks = cached_grid(cache, kernel, warps, smem, device);
     if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
     const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
     const long long want = (ntiles + warps - 1) / warps;
     const int grid = work_grid(want, max_blocks, iters);
     kernel<<<grid, warps * 32, smem, stream>>>(xyz, sph_grad, n, xyz_grad, make_tables<T, LMAX>(host_tables),
-                                               use_bulk ? 1 : 0, buffers);
-    return cudaGetLastError();
-}
-
-template <typename T, int LMAX, bool NORM>
-cudaError_t launch_vjp_split(const T* xyz, const T* sph_grad, long long n, T* xyz_grad, const T* host_tables, bool use_bulk,
-                             int iters, int device, cudaStream_t stream) {
-    constexpr int W = vjp_split_warps(LMAX, int(sizeof(T)));
-    const size_t smem = vjp_split_smem_bytes<T, LMAX, W>();
-    const int max_blocks = memo_grid<sph_vjp_split_kernel<T, LMAX, NORM, W>>(32 * W, smem, device);
-    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
-    const long long ntiles = (n + TILE_POINTS - 1) / TILE_POINTS;
-    const int grid = work_grid(ntiles, max_blocks, iters);
-    sph_vjp_split_kernel<T, LMAX, NORM, W><<<grid, 32 * W, smem, stream>>>(xyz, sph_grad, n, xyz_grad,
-                                                                          make_tables<T, LMAX>(host_tables), use_bulk ? 1 : 0);
+                                               use_bulk ? 1 : 0);
     return cudaGetLastError();
 }
 
@@ -233,25 +217,13 @@ cudaError_t TileLaunch<T, LMAX>::forward(int level, bool normalized, const T* xy
 
 template <typename T, int LMAX>
 cudaError_t TileLaunch<T, LMAX>::vjp(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                     const T* host_tables, int warps, bool use_bulk, int buffers, int iters, int device,
+                                     const T* host_tables, int warps, bool use_bulk, int iters, int device,
                                      cudaStream_t stream) {
     if constexpr (tile_serves(3, LMAX, int(sizeof(T)))) {
-        return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, buffers,
+        return normalized ? launch_vjp<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk,
                                                       iters, device, stream)
-                          : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk, buffers,
+                          : launch_vjp<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, warps, use_bulk,
                                                        iters, device, stream);
-    } else {
-        return cudaErrorInvalidConfiguration;
-    }
-}
-
-template <typename T, int LMAX>
-cudaError_t TileLaunch<T, LMAX>::vjp_split(bool normalized, const T* xyz, const T* sph_grad, long long n, T* xyz_grad,
-                                           const T* host_tables, bool use_bulk, int iters, int device, cudaStream_t stream) {
-    if constexpr (vjp_split_compiled(LMAX, int(sizeof(T)))) {
-        return normalized
-                   ? launch_vjp_split<T, LMAX, true>(xyz, sph_grad, n, xyz_grad, host_tables, use_bulk, iters, device, stream)
-                   : launch_vjp_split<T, LMAX, false>(xyz, sph_grad, n, xyz_grad, host_tables, use_bulk, iters, device, stream);
     } else {
         return cudaErrorInvalidConfiguration;
     }

@@ -144,7 +144,7 @@ def test_launch_rules(tmp_path):
     assert serves[(1, 4)] == 10 and serves[(1, 8)] == 8           # gradients: the panel kernels take over earlier in float64
     assert serves[(2, 4)] == 4 and serves[(2, 8)] == 4            # Hessians
     assert serves[(3, 4)] == 20 and serves[(3, 8)] == 20          # VJP: two tiles of upstream rows per SM
-    assert serves[(4, 4)] == 5 and serves[(4, 8)] == 5            # second-order VJP
+    assert serves[(4, 4)] == 10 and serves[(4, 8)] == 8           # second-order VJP
 
 
 def test_out_buffers_are_validated_before_they_reach_a_kernel():

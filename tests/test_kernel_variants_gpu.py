@@ -74,8 +74,6 @@ VARIANTS = [
     {"SPH_B200_TILE_POINTS": "8"},
     {"SPH_B200_TILE_POINTS": "16", "SPH_B200_TILE_ITERS": "-1"},
     {"SPH_B200_TILE_POINTS": "32"},
-    # the one-warp-per-tile VJP kernel at the degrees where the shared-tile kernel normally takes over
-    {"SPH_B200_VJP_SPLIT": "-1"},
     # every degree above l_max = 2 through the run-time-degree kernels: the panel kernels (forward) ...
     {"SPH_B200_TILE_LMAX": "2"},
     # ... and the band kernel alone

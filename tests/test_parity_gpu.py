@@ -298,7 +298,7 @@ def test_fused_second_order_backward(sb, oracle_mod, dtype):
     dev = torch.device("cuda", 0)
     tol = 1e-12 if dtype == np.float64 else 1e-5
     for cls, normalized in _classes(sb):
-        for l_max in list(range(0, 10)) + [12, 16]:  # tile kernels up to 5, band kernel beyond
+        for l_max in list(range(0, 12)) + [12, 16]:  # tile kernels up to 10 (float32) / 8 (float64), band kernel beyond
             for n in (1, 33, 500):
                 ny = (l_max + 1) ** 2
                 xyz = (rng.standard_normal((n, 3)) * 1.4).astype(dtype)
