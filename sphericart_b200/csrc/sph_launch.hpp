@@ -24,7 +24,8 @@ constexpr int MAX_DEVICES = 64;
 //   Hessians      float32 l = 4: 0.88 / 0.86, l = 5: 0.57 / 0.67; float64 l = 4: 0.84 / 0.53, l = 5: 0.57 / 0.57
 //                                                               -> tile up to 4
 //   VJP           l = 9..20: 0.57-1.03 / 0.15-0.25 (band)       -> tile wherever compiled
-//   2nd-order VJP l = 5: 1.2-2.1 / 0.7-1.8 Gpoints/s, l = 6: 0.6-1.1 / 0.6-1.7 (band)   -> tile up to 5
+//   2nd-order VJP float32 l = 5: 1.02, l = 8: 0.59, l = 10: 0.39 / 0.25 (band), float64 l = 8: 0.50 / 0.19 (band at l = 9)
+//                                                               -> tile up to 10 (float32), 8 (float64)
 constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
     if (l_max > TILE_LMAX) return false;
     if (kind == 1) return l_max <= (elem_bytes == 4 ? 10 : 8);
@@ -141,6 +142,22 @@ template <typename T> struct BandLaunchArgs {
     int grid_cap;  // upper bound on the number of CTAs of a persistent launch (0 = none)
     int iters;     // see work_grid()
 };
+
+// Layout of the panel kernels' per-point state in shared memory (used by the kernels and by the plan).
+constexpr int PANEL_ROW_PAD = 4;    // zeros after the diagonal of every Q row
+
+// Element offset (for TPT = 1) of row l of the triangular Q table: a block of PANEL_ROW_PAD zeros
+// (standing for the rows -1 and -2), then row 0, row 1, ... each with its PANEL_ROW_PAD zeros.
+__host__ __device__ constexpr int panel_row_start(int l) { return PANEL_ROW_PAD + l * (l - 1) / 2 + (PANEL_ROW_PAD + 1) * l; }
+// Elements of per-point state: the point itself (x, y, z - normalised where the harmonics are - and
+// 1/r), c and s with two leading zeros each, then the Q table.
+// The values-only kernels keep no Q table (and stage no pair descriptors): they carry the rows in registers.
+__host__ __device__ constexpr int panel_point_state(int l_max, int level) {
+    return 4 + 2 * (l_max + 3) + (level >= 1 ? panel_row_start(l_max + 1) : 0);
+}
+// Values only: points per thread. A thread runs the same row for this many points of the panel at once:
+// independent recurrence chains, and the row's constants are read once for all of them.
+constexpr int PANEL_VALUES_PPT = 2;
 
 // Panel kernels, run-time l_max, forward levels only. Tables for TPT points at a time, tp points per
 // image (a power of two dividing TPT), threads / tp slices per point, `slots` images per CTA.

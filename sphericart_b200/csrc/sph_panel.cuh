@@ -42,19 +42,12 @@
 
 #include <cstdint>
 
+#include "sph_launch.hpp"  // layout constants shared with the host-side plan
 #include "sph_band.cuh"  // per-pair evaluation, shared-memory access helpers, bulk-store helpers
 
 namespace sph_b200 {
 
-constexpr int PANEL_ROW_PAD = 4;    // zeros after the diagonal of every Q row
 constexpr int PANEL_MAX_SLOTS = 4;  // images per CTA
-
-// Element offset (for TPT = 1) of row l of the triangular Q table: a block of PANEL_ROW_PAD zeros
-// (standing for the rows -1 and -2), then row 0, row 1, ... each with its PANEL_ROW_PAD zeros.
-__host__ __device__ constexpr int panel_row_start(int l) { return PANEL_ROW_PAD + l * (l - 1) / 2 + (PANEL_ROW_PAD + 1) * l; }
-// Elements of per-point state: the point itself (x, y, z - normalised where the harmonics are - and
-// 1/r), c and s with two leading zeros each, then the Q table.
-__host__ __device__ constexpr int panel_point_state(int l_max) { return 4 + 2 * (l_max + 3) + panel_row_start(l_max + 1); }
 
 // Elements between the image rows of neighbouring points for an array with `comps` rows of ny
 // columns per point. Odd ny: the rows are packed (the image is the exact picture of global memory).
@@ -185,7 +178,16 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
             row[(l - 1) * TPT] = T(q1);
             A tm = A(2 * (l - 1));  // 2 (m + 1)
             for (int m = l - 2; m >= 0; --m) {
-                const A q0 = A(Kl[m]) * (tm * zd * q1 + rhod * q2);
+                A q0;
+                if constexpr (sizeof(A) == 8) {
+                    // float64: the coefficients are formed off the dependent chain, which is then one
+                    // fused multiply-add per step instead of three operations (the rounding differs from
+                    // the reference's expression order by a few units of 1e-16 per step)
+                    const A k = A(Kl[m]);
+                    q0 = (k * (tm * zd)) * q1 + (k * rhod) * q2;
+                } else {
+                    q0 = A(Kl[m]) * (tm * zd * q1 + rhod * q2);
+                }
                 row[m * TPT] = T(q0);
                 q2 = q1;
                 q1 = q0;
@@ -217,21 +219,23 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     const int qa = tid % TPT;
     const int sa = tid / TPT;
     const int SA = blockDim.x / TPT;
-    // phase B: thread = (point of the panel, pair slice)
-    const int p = tid & (tp - 1);
-    const int s = tid / tp;
-    const int S = blockDim.x / tp;
+    // phase B: thread = (point of the panel, pair slice); values only: PPT points of the panel, lanes apart
+    constexpr int PPT = LEVEL == 0 ? PANEL_VALUES_PPT : 1;
+    const int lanes = tp / PPT;
+    const int p = tid & (lanes - 1);
+    const int s = tid / lanes;
+    const int S = blockDim.x / lanes;
 
     // carve-up: F | K | descriptors | per-point state of a batch (point-minor) | slots x images
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
     PanelDesc* sDesc = reinterpret_cast<PanelDesc*>(sF + align16_elems<T>(2 * nq));
-    T* state = reinterpret_cast<T*>(sDesc + nq);
+    T* state = reinterpret_cast<T*>(sDesc + (LEVEL >= 1 ? nq : 0));
     T* sP = state;              // x, y, z, 1/r of point q at sP[c * TPT + q]
     T* sc = sP + 4 * TPT;       // c_m of point q at sc[(m + 2) * TPT + q]
     T* ss = sc + (L + 3) * TPT;  // s_m likewise
     T* sQ = ss + (L + 3) * TPT;  // element e of point q at sQ[e * TPT + q]
-    T* images = state + align16_elems<T>(TPT * panel_point_state(L));
+    T* images = state + align16_elems<T>(TPT * panel_point_state(L, LEVEL));
     const int st0 = panel_point_stride(1, ny, int(sizeof(T)));
     const int st1 = panel_point_stride(3, ny, int(sizeof(T)));
     const int st2 = panel_point_stride(9, ny, int(sizeof(T)));
@@ -242,22 +246,24 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
 
     // ---- once per CTA: constants, and the zeros that never change
     for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
-    for (int t = tid; t < nq; t += blockDim.x) {
-        PanelDesc d = a.desc[t];
-        d.off0 *= int(E);
-        d.off1 *= int(E);
-        d.off2 *= int(E);
-        sDesc[t] = d;
-    }
     for (int e = tid; e < 2 * TPT; e += blockDim.x) {
         sc[e] = T(0);
         ss[e] = T(0);
     }
-    for (int e = tid; e < PANEL_ROW_PAD * TPT; e += blockDim.x) sQ[e] = T(0);
-    for (int e = tid; e < (L + 1) * PANEL_ROW_PAD * TPT; e += blockDim.x) {
-        const int l = e / (PANEL_ROW_PAD * TPT);
-        const int r = e % (PANEL_ROW_PAD * TPT);
-        sQ[(panel_row_start(l) + l + 1) * TPT + r] = T(0);
+    if constexpr (LEVEL >= 1) {
+        for (int t = tid; t < nq; t += blockDim.x) {
+            PanelDesc d = a.desc[t];
+            d.off0 *= int(E);
+            d.off1 *= int(E);
+            d.off2 *= int(E);
+            sDesc[t] = d;
+        }
+        for (int e = tid; e < PANEL_ROW_PAD * TPT; e += blockDim.x) sQ[e] = T(0);
+        for (int e = tid; e < (L + 1) * PANEL_ROW_PAD * TPT; e += blockDim.x) {
+            const int l = e / (PANEL_ROW_PAD * TPT);
+            const int r = e % (PANEL_ROW_PAD * TPT);
+            sQ[(panel_row_start(l) + l + 1) * TPT + r] = T(0);
+        }
     }
     __syncthreads();
 
@@ -448,6 +454,20 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                 };
                 if constexpr (LEVEL >= 1) {
                     int t = s;
+                    if constexpr (sizeof(T) == 8 && LEVEL == 1) {
+                        // float64 arithmetic has long dependent chains: four independent pairs in flight
+                        // (with Hessians four pairs' inputs no longer fit the registers)
+                        for (; t + 3 * S < nq; t += 4 * S) {
+                            const PairInputs<T, LEVEL> in0 = load(t);
+                            const PairInputs<T, LEVEL> in1 = load(t + S);
+                            const PairInputs<T, LEVEL> in2 = load(t + 2 * S);
+                            const PairInputs<T, LEVEL> in3 = load(t + 3 * S);
+                            finish_pair(in0);
+                            finish_pair(in1);
+                            finish_pair(in2);
+                            finish_pair(in3);
+                        }
+                    }
                     // two pairs in flight per thread
                     for (; t + S < nq; t += 2 * S) {
                         const PairInputs<T, LEVEL> in0 = load(t);
@@ -461,35 +481,59 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     // total length, carries each row's recurrence in registers (the reference's own scheme,
                     // sphericart/include/templates_core.hpp:123,155,202, in the element type) and writes the
                     // two values of every m as it goes: Y_{l,+m} = F Q_l^m c_m, Y_{l,-m} = F Q_l^m s_m.
-                    const T rho = x2 + y2;
-                    const T* cp = sc + sub + p + 2 * TPT;  // c_m at cp[m * TPT]
+                    // A thread does this for PPT points of the panel at once (points p, p + lanes, ...).
+                    T zz[PPT], rho[PPT];
+                    const T* cp = sc + sub + p + 2 * TPT;  // c_m of point i at cp[m * TPT + i * lanes]
                     const T* sp = ss + sub + p + 2 * TPT;
-                    T* out = image0 + p * st0;
+                    T* out = image0 + p * st0;             // row of point i at out + i * lanes * st0
+                    const int pst = lanes * st0;
+#pragma unroll
+                    for (int i = 0; i < PPT; ++i) {
+                        const T px = sP[0 * TPT + sub + p + i * lanes], py = sP[1 * TPT + sub + p + i * lanes];
+                        zz[i] = sP[2 * TPT + sub + p + i * lanes];
+                        rho[i] = px * px + py * py;
+                    }
                     auto row_values = [&](int l) {
                         const T* Kl = sK + tri(l, 0);
                         const T* Fl = sF + tri(l, 0);
                         T* mid = out + l * l + l;
-                        T q2 = Kl[l];  // Q_l^l is tabulated
+                        T q2[PPT], q1[PPT];
                         {
-                            const T pq = q2 * Fl[l];
-                            mid[l] = pq * cp[l * TPT];
-                            if (l > 0) mid[-l] = pq * sp[l * TPT];
+                            const T kll = Kl[l], fll = Fl[l];  // Q_l^l is tabulated
+#pragma unroll
+                            for (int i = 0; i < PPT; ++i) {
+                                q2[i] = kll;
+                                const T pq = kll * fll;
+                                mid[i * pst + l] = pq * cp[l * TPT + i * lanes];
+                                if (l > 0) mid[i * pst - l] = pq * sp[l * TPT + i * lanes];
+                            }
                         }
                         if (l >= 1) {
-                            T q1 = -z * q2;  // Q_l^{l-1}
-                            {
-                                const T pq = q1 * Fl[l - 1];
-                                mid[l - 1] = pq * cp[(l - 1) * TPT];
-                                if (l > 1) mid[1 - l] = pq * sp[(l - 1) * TPT];
+                            const T f1 = Fl[l - 1];
+#pragma unroll
+                            for (int i = 0; i < PPT; ++i) {
+                                q1[i] = -zz[i] * q2[i];  // Q_l^{l-1}
+                                const T pq = q1[i] * f1;
+                                mid[i * pst + l - 1] = pq * cp[(l - 1) * TPT + i * lanes];
+                                if (l > 1) mid[i * pst + 1 - l] = pq * sp[(l - 1) * TPT + i * lanes];
                             }
                             T tm = T(2 * (l - 1));  // 2 (m + 1)
                             for (int m = l - 2; m >= 0; --m) {
-                                const T q0 = Kl[m] * (tm * z * q1 + rho * q2);
-                                const T pq = q0 * Fl[m];
-                                mid[m] = pq * cp[m * TPT];
-                                if (m > 0) mid[-m] = pq * sp[m * TPT];
-                                q2 = q1;
-                                q1 = q0;
+                                const T km = Kl[m], fm = Fl[m];
+#pragma unroll
+                                for (int i = 0; i < PPT; ++i) {
+                                    T q0;
+                                    if constexpr (sizeof(T) == 8) {
+                                        q0 = (km * (tm * zz[i])) * q1[i] + (km * rho[i]) * q2[i];  // one dependent operation per step
+                                    } else {
+                                        q0 = km * (tm * zz[i] * q1[i] + rho[i] * q2[i]);
+                                    }
+                                    const T pq = q0 * fm;
+                                    mid[i * pst + m] = pq * cp[m * TPT + i * lanes];
+                                    if (m > 0) mid[i * pst - m] = pq * sp[m * TPT + i * lanes];
+                                    q2[i] = q1[i];
+                                    q1[i] = q0;
+                                }
                                 tm -= T(2);
                             }
                         }

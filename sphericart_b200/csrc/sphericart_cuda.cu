@@ -311,10 +311,10 @@ size_t panel_image_bytes(int l_max, int level, int tp, size_t elem) {
     return image * elem;
 }
 
-size_t panel_fixed_bytes(int l_max, int batch, size_t elem) {
+size_t panel_fixed_bytes(int l_max, int level, int batch, size_t elem) {
     const size_t nq = size_t(n_table(l_max));
-    const size_t consts = band_align16(2 * nq, elem) * elem + nq * 16;
-    const size_t per_point = 4 + 2 * size_t(l_max + 3) + size_t(4 + (l_max + 1) * l_max / 2 + 5 * (l_max + 1));
+    const size_t consts = band_align16(2 * nq, elem) * elem + (level >= 1 ? nq * 16 : 0);
+    const size_t per_point = size_t(panel_point_state(l_max, level));
     return consts + band_align16(size_t(batch) * per_point, elem) * elem;
 }
 
@@ -346,7 +346,7 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
     double best_score = -1.0;
     for (int batch = 32; batch >= 1; batch /= 2) {
         if (k.panel_batch > 0 && batch != k.panel_batch) continue;
-        const size_t fixed = panel_fixed_bytes(l_max, batch, elem);
+        const size_t fixed = panel_fixed_bytes(l_max, level, batch, elem);
         for (int tp = batch; tp >= 1; tp /= 2) {
             if (k.panel_points > 0 && tp != k.panel_points) continue;
             // table batches of 32 points only for whole-warp panels (measured, l_max = 16 float32 gradients,
@@ -362,19 +362,22 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                 if (smem > smem_limit) break;
                 // the work a slice divides: (l, m) pairs, or - values only - pairs of rows (j, l_max - j)
                 const int items = level == 0 ? l_max / 2 + 1 : nq;
+                // threads side by side in a slice: one per point, or - values only - one per PANEL_VALUES_PPT points
+                const int lanes = level == 0 ? tp / PANEL_VALUES_PPT : tp;
+                if (lanes < 1) continue;
                 for (int per_slice = 1; per_slice <= items; ++per_slice) {
                     const int slices = (items + per_slice - 1) / per_slice;
-                    int threads = slices * tp;
+                    int threads = slices * lanes;
                     if (k.panel_threads > 0) threads = k.panel_threads;
                     if (threads > 256) continue;
-                    if (threads < 64 && k.panel_threads <= 0) break;
+                    if (threads < (level == 0 ? 32 : 64) && k.panel_threads <= 0) break;
                     if (threads < batch) continue;
                     const int warp_threads = (threads + 31) / 32 * 32;
                     long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
                     ctas = std::min<long long>(ctas, 2048 / warp_threads);
                     ctas = std::min<long long>(ctas, 65536 / (regs_alloc * warp_threads));
                     if (ctas < 1) continue;
-                    const int real_slices = threads / tp;
+                    const int real_slices = threads / lanes;
                     const int real_per_slice = (items + real_slices - 1) / real_slices;
                     const double in_flight = std::min<double>(double(ctas * slots) * double(image), 160.0 * 1024) / (160.0 * 1024);
                     const double warps = std::min<double>(double(ctas * warp_threads / 32), 12.0) / 12.0;
