@@ -293,4 +293,78 @@ __device__ __forceinline__ void eval_point(T x, T y, T z, const Tables<T, LMAX>&
     }
 }
 
+// Vector-Jacobian product of one point with the maximum degree known at compile time:
+//   (ax, ay, az) = sum_k g[k] dY_k/d(x, y, z)
+// at the point (x, y, z) as given (for the normalised harmonics the caller passes the unit vector and
+// applies the linear chain rule to the result). Same Q recurrence and prefactors as eval_point, but the
+// gradient columns are never formed: with W = g+ c_m + g- s_m, U = g+ c_{m-1} + g- s_{m-1},
+// V = g- c_{m-1} - g+ s_{m-1} (g+, g- the upstream entries of the columns +m and -m) the reference's
+// expressions for the pair's six derivatives (sphericart/include/templates_core.hpp:201-292) contract to
+//   ax += m F Q_l^m U + x F Q_{l-1}^{m+1} W,   ay += m F Q_l^m V + y F Q_{l-1}^{m+1} W,
+//   az += (l+m) F Q_{l-1}^m W,
+// and the common factors x, y of the second terms are applied once to their sum: 15 operations per pair
+// instead of 21, and a third less code to fetch (the fully unrolled body is bound by instruction issue
+// and fetch from l_max = 14 on).
+template <typename T, int LMAX>
+__device__ __forceinline__ void eval_point_vjp(T x, T y, T z, const Tables<T, LMAX>& tab, const T* g, T& ax, T& ay, T& az) {
+    const T rho = x * x + y * y;
+    T c[LMAX + 1], s[LMAX + 1], tz[LMAX + 1];
+    c[0] = T(1);
+    s[0] = T(0);
+    const T twoz = z + z;
+    tz[0] = twoz;
+    static_for<1, LMAX + 1>([&](auto mc) {
+        constexpr int m = decltype(mc)::value;
+        c[m] = c[m - 1] * x - s[m - 1] * y;
+        s[m] = c[m - 1] * y + s[m - 1] * x;
+        tz[m] = tz[m - 1] + twoz;
+    });
+    T sx = T(0), sy = T(0), sz = T(0), sw = T(0);  // sw: the sum that x and y multiply
+    if constexpr (LMAX >= 1) {
+        const T a1 = T(0.48860251190292);
+        sy = a1 * g[1];
+        sz = a1 * g[2];
+        sx = a1 * g[3];
+    }
+    if constexpr (LMAX >= 2) {
+        T Q[n_table(LMAX)];
+        Q[tri(0, 0)] = tab.K[tri(0, 0)];
+        Q[tri(1, 1)] = tab.K[tri(1, 1)];
+        Q[tri(1, 0)] = -z * Q[tri(1, 1)];
+        static_for<2, LMAX + 1>([&](auto lc) {
+            constexpr int l = decltype(lc)::value;
+            constexpr int mid = l * l + l;
+            Q[tri(l, l)] = tab.K[tri(l, l)];
+            Q[tri(l, l - 1)] = -z * Q[tri(l, l)];
+            static_for_down<l - 2, 0>([&](auto mc) {
+                constexpr int m = decltype(mc)::value;
+                Q[tri(l, m)] = tab.K[tri(l, m)] * (tz[m] * Q[tri(l, m + 1)] + rho * Q[tri(l, m + 2)]);
+            });
+            static_for_down<l, 1>([&](auto mc) {
+                constexpr int m = decltype(mc)::value;
+                const T f = tab.F[tri(l, m)];
+                const T gp = g[mid + m], gm = g[mid - m];
+                const T u = gp * c[m - 1] + gm * s[m - 1];
+                const T v = gm * c[m - 1] - gp * s[m - 1];
+                const T pqm = Q[tri(l, m)] * f * T(m);
+                sx += pqm * u;
+                sy += pqm * v;
+                if constexpr (m <= l - 1) {
+                    const T w = gp * c[m] + gm * s[m];
+                    if constexpr (m + 1 <= l - 1) sw += f * Q[tri(l - 1, m + 1)] * w;
+                    sz += f * T(l + m) * Q[tri(l - 1, m)] * w;
+                }
+            });
+            {
+                const T fg = tab.F[tri(l, 0)] * g[mid];
+                sw += fg * Q[tri(l - 1, 1)];
+                sz += fg * T(l) * Q[tri(l - 1, 0)];
+            }
+        });
+    }
+    ax = sx + x * sw;
+    ay = sy + y * sw;
+    az = sz;
+}
+
 }  // namespace sph_b200

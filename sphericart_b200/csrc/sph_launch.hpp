@@ -155,9 +155,10 @@ __host__ __device__ constexpr int panel_row_start(int l) { return PANEL_ROW_PAD 
 __host__ __device__ constexpr int panel_point_state(int l_max, int level) {
     return 4 + 2 * (l_max + 3) + (level >= 1 ? panel_row_start(l_max + 1) : 0);
 }
-// Values only: points per thread. A thread runs the same row for this many points of the panel at once:
-// independent recurrence chains, and the row's constants are read once for all of them.
-constexpr int PANEL_VALUES_PPT = 2;
+// Values only: points per thread. A thread runs the same row for this many neighbouring points of the panel
+// at once (16 bytes' worth: their table entries arrive as one vector load): independent recurrence chains,
+// and the row's constants are read once for all of them.
+__host__ __device__ constexpr int panel_values_ppt(int elem_bytes) { return 16 / elem_bytes; }
 
 // Panel kernels, run-time l_max, forward levels only. Tables for TPT points at a time, tp points per
 // image (a power of two dividing TPT), threads / tp slices per point, `slots` images per CTA.

@@ -140,7 +140,7 @@ __device__ __forceinline__ void bulk_wait_read_pending(int pending) {
 // double (rounded once on storing) or the element type itself.
 template <typename T, typename A, int TPT, bool WITH_Q = true>
 __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa, int SA, int qa, T* sc, T* ss, T* sQ,
-                                                   const T* sK) {
+                                                   const T* sK, bool fast_chain = true) {
     const A xd = A(x), yd = A(y), zd = A(z);
     const A rhod = xd * xd + yd * yd;
     const int block = (L + SA) / SA;  // ceil((L + 1) / SA)
@@ -179,7 +179,7 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
             A tm = A(2 * (l - 1));  // 2 (m + 1)
             for (int m = l - 2; m >= 0; --m) {
                 A q0;
-                if constexpr (sizeof(A) == 8) {
+                if (sizeof(A) == 8 && fast_chain) {
                     // float64: the coefficients are formed off the dependent chain, which is then one
                     // fused multiply-add per step instead of three operations (the rounding differs from
                     // the reference's expression order by a few units of 1e-16 per step)
@@ -220,11 +220,18 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     const int sa = tid / TPT;
     const int SA = blockDim.x / TPT;
     // phase B: thread = (point of the panel, pair slice); values only: PPT points of the panel, lanes apart
-    constexpr int PPT = LEVEL == 0 ? PANEL_VALUES_PPT : 1;
+    constexpr int PPT = LEVEL == 0 ? panel_values_ppt(int(sizeof(T))) : 1;
     const int lanes = tp / PPT;
     const int p = tid & (lanes - 1);
     const int s = tid / lanes;
     const int S = blockDim.x / lanes;
+    // Table slot of phase A's point. Values only: the PPT points of a phase B thread (r = p + i lanes within
+    // their panel) take the neighbouring slots PPT p + i, so that one vector load fetches them all.
+    int qs = qa;
+    if constexpr (LEVEL == 0) {
+        const int r = qa & (tp - 1);
+        qs = (qa - r) + PPT * (r & (lanes - 1)) + r / lanes;
+    }
 
     // carve-up: F | K | descriptors | per-point state of a batch (point-minor) | slots x images
     T* sF = reinterpret_cast<T*>(smem_raw);
@@ -306,15 +313,15 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
             }
             if (sa == 0) {
                 // phase B reads the point from here
-                sP[0 * TPT + qa] = x;
-                sP[1 * TPT + qa] = y;
-                sP[2 * TPT + qa] = z;
-                sP[3 * TPT + qa] = ir;
+                sP[0 * TPT + qs] = x;
+                sP[1 * TPT + qs] = y;
+                sP[2 * TPT + qs] = z;
+                sP[3 * TPT + qs] = ir;
             }
-            if (a.tables_f64 != 0) {
-                panel_build_tables<T, double, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
+            if ((a.tables_f64 & 1) != 0) {
+                panel_build_tables<T, double, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qs, sc, ss, sQ, sK, (a.tables_f64 & 2) == 0);
             } else {
-                panel_build_tables<T, T, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qa, sc, ss, sQ, sK);
+                panel_build_tables<T, T, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qs, sc, ss, sQ, sK, (a.tables_f64 & 2) == 0);
             }
         }
 
@@ -457,7 +464,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     if constexpr (sizeof(T) == 8 && LEVEL == 1) {
                         // float64 arithmetic has long dependent chains: four independent pairs in flight
                         // (with Hessians four pairs' inputs no longer fit the registers)
-                        for (; t + 3 * S < nq; t += 4 * S) {
+                        for (; (a.tables_f64 & 4) == 0 && t + 3 * S < nq; t += 4 * S) {
                             const PairInputs<T, LEVEL> in0 = load(t);
                             const PairInputs<T, LEVEL> in1 = load(t + S);
                             const PairInputs<T, LEVEL> in2 = load(t + 2 * S);
@@ -481,58 +488,98 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     // total length, carries each row's recurrence in registers (the reference's own scheme,
                     // sphericart/include/templates_core.hpp:123,155,202, in the element type) and writes the
                     // two values of every m as it goes: Y_{l,+m} = F Q_l^m c_m, Y_{l,-m} = F Q_l^m s_m.
-                    // A thread does this for PPT points of the panel at once (points p, p + lanes, ...).
-                    T zz[PPT], rho[PPT];
-                    const T* cp = sc + sub + p + 2 * TPT;  // c_m of point i at cp[m * TPT + i * lanes]
-                    const T* sp = ss + sub + p + 2 * TPT;
-                    T* out = image0 + p * st0;             // row of point i at out + i * lanes * st0
+                    // A thread does this for PPT neighbouring points of the panel at once: their c_m (s_m) sit
+                    // side by side in the point-minor tables and arrive as one 16-byte load, the row's
+                    // constants are read once for all of them, and in float32 two points share each
+                    // arithmetic instruction (packed fma.rn.f32x2).
+                    // (thread p's points are p, p + lanes, ... of the panel: rows `lanes` apart in the image, which
+                    // keeps a warp's image writes conflict-free; their table entries sit in neighbouring slots)
+                    const int q0i = sub + PPT * p;     // first of this thread's table slots within the batch
+                    const T* cp = sc + 2 * TPT + q0i;  // c_m of point i at cp[m * TPT + i]
+                    const T* sp = ss + 2 * TPT + q0i;
+                    T* out = image0 + p * st0;         // row of point i at out + i * pst
                     const int pst = lanes * st0;
+                    T zz[PPT], rho[PPT];
 #pragma unroll
                     for (int i = 0; i < PPT; ++i) {
-                        const T px = sP[0 * TPT + sub + p + i * lanes], py = sP[1 * TPT + sub + p + i * lanes];
-                        zz[i] = sP[2 * TPT + sub + p + i * lanes];
+                        const T px = sP[0 * TPT + q0i + i], py = sP[1 * TPT + q0i + i];
+                        zz[i] = sP[2 * TPT + q0i + i];
                         rho[i] = px * px + py * py;
                     }
+                    // the PPT values of one table row, as one 16-byte load
+                    auto load_vec = [](const T* ptr, T (&v)[PPT]) {
+                        if constexpr (sizeof(T) == 4) {
+                            const float4 t = *reinterpret_cast<const float4*>(ptr);
+                            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+                        } else {
+                            const double2 t = *reinterpret_cast<const double2*>(ptr);
+                            v[0] = t.x; v[1] = t.y;
+                        }
+                    };
+                    // writes F Q (c_m, s_m) of every point for one m; q holds Q_l^m per point
+                    auto emit = [&](T* mid, int m, T fm, const T (&q)[PPT]) {
+                        T cv[PPT], sv[PPT];
+                        load_vec(cp + m * TPT, cv);
+                        load_vec(sp + m * TPT, sv);
+                        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                            for (int i = 0; i < PPT; i += 2) {
+                                const F2 pq = f2(q[i], q[i + 1]) * bc(fm);
+                                const F2 yp = pq * f2(cv[i], cv[i + 1]);
+                                const F2 ym = pq * f2(sv[i], sv[i + 1]);
+                                mid[i * pst + m] = yp.v.x;
+                                mid[(i + 1) * pst + m] = yp.v.y;
+                                if (m > 0) {
+                                    mid[i * pst - m] = ym.v.x;
+                                    mid[(i + 1) * pst - m] = ym.v.y;
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < PPT; ++i) {
+                                const T pq = q[i] * fm;
+                                mid[i * pst + m] = pq * cv[i];
+                                if (m > 0) mid[i * pst - m] = pq * sv[i];
+                            }
+                        }
+                    };
                     auto row_values = [&](int l) {
                         const T* Kl = sK + tri(l, 0);
                         const T* Fl = sF + tri(l, 0);
                         T* mid = out + l * l + l;
                         T q2[PPT], q1[PPT];
-                        {
-                            const T kll = Kl[l], fll = Fl[l];  // Q_l^l is tabulated
+                        const T kll = Kl[l];  // Q_l^l is tabulated
 #pragma unroll
-                            for (int i = 0; i < PPT; ++i) {
-                                q2[i] = kll;
-                                const T pq = kll * fll;
-                                mid[i * pst + l] = pq * cp[l * TPT + i * lanes];
-                                if (l > 0) mid[i * pst - l] = pq * sp[l * TPT + i * lanes];
-                            }
-                        }
+                        for (int i = 0; i < PPT; ++i) q2[i] = kll;
+                        emit(mid, l, Fl[l], q2);
                         if (l >= 1) {
-                            const T f1 = Fl[l - 1];
 #pragma unroll
-                            for (int i = 0; i < PPT; ++i) {
-                                q1[i] = -zz[i] * q2[i];  // Q_l^{l-1}
-                                const T pq = q1[i] * f1;
-                                mid[i * pst + l - 1] = pq * cp[(l - 1) * TPT + i * lanes];
-                                if (l > 1) mid[i * pst + 1 - l] = pq * sp[(l - 1) * TPT + i * lanes];
-                            }
+                            for (int i = 0; i < PPT; ++i) q1[i] = -zz[i] * q2[i];  // Q_l^{l-1}
+                            emit(mid, l - 1, Fl[l - 1], q1);
                             T tm = T(2 * (l - 1));  // 2 (m + 1)
                             for (int m = l - 2; m >= 0; --m) {
-                                const T km = Kl[m], fm = Fl[m];
+                                const T km = Kl[m];
+                                T q0[PPT];
+                                if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                                    for (int i = 0; i < PPT; i += 2) {
+                                        const F2 a1 = bc(tm) * f2(zz[i], zz[i + 1]) * f2(q1[i], q1[i + 1]);
+                                        const F2 r = bc(km) * fma2(f2(rho[i], rho[i + 1]), f2(q2[i], q2[i + 1]), a1);
+                                        q0[i] = r.v.x;
+                                        q0[i + 1] = r.v.y;
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < PPT; ++i) {
+                                        // one dependent operation per step: the coefficients are formed off the chain
+                                        q0[i] = (km * (tm * zz[i])) * q1[i] + (km * rho[i]) * q2[i];
+                                    }
+                                }
+                                emit(mid, m, Fl[m], q0);
 #pragma unroll
                                 for (int i = 0; i < PPT; ++i) {
-                                    T q0;
-                                    if constexpr (sizeof(T) == 8) {
-                                        q0 = (km * (tm * zz[i])) * q1[i] + (km * rho[i]) * q2[i];  // one dependent operation per step
-                                    } else {
-                                        q0 = km * (tm * zz[i] * q1[i] + rho[i] * q2[i]);
-                                    }
-                                    const T pq = q0 * fm;
-                                    mid[i * pst + m] = pq * cp[m * TPT + i * lanes];
-                                    if (m > 0) mid[i * pst - m] = pq * sp[m * TPT + i * lanes];
                                     q2[i] = q1[i];
-                                    q1[i] = q0;
+                                    q1[i] = q0[i];
                                 }
                                 tm -= T(2);
                             }

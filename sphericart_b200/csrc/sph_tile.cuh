@@ -242,21 +242,12 @@ sph_tile_kernel(const T* __restrict__ xyz, long long n, T* __restrict__ sph, T* 
 // Fused vector-Jacobian product: xyz_grad[i][a] = sum_k sph_grad[i][k] * dY[i][a][k], without
 // ever writing dY to memory. The tile's 32 rows of sph_grad are one contiguous span of the
 // input; the warp loads it with coalesced reads into shared memory, then thread t walks row t
-// (odd stride: conflict-free) while it evaluates the gradient columns in registers.
+// (odd stride: conflict-free) while it accumulates the contraction in registers
+// (eval_point_vjp in sph_core.cuh: the gradient columns themselves are never formed).
 //
 // Replaces the reference's backward (a gradients launch that materialises dsph, then an
 // element-wise product and a reduction: sphericart-torch/python/sphericart/torch/register.py:90-108)
 // and its unused backward_kernel (sphericart/src/sphericart_impl.cu:650-684).
-template <typename T, int NY> struct VjpSink {
-    const T* g;  // this point's row of the upstream gradient, in shared memory
-    T ax, ay, az;
-    template <int K> __device__ __forceinline__ void put(const Column<T>& v) {
-        const T gk = g[K];
-        ax += gk * v.gx;
-        ay += gk * v.gy;
-        az += gk * v.gz;
-    }
-};
 
 // ---- mbarrier + TMA 1-D bulk load (global -> the issuing CTA's own shared memory) ----------
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
@@ -393,20 +384,23 @@ sph_vjp_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, l
 
         // The chain rule through r -> r/|r| is linear in the gradient, so it is applied once to the
         // accumulated sum of raw gradients instead of to each of the (l_max+1)^2 columns.
-        VjpSink<T, NY> sink{img + lane * S, T(0), T(0), T(0)};
-        eval_point<T, LMAX, 1, NORM, VjpSink<T, NY>, true>(x, y, z, tab, sink);
+        T ax, ay, az;
         if constexpr (NORM) {
+            // IEEE square root and division, as on the CPU (sphericart/include/templates.hpp:392-400)
             const T ir = T(1) / sqrt(x * x + y * y + z * z);
             const T ux = x * ir, uy = y * ir, uz = z * ir;
-            const T t = sink.ax * ux + sink.ay * uy + sink.az * uz;
-            sink.ax = (sink.ax - ux * t) * ir;
-            sink.ay = (sink.ay - uy * t) * ir;
-            sink.az = (sink.az - uz * t) * ir;
+            eval_point_vjp<T, LMAX>(ux, uy, uz, tab, img + lane * S, ax, ay, az);
+            const T t = ax * ux + ay * uy + az * uz;
+            ax = (ax - ux * t) * ir;
+            ay = (ay - uy * t) * ir;
+            az = (az - uz * t) * ir;
+        } else {
+            eval_point_vjp<T, LMAX>(x, y, z, tab, img + lane * S, ax, ay, az);
         }
         if (i < n) {
-            xyz_grad[3 * i + 0] = sink.ax;
-            xyz_grad[3 * i + 1] = sink.ay;
-            xyz_grad[3 * i + 2] = sink.az;
+            xyz_grad[3 * i + 0] = ax;
+            xyz_grad[3 * i + 1] = ay;
+            xyz_grad[3 * i + 2] = az;
         }
         // the image is written next by the TMA engine (async proxy) after having been read through
         // ordinary loads: order the two, then ask for the next tile

@@ -354,7 +354,9 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
             if (batch == 32 && tp < 32 && k.panel_batch <= 0) continue;
             // rows of even length: neighbouring points sit a multiple of 16 bytes apart, which is
             // conflict-free for up to eight points side by side
-            if (even_rows && tp > 8 && k.panel_points <= 0) continue;
+            // (values only: the threads of a slice hold every fourth / second point)
+            const int side_by_side = level == 0 ? tp / panel_values_ppt(int(elem)) : tp;
+            if (even_rows && side_by_side > 8 && k.panel_points <= 0) continue;
             const size_t image = panel_image_bytes(l_max, level, tp, elem);
             for (int slots = 1; slots <= 4; ++slots) {
                 if (k.panel_slots > 0 ? slots != k.panel_slots : slots != 1) continue;
@@ -362,8 +364,8 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                 if (smem > smem_limit) break;
                 // the work a slice divides: (l, m) pairs, or - values only - pairs of rows (j, l_max - j)
                 const int items = level == 0 ? l_max / 2 + 1 : nq;
-                // threads side by side in a slice: one per point, or - values only - one per PANEL_VALUES_PPT points
-                const int lanes = level == 0 ? tp / PANEL_VALUES_PPT : tp;
+                // threads side by side in a slice: one per point, or - values only - one per 16 bytes' worth of points
+                const int lanes = level == 0 ? tp / panel_values_ppt(int(elem)) : tp;
                 if (lanes < 1) continue;
                 for (int per_slice = 1; per_slice <= items; ++per_slice) {
                     const int slices = (items + per_slice - 1) / per_slice;

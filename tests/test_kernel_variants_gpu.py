@@ -55,7 +55,10 @@ print("WORST", worst["f32"], worst["f64"])
 """
 
 CASES = [(True, "f32", 3, 2, 70), (False, "f32", 8, 1, 333), (True, "f64", 6, 2, 65), (True, "f32", 12, 1, 257),
-         (True, "f64", 20, 1, 100), (False, "f64", 33, 2, 33), (True, "f32", 16, 2, 129), (True, "f64", 32, 1, 64)]
+         (True, "f64", 20, 1, 100), (False, "f64", 33, 2, 33), (True, "f32", 16, 2, 129), (True, "f64", 32, 1, 64),
+         # values only (the panel kernels carry the rows in registers there): even and odd row lengths; float32 stays
+         # below l_max = 19, where its gradients - the VJP half of the check is against float64 - lose their accuracy
+         (True, "f32", 18, 0, 100), (False, "f64", 9, 0, 77), (True, "f64", 31, 0, 45)]
 
 VARIANTS = [
     {},
