@@ -176,22 +176,45 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
         if (l >= 1) {
             A q1 = -zd * q2;  // Q_l^{l-1}
             row[(l - 1) * TPT] = T(q1);
-            A tm = A(2 * (l - 1));  // 2 (m + 1)
-            for (int m = l - 2; m >= 0; --m) {
-                A q0;
-                if (sizeof(A) == 8 && fast_chain) {
-                    // float64: the coefficients are formed off the dependent chain, which is then one
-                    // fused multiply-add per step instead of three operations (the rounding differs from
-                    // the reference's expression order by a few units of 1e-16 per step)
-                    const A k = A(Kl[m]);
-                    q0 = (k * (tm * zd)) * q1 + (k * rhod) * q2;
-                } else {
-                    q0 = A(Kl[m]) * (tm * zd * q1 + rhod * q2);
+            if (sizeof(A) == 8 && fast_chain) {
+                // float64: the coefficients K 2(m+1) z and K rho are formed off the dependent chain, which
+                // is then one fused multiply-add per step instead of three operations; unrolled so that the
+                // loads of K and the coefficient products of several steps are issued ahead of the chain
+                // (the rounding differs from the reference's expression order by a few units of 1e-16 per step)
+                const A twoz = zd + zd;
+                int m = l - 2;
+                for (; m >= 3; m -= 4) {
+                    const A k0 = A(Kl[m]), k1 = A(Kl[m - 1]), k2 = A(Kl[m - 2]), k3 = A(Kl[m - 3]);
+                    const A a0 = k0 * (A(m + 1) * twoz), a1 = k1 * (A(m) * twoz), a2 = k2 * (A(m - 1) * twoz),
+                            a3 = k3 * (A(m - 2) * twoz);
+                    const A b0 = k0 * rhod, b1 = k1 * rhod, b2 = k2 * rhod, b3 = k3 * rhod;
+                    const A r0 = a0 * q1 + b0 * q2;
+                    const A r1 = a1 * r0 + b1 * q1;
+                    const A r2 = a2 * r1 + b2 * r0;
+                    const A r3 = a3 * r2 + b3 * r1;
+                    row[m * TPT] = T(r0);
+                    row[(m - 1) * TPT] = T(r1);
+                    row[(m - 2) * TPT] = T(r2);
+                    row[(m - 3) * TPT] = T(r3);
+                    q2 = r2;
+                    q1 = r3;
                 }
-                row[m * TPT] = T(q0);
-                q2 = q1;
-                q1 = q0;
-                tm -= A(2);
+                for (; m >= 0; --m) {
+                    const A k = A(Kl[m]);
+                    const A q0 = (k * (A(m + 1) * twoz)) * q1 + (k * rhod) * q2;
+                    row[m * TPT] = T(q0);
+                    q2 = q1;
+                    q1 = q0;
+                }
+            } else {
+                A tm = A(2 * (l - 1));  // 2 (m + 1)
+                for (int m = l - 2; m >= 0; --m) {
+                    const A q0 = A(Kl[m]) * (tm * zd * q1 + rhod * q2);
+                    row[m * TPT] = T(q0);
+                    q2 = q1;
+                    q1 = q0;
+                    tm -= A(2);
+                }
             }
         }
     };
@@ -461,20 +484,6 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                 };
                 if constexpr (LEVEL >= 1) {
                     int t = s;
-                    if constexpr (sizeof(T) == 8 && LEVEL == 1) {
-                        // float64 arithmetic has long dependent chains: four independent pairs in flight
-                        // (with Hessians four pairs' inputs no longer fit the registers)
-                        for (; (a.tables_f64 & 4) == 0 && t + 3 * S < nq; t += 4 * S) {
-                            const PairInputs<T, LEVEL> in0 = load(t);
-                            const PairInputs<T, LEVEL> in1 = load(t + S);
-                            const PairInputs<T, LEVEL> in2 = load(t + 2 * S);
-                            const PairInputs<T, LEVEL> in3 = load(t + 3 * S);
-                            finish_pair(in0);
-                            finish_pair(in1);
-                            finish_pair(in2);
-                            finish_pair(in3);
-                        }
-                    }
                     // two pairs in flight per thread
                     for (; t + S < nq; t += 2 * S) {
                         const PairInputs<T, LEVEL> in0 = load(t);

@@ -388,8 +388,17 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                     const double pairs_each = level == 0 ? double(real_per_slice) * (l_max + 2) : double(real_per_slice);
                     const double panel_cost = pairs_each / (pairs_each + 2.0);
                     const double table_busy = std::min(1.0, double(batch) * ((l_max + 2) / 2) / threads);
-                    const double score = in_flight * warps * balance * panel_cost * (0.7 + 0.3 * table_busy) *
-                                         (ctas >= 2 ? 1.0 : 0.8) * (tp == 32 ? 1.15 : 1.0);
+                    double score = in_flight * warps * balance * panel_cost * (0.7 + 0.3 * table_busy) *
+                                   (ctas >= 2 ? 1.0 : 0.8) * (tp == 32 ? 1.15 : 1.0);
+                    if (level == 0) {
+                        // Values only: a thread carries 16 bytes' worth of points through whole rows, which gives
+                        // it the independent work that the other levels get from many warps. Measured (float32
+                        // l_max = 24, float64 l_max = 32): eight threads side by side (32 / 16 points per panel) and
+                        // one pair of rows per thread is best even where only one or two CTAs fit an SM
+                        // (float32 l_max = 24: 32 / 16 / 8 points per panel -> 0.79 / 0.64 / 0.56 of the copy peak;
+                        // two pairs of rows per thread: 0.49; float64 l_max = 32: 16 / 8 / 4 points -> 0.53 / 0.47 / 0.41).
+                        score = std::min(lanes, 8) / 8.0 * balance / real_per_slice * (0.85 + 0.05 * std::min<long long>(ctas, 3));
+                    }
                     if (score > best_score + 1e-9) {
                         best_score = score;
                         best.batch = batch;
