@@ -140,7 +140,7 @@ __device__ __forceinline__ void bulk_wait_read_pending(int pending) {
 // double (rounded once on storing) or the element type itself.
 template <typename T, typename A, int TPT, bool WITH_Q = true>
 __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa, int SA, int qa, T* sc, T* ss, T* sQ,
-                                                   const T* sK, bool fast_chain = true) {
+                                                   const T* sK) {
     const A xd = A(x), yd = A(y), zd = A(z);
     const A rhod = xd * xd + yd * yd;
     const int block = (L + SA) / SA;  // ceil((L + 1) / SA)
@@ -176,11 +176,12 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
         if (l >= 1) {
             A q1 = -zd * q2;  // Q_l^{l-1}
             row[(l - 1) * TPT] = T(q1);
-            if (sizeof(A) == 8 && fast_chain) {
+            if constexpr (sizeof(A) == 8) {
                 // float64: the coefficients K 2(m+1) z and K rho are formed off the dependent chain, which
                 // is then one fused multiply-add per step instead of three operations; unrolled so that the
                 // loads of K and the coefficient products of several steps are issued ahead of the chain
-                // (the rounding differs from the reference's expression order by a few units of 1e-16 per step)
+                // (the rounding differs from the reference's expression order by a few units of 1e-16 per step;
+                // measured on l_max = 32 gradients, 1e6 points: 7.50 ms against 7.78 ms for the rolled loop)
                 const A twoz = zd + zd;
                 int m = l - 2;
                 for (; m >= 3; m -= 4) {
@@ -207,13 +208,27 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
                     q1 = q0;
                 }
             } else {
-                A tm = A(2 * (l - 1));  // 2 (m + 1)
-                for (int m = l - 2; m >= 0; --m) {
-                    const A q0 = A(Kl[m]) * (tm * zd * q1 + rhod * q2);
+                // the reference's expression order; four steps per turn so that the loads of K are issued
+                // ahead of the dependent chain instead of inside it
+                int m = l - 2;
+                for (; m >= 3; m -= 4) {
+                    const A k0 = A(Kl[m]), k1 = A(Kl[m - 1]), k2 = A(Kl[m - 2]), k3 = A(Kl[m - 3]);
+                    const A r0 = k0 * (A(2 * (m + 1)) * zd * q1 + rhod * q2);
+                    const A r1 = k1 * (A(2 * m) * zd * r0 + rhod * q1);
+                    const A r2 = k2 * (A(2 * (m - 1)) * zd * r1 + rhod * r0);
+                    const A r3 = k3 * (A(2 * (m - 2)) * zd * r2 + rhod * r1);
+                    row[m * TPT] = T(r0);
+                    row[(m - 1) * TPT] = T(r1);
+                    row[(m - 2) * TPT] = T(r2);
+                    row[(m - 3) * TPT] = T(r3);
+                    q2 = r2;
+                    q1 = r3;
+                }
+                for (; m >= 0; --m) {
+                    const A q0 = A(Kl[m]) * (A(2 * (m + 1)) * zd * q1 + rhod * q2);
                     row[m * TPT] = T(q0);
                     q2 = q1;
                     q1 = q0;
-                    tm -= A(2);
                 }
             }
         }
@@ -341,10 +356,10 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                 sP[2 * TPT + qs] = z;
                 sP[3 * TPT + qs] = ir;
             }
-            if ((a.tables_f64 & 1) != 0) {
-                panel_build_tables<T, double, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qs, sc, ss, sQ, sK, (a.tables_f64 & 2) == 0);
+            if (a.tables_f64 != 0) {
+                panel_build_tables<T, double, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qs, sc, ss, sQ, sK);
             } else {
-                panel_build_tables<T, T, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qs, sc, ss, sQ, sK, (a.tables_f64 & 2) == 0);
+                panel_build_tables<T, T, TPT, LEVEL >= 1>(x, y, z, L, sa, SA, qs, sc, ss, sQ, sK);
             }
         }
 

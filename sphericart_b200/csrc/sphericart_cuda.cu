@@ -392,12 +392,16 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                                    (ctas >= 2 ? 1.0 : 0.8) * (tp == 32 ? 1.15 : 1.0);
                     if (level == 0) {
                         // Values only: a thread carries 16 bytes' worth of points through whole rows, which gives
-                        // it the independent work that the other levels get from many warps. Measured (float32
-                        // l_max = 24, float64 l_max = 32): eight threads side by side (32 / 16 points per panel) and
-                        // one pair of rows per thread is best even where only one or two CTAs fit an SM
-                        // (float32 l_max = 24: 32 / 16 / 8 points per panel -> 0.79 / 0.64 / 0.56 of the copy peak;
-                        // two pairs of rows per thread: 0.49; float64 l_max = 32: 16 / 8 / 4 points -> 0.53 / 0.47 / 0.41).
-                        score = std::min(lanes, 8) / 8.0 * balance / real_per_slice * (0.85 + 0.05 * std::min<long long>(ctas, 3));
+                        // it the independent work that the other levels get from many warps; the kernel is bound
+                        // by shared-memory traffic (image writes, the engine's reads, the c/s loads), and four
+                        // slices share a warp, so bank conflicts between slices vary with l_max. Measured: one
+                        // pair of rows per thread is best (two: 0.49 against 0.79, float32 l_max = 24); eight
+                        // threads side by side (32 / 16 points per panel) where two CTAs fit an SM
+                        // (float32 l_max = 24: 32 / 16 / 8 points per panel -> 0.79 / 0.64 / 0.56 of the copy
+                        // peak; float64 l_max = 24: 16 / 8 points -> 0.77 / 0.67), half as many where only one
+                        // would fit (float32 l_max = 28: 0.53 against 0.62).
+                        score = std::sqrt(std::min(lanes, 8) / 8.0) * balance / real_per_slice * (ctas >= 2 ? 1.0 : 0.7) *
+                                (0.85 + 0.05 * std::min<long long>(ctas, 3));
                     }
                     if (score > best_score + 1e-9) {
                         best_score = score;
