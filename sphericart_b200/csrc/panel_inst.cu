@@ -42,7 +42,46 @@ cudaError_t launch_panel(const PanelLaunchArgs<T>& a, int device, cudaStream_t s
     return cudaGetLastError();
 }
 
+template <typename T, bool NORM, int TP>
+cudaError_t launch_panel_vjp(const PanelVjpLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    auto kernel = sph_panel_vjp_kernel<T, NORM, TP>;
+    if (a.threads < TP || a.threads > 256 || a.threads % TP != 0 ||
+        a.smem < panel_vjp_smem_bytes<T>(a.l_max, TP, a.threads)) {
+        return cudaErrorInvalidValue;
+    }
+    const int max_blocks = memo_grid<sph_panel_vjp_kernel<T, NORM, TP>>(a.threads, a.smem, device);
+    if (max_blocks <= 0) return cudaErrorLaunchOutOfResources;
+    const long long nbatches = (a.n + TP - 1) / TP;
+    const int grid = work_grid(nbatches, max_blocks, a.iters, /*all_or_nothing=*/true);
+    PanelVjpArgs<T> k{};
+    k.xyz = a.xyz;
+    k.sph_grad = a.sph_grad;
+    k.n = a.n;
+    k.xyz_grad = a.xyz_grad;
+    k.tables = a.d_tables;
+    k.desc = static_cast<const PanelDesc*>(a.d_desc);
+    k.l_max = a.l_max;
+    k.bulk = (a.bulk != 0 && TP * sizeof(T) >= 16) ? 1 : 0;  // a batch's span of packed rows must be a multiple of 16 bytes
+    k.tables_f64 = a.tables_f64;
+    kernel<<<grid, a.threads, a.smem, stream>>>(k);
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+template <typename T, int TP>
+cudaError_t PanelLaunch<T, TP>::run_vjp(bool normalized, const PanelVjpLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    return normalized ? launch_panel_vjp<T, true, TP>(a, device, stream) : launch_panel_vjp<T, false, TP>(a, device, stream);
+}
+
+template <typename T, int TP> int PanelLaunch<T, TP>::device_error_flag() {
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_tile_wait_gave_up, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return flag;
+}
 
 template <typename T, int TP>
 cudaError_t PanelLaunch<T, TP>::run(int level, bool normalized, const PanelLaunchArgs<T>& a, int device,

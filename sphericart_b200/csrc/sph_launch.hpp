@@ -180,10 +180,29 @@ template <typename T> struct PanelLaunchArgs {
     int iters;           // table batches per CTA, see work_grid()
 };
 
+// Fused VJP with run-time l_max (sph_panel_vjp_kernel): tables and upstream rows for TPT points at a time.
+template <typename T> struct PanelVjpLaunchArgs {
+    const T* xyz;
+    const T* sph_grad;
+    long long n;
+    T* xyz_grad;
+    const T* d_tables;
+    const void* d_desc;
+    int l_max;
+    int bulk;        // 1: the upstream rows may come through the TMA engine (sph_grad is 16-byte aligned)
+    int tables_f64;
+    int threads;     // a multiple of TPT
+    size_t smem;
+    int iters;       // table batches per CTA, see work_grid()
+};
+
 template <typename T, int TPT> struct PanelLaunch {
     static cudaError_t run(int level, bool normalized, const PanelLaunchArgs<T>& a, int device, cudaStream_t stream);
+    static cudaError_t run_vjp(bool normalized, const PanelVjpLaunchArgs<T>& a, int device, cudaStream_t stream);
     // registers per thread of the kernel that run() would launch (0 if it cannot be queried)
     static int registers(int level, bool normalized);
+    // 1 if a kernel of this translation unit gave up waiting for a TMA load, 0 if not, -1 if unknown
+    static int device_error_flag();
 };
 
 template <typename T, int G> struct BandLaunch {

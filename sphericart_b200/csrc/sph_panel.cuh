@@ -666,4 +666,248 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     if (tid == 0 && committed > 0) bulk_wait_read_all();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused vector-Jacobian product with the maximum degree known only at run time:
+//   xyz_grad[i][a] = sum_k sph_grad[i][k] dY[i][a][k],
+// dY never in memory. Same division of labour as the forward kernel: a CTA takes batches of TPT
+// points; phase A builds the batch's c/s and Q tables (all threads, point-minor); in phase B thread
+// (point p, slice s) walks the pairs t = s, s + S, ... and accumulates the contraction (the gradient
+// columns are never formed, see eval_point_vjp in sph_core.cuh for the algebra); the S partial sums of
+// a point meet in shared memory, the linear unit-sphere chain rule is applied once to their total.
+// The batch's TPT rows of sph_grad are one contiguous span of the input: the TMA engine fetches it
+// (one bulk load when the rows are of odd length and packed, one per row into padded rows
+// otherwise), completion on an mbarrier that every thread waits for with a bounded number of polls
+// (on give-up the CTA records it in g_tile_wait_gave_up and returns: nothing else of it is in
+// flight); the next batch's rows are requested as soon as phase B is over, so the load runs under the
+// reduction and the next table phase. No output image, hence small CTAs footprints and many of them
+// per SM. Replaces the reference's backward (a gradients launch that materialises dsph, a product and
+// a reduction: sphericart-torch/python/sphericart/torch/register.py:90-108).
+template <typename T> struct PanelVjpArgs {
+    const T* xyz;
+    const T* sph_grad;
+    long long n;
+    T* xyz_grad;
+    const T* tables;        // F then K
+    const PanelDesc* desc;
+    int l_max;
+    int bulk;               // 1: sph_grad is 16-byte aligned, rows may come through the TMA engine
+    int tables_f64;
+};
+
+// Dynamic shared memory of sph_panel_vjp_kernel, in bytes.
+template <typename T> __host__ __device__ constexpr size_t panel_vjp_smem_bytes(int l_max, int tpt, int threads) {
+    const int nq = n_table(l_max);
+    const int ny = n_columns(l_max);
+    return size_t(align16_elems<T>(2 * nq)) * sizeof(T) + size_t(nq) * sizeof(PanelDesc) +
+           size_t(align16_elems<T>(tpt * panel_point_state(l_max, 1)) + align16_elems<T>(tpt * panel_point_stride(1, ny, int(sizeof(T)))) +
+                  align16_elems<T>(3 * threads)) * sizeof(T) + 16;
+}
+
+template <typename T, bool NORM, int TPT>
+__global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constant__ PanelVjpArgs<T> a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int L = a.l_max;
+    const int ny = (L + 1) * (L + 1);
+    const int nq = (L + 1) * (L + 2) / 2;
+    const int tid = threadIdx.x;
+    constexpr unsigned E = unsigned(TPT) * unsigned(sizeof(T));
+    // thread = (point of the batch, slice), in both phases
+    const int p = tid % TPT;
+    const int s = tid / TPT;
+    const int S = blockDim.x / TPT;
+
+    // carve-up: F | K | descriptors | per-point state of a batch (point-minor) | the batch's rows of sph_grad | partial sums | mbarrier
+    T* sF = reinterpret_cast<T*>(smem_raw);
+    T* sK = sF + nq;
+    PanelDesc* sDesc = reinterpret_cast<PanelDesc*>(sF + align16_elems<T>(2 * nq));
+    T* state = reinterpret_cast<T*>(sDesc + nq);
+    T* sP = state;
+    T* sc = sP + 4 * TPT;
+    T* ss = sc + (L + 3) * TPT;
+    T* sQ = ss + (L + 3) * TPT;
+    T* rows = state + align16_elems<T>(TPT * panel_point_state(L, 1));
+    const int gst = panel_point_stride(1, ny, int(sizeof(T)));  // elements between neighbouring points' rows
+    T* red = rows + align16_elems<T>(TPT * gst);                // partial sums [3][blockDim]
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(red + align16_elems<T>(3 * int(blockDim.x)));
+
+    for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
+    for (int t = tid; t < nq; t += blockDim.x) {
+        PanelDesc d = a.desc[t];
+        d.off0 *= int(E);
+        d.off1 *= int(E);
+        d.off2 *= int(E);
+        sDesc[t] = d;
+    }
+    for (int e = tid; e < 2 * TPT; e += blockDim.x) {
+        sc[e] = T(0);
+        ss[e] = T(0);
+    }
+    for (int e = tid; e < PANEL_ROW_PAD * TPT; e += blockDim.x) sQ[e] = T(0);
+    for (int e = tid; e < (L + 1) * PANEL_ROW_PAD * TPT; e += blockDim.x) {
+        const int l = e / (PANEL_ROW_PAD * TPT);
+        const int r = e % (PANEL_ROW_PAD * TPT);
+        sQ[(panel_row_start(l) + l + 1) * TPT + r] = T(0);
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const unsigned f_addr = static_cast<unsigned>(__cvta_generic_to_shared(sF));
+    const unsigned desc_addr = static_cast<unsigned>(__cvta_generic_to_shared(sDesc));
+    const unsigned q_addr = static_cast<unsigned>(__cvta_generic_to_shared(sQ + p));
+    const unsigned c_addr = static_cast<unsigned>(__cvta_generic_to_shared(sc + p));
+    const unsigned s_addr = static_cast<unsigned>(__cvta_generic_to_shared(ss + p));
+    const unsigned g_addr = static_cast<unsigned>(__cvta_generic_to_shared(rows + p * gst));
+
+    const long long nbatches = (a.n + TPT - 1) / TPT;
+    const bool packed_rows = (ny & 1) != 0;
+    const unsigned row_bytes = unsigned(ny) * unsigned(sizeof(T));
+    // a batch can come through the engine when it is full: its span (packed rows) or each of its rows
+    // (rows of even length are multiples of 16 bytes) then starts and ends on 16-byte boundaries
+    auto engine_batch = [&](long long batch) { return a.bulk != 0 && (batch + 1) * TPT <= a.n; };
+    auto issue = [&](long long batch) {  // thread 0 only
+        if (batch < nbatches && engine_batch(batch)) {
+            const T* src = a.sph_grad + batch * TPT * ny;
+            mbar_expect_tx(bar, unsigned(TPT) * row_bytes);
+            if (packed_rows) {
+                bulk_load_global_to_smem(rows, src, unsigned(TPT) * row_bytes, bar);
+            } else {
+                for (int r = 0; r < TPT; ++r) bulk_load_global_to_smem(rows + r * gst, src + size_t(r) * ny, row_bytes, bar);
+            }
+        }
+    };
+    auto fetch_point = [&](long long batch, T& px, T& py, T& pz) {
+        px = T(1);
+        py = T(0);
+        pz = T(0);
+        const long long ip = batch * TPT + p;
+        if (batch < nbatches && ip < a.n) {
+            px = a.xyz[3 * ip + 0];
+            py = a.xyz[3 * ip + 1];
+            pz = a.xyz[3 * ip + 2];
+        }
+    };
+
+    if (tid == 0) issue(blockIdx.x);
+    T next_x, next_y, next_z;
+    fetch_point(blockIdx.x, next_x, next_y, next_z);
+    unsigned phase = 0u;
+    for (long long batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
+        // ---- phase A: the batch's tables
+        {
+            T x = next_x, y = next_y, z = next_z, ir = T(1);
+            fetch_point(batch + gridDim.x, next_x, next_y, next_z);
+            if constexpr (NORM) {
+                // IEEE square root and division, as on the CPU (sphericart/include/templates.hpp:392-400)
+                ir = T(1) / sqrt(x * x + y * y + z * z);
+                x *= ir;
+                y *= ir;
+                z *= ir;
+            }
+            if (s == 0) {
+                sP[0 * TPT + p] = x;
+                sP[1 * TPT + p] = y;
+                sP[2 * TPT + p] = z;
+                sP[3 * TPT + p] = ir;
+            }
+            if (a.tables_f64 != 0) {
+                panel_build_tables<T, double, TPT, true>(x, y, z, L, s, S, p, sc, ss, sQ, sK);
+            } else {
+                panel_build_tables<T, T, TPT, true>(x, y, z, L, s, S, p, sc, ss, sQ, sK);
+            }
+        }
+        // ---- the batch's rows of sph_grad
+        if (engine_batch(batch)) {
+            if (!mbar_wait_bounded(bar, phase)) {
+                g_tile_wait_gave_up = 1;
+                return;  // the same for every thread of the CTA; nothing else is in flight
+            }
+            phase ^= 1u;
+        } else {
+            // ragged last batch, or an input that is not 16-byte aligned: coalesced loads by all threads
+            const long long first = batch * TPT;
+            const int nvalid = (a.n - first) < TPT ? int(a.n - first) : TPT;
+            const T* src = a.sph_grad + first * ny;
+            for (int r = 0; r < TPT; ++r) {
+                for (int e = tid; e < ny; e += blockDim.x) rows[r * gst + e] = r < nvalid ? src[size_t(r) * ny + e] : T(0);
+            }
+        }
+        __syncthreads();  // tables and rows complete
+
+        // ---- phase B
+        const T x = sP[0 * TPT + p], y = sP[1 * TPT + p];
+        T ax = T(0), ay = T(0), az = T(0), aw = T(0);  // aw: the sum that x and y multiply
+        auto load = [&](int t) {
+            PanelDesc d;
+            asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(d.off0), "=r"(d.off1), "=r"(d.off2), "=r"(d.klm)
+                         : "r"(desc_addr + unsigned(t) * 16u));
+            const T f = lds_at<T, 0>(f_addr + unsigned(t) * unsigned(sizeof(T)));
+            return panel_load_pair<T, TPT, 1>(d, f, q_addr, c_addr, s_addr);
+        };
+        auto finish_pair = [&](const PairInputs<T, 1>& in) {
+            const T gp = lds_at<T, 0>(g_addr + unsigned(in.kp) * unsigned(sizeof(T)));
+            const T gm = lds_at<T, 0>(g_addr + unsigned(in.kp - 2 * in.m) * unsigned(sizeof(T)));
+            // m = 0: c_{-1} = s_{-1} = s_0 = 0 in the tables, so u = v = 0 and w = gp
+            const T w = gp * in.cm + gm * in.sm;
+            const T u = gp * in.cm1 + gm * in.sm1;
+            const T v = gm * in.cm1 - gp * in.sm1;
+            const T pqm = in.q * in.f * in.fm;
+            ax += pqm * u;
+            ay += pqm * v;
+            aw += in.f * in.q1a * w;
+            az += in.f * in.flm * in.q1b * w;
+        };
+        {
+            int t = s;
+            for (; t + S < nq; t += 2 * S) {
+                const PairInputs<T, 1> in0 = load(t);
+                const PairInputs<T, 1> in1 = load(t + S);
+                finish_pair(in0);
+                finish_pair(in1);
+            }
+            if (t < nq) finish_pair(load(t));
+        }
+        red[0 * blockDim.x + tid] = ax + x * aw;
+        red[1 * blockDim.x + tid] = ay + y * aw;
+        red[2 * blockDim.x + tid] = az;
+        // the threads that finish the reduction read their point before the next table phase overwrites it
+        T ux = T(0), uy = T(0), uz = T(0), ir = T(1);
+        if (s == 0) {
+            ux = x;
+            uy = y;
+            uz = sP[2 * TPT + p];
+            ir = sP[3 * TPT + p];
+        }
+        fence_proxy_async_smem();  // the rows were read through ordinary loads and are written next by the engine
+        __syncthreads();           // partial sums complete; rows and tables free
+        if (tid == 0) issue(batch + gridDim.x);
+        if (s == 0) {
+            T gx = T(0), gy = T(0), gz = T(0);
+            for (int j = 0; j < S; ++j) {
+                gx += red[0 * blockDim.x + j * TPT + p];
+                gy += red[1 * blockDim.x + j * TPT + p];
+                gz += red[2 * blockDim.x + j * TPT + p];
+            }
+            if constexpr (NORM) {
+                // the chain rule through r -> r/|r| is linear in the gradient: applied once to the sum
+                const T t = gx * ux + gy * uy + gz * uz;
+                gx = (gx - ux * t) * ir;
+                gy = (gy - uy * t) * ir;
+                gz = (gz - uz * t) * ir;
+            }
+            const long long ip = batch * TPT + p;
+            if (ip < a.n) {
+                a.xyz_grad[3 * ip + 0] = gx;
+                a.xyz_grad[3 * ip + 1] = gy;
+                a.xyz_grad[3 * ip + 2] = gz;
+            }
+        }
+        // (the partial sums are overwritten only after the next batch's first barrier, which the
+        // reducing threads reach after they are done reading them)
+    }
+}
+
 }  // namespace sph_b200

@@ -424,6 +424,65 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
     return best;
 }
 
+// Shape of the run-time-degree VJP kernel: points per table batch, threads per CTA (batch x slices), dynamic
+// shared memory (panel_vjp_smem_bytes of sph_panel.cuh for a run-time element size), batches per CTA.
+struct PanelVjpPlan {
+    int batch = 0;
+    int threads = 0;
+    size_t smem = 0;
+    int iters = 8;
+    bool feasible = false;
+};
+
+size_t panel_vjp_bytes(int l_max, int batch, int threads, size_t elem) {
+    const size_t nq = size_t(n_table(l_max));
+    const size_t ny = size_t(n_columns(l_max));
+    const size_t q = 16 / elem;
+    const size_t stride = ny % 2 != 0 ? ny : ((ny / q) % 2 == 0 ? ny + q : ny);
+    return band_align16(2 * nq, elem) * elem + nq * 16 +
+           (band_align16(size_t(batch) * size_t(panel_point_state(l_max, 1)), elem) + band_align16(size_t(batch) * stride, elem) +
+            band_align16(3 * size_t(threads), elem)) * elem + 16;
+}
+
+// The kernel has no output image, so its footprint is small: the plan looks for the most resident warps
+// (up to 32 per SM) with at least four pairs per thread, preferring batches of eight points (eight
+// neighbouring lanes read eight neighbouring table entries; rows of even length stay conflict-free).
+PanelVjpPlan make_panel_vjp_plan(int l_max, size_t elem, size_t smem_limit) {
+    PanelVjpPlan best;
+    if (l_max > PANEL_LMAX || knobs().no_panel != 0) return best;
+    const int nq = n_table(l_max);
+    double best_score = -1.0;
+    const int batches[3] = {8, 4, 16};
+    for (int batch : batches) {
+        if (size_t(batch) * elem < 16) continue;  // a batch's packed rows must span a multiple of 16 bytes
+        if (knobs().panel_batch > 0 && batch != knobs().panel_batch) continue;
+        for (int threads = 256; threads >= 64; threads -= 64) {
+            if (knobs().panel_threads > 0 && threads != knobs().panel_threads / batch * batch) continue;
+            const int slices = threads / batch;
+            if (slices < 1 || slices > nq) continue;
+            const size_t smem = panel_vjp_bytes(l_max, batch, threads, elem);
+            if (smem > smem_limit) continue;
+            long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
+            ctas = std::min<long long>(ctas, 2048 / threads);
+            ctas = std::min<long long>(ctas, 65536 / (64LL * threads));
+            if (ctas < 1) continue;
+            const double warps = std::min<double>(double(ctas * threads / 32), 32.0) / 32.0;
+            const int per_slice = (nq + slices - 1) / slices;
+            const double work = std::min(1.0, per_slice / 4.0) * double(nq) / (double(slices) * per_slice);
+            const double score = warps * work * (batch == 8 ? 1.0 : 0.9);
+            if (score > best_score + 1e-9) {
+                best_score = score;
+                best.batch = batch;
+                best.threads = threads;
+                best.smem = smem;
+                best.feasible = true;
+            }
+        }
+    }
+    best.iters = resolve_iters(knobs().panel_iters, std::max(8, best.batch > 0 ? 256 / best.batch : 8));
+    return best;
+}
+
 // Descriptors of the (l, m >= 0) pairs for the panel kernels (PanelDesc in sph_panel.cuh): element
 // offsets of Q_l^m, Q_{l-1}^m, Q_{l-2}^m in the triangular per-point table (rows -1 and -2 are the
 // block of zeros at offset 0), and column | m << 16 | l << 24.
@@ -447,6 +506,8 @@ template <typename T> struct CalculatorState {
     bool plan_ready[5] = {false, false, false, false, false};
     PanelPlan panel_plans[3];
     bool panel_plan_ready[3] = {false, false, false};
+    PanelVjpPlan panel_vjp_plan;
+    bool panel_vjp_plan_ready = false;
     // device copies of the F and K tables followed (from the next 16-byte boundary) by the panel
     // kernels' pair descriptors, made on first use per device
     T* tables[MAX_DEVICES] = {};
@@ -625,6 +686,28 @@ cudaError_t panel_dispatch(int tp, int level, bool normalized, const PanelLaunch
 }
 
 template <typename T>
+cudaError_t panel_vjp_dispatch(int batch, bool normalized, const PanelVjpLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    switch (batch) {
+        case 4: return PanelLaunch<T, 4>::run_vjp(normalized, a, device, stream);
+        case 8: return PanelLaunch<T, 8>::run_vjp(normalized, a, device, stream);
+        case 16: return PanelLaunch<T, 16>::run_vjp(normalized, a, device, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+template <typename T> int panel_error_flags() {
+    const int flags[6] = {PanelLaunch<T, 1>::device_error_flag(), PanelLaunch<T, 2>::device_error_flag(),
+                          PanelLaunch<T, 4>::device_error_flag(), PanelLaunch<T, 8>::device_error_flag(),
+                          PanelLaunch<T, 16>::device_error_flag(), PanelLaunch<T, 32>::device_error_flag()};
+    int all = 0;
+    for (int f : flags) {
+        if (f < 0) return -1;
+        all |= f;
+    }
+    return all;
+}
+
+template <typename T>
 cudaError_t band_dispatch(int lanes, int level, bool vjp, bool normalized, const BandLaunchArgs<T>& a, int device,
                           cudaStream_t stream) {
     switch (lanes) {
@@ -766,6 +849,37 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
         }
     }
 
+    if (kind == 3 && knobs().no_panel == 0 && !force_band) {
+        const PanelVjpPlan* vplan = nullptr;
+        const T* d_tables = nullptr;
+        {
+            std::lock_guard<std::mutex> lock(st.mutex);
+            if (!st.panel_vjp_plan_ready) {
+                st.panel_vjp_plan = make_panel_vjp_plan(l_max, sizeof(T), props.smem_optin);
+                st.panel_vjp_plan_ready = true;
+            }
+            vplan = &st.panel_vjp_plan;
+            if (vplan->feasible) d_tables = device_tables(st, host_tables, l_max, scope.device);
+        }
+        if (vplan->feasible) {
+            PanelVjpLaunchArgs<T> a{};
+            a.xyz = xyz;
+            a.sph_grad = sph_grad;
+            a.n = n;
+            a.xyz_grad = xyz_grad;
+            a.d_tables = d_tables;
+            a.d_desc = reinterpret_cast<const unsigned char*>(d_tables) + desc_offset_bytes<T>(l_max);
+            a.l_max = l_max;
+            a.bulk = (aligned16(sph_grad) && knobs().no_bulk == 0) ? 1 : 0;
+            a.tables_f64 = knobs().panel_tables_f64;
+            a.threads = vplan->threads;
+            a.smem = vplan->smem;
+            a.iters = vplan->iters;
+            check(panel_vjp_dispatch<T>(vplan->batch, normalized, a, scope.device, stream), "panel VJP kernel launch");
+            return;
+        }
+    }
+
     const BandPlan* plan = nullptr;
     const T* d_tables = nullptr;
     band_resources(st, host_tables, l_max, kind, scope.device, props.smem_optin, props.sm_count, plan, d_tables);
@@ -837,6 +951,9 @@ const char* kernel_family(int kind, int l_max, int elem_bytes, size_t smem_limit
     if (kind <= 2 && knobs().no_panel == 0 && !force_band &&
         make_panel_plan(l_max, kind, size_t(elem_bytes), smem_limit, 0).feasible) {
         return "sph_panel_kernel";
+    }
+    if (kind == 3 && !force_band && make_panel_vjp_plan(l_max, size_t(elem_bytes), smem_limit).feasible) {
+        return "sph_panel_vjp_kernel";
     }
     return "sph_band_kernel";
 }
@@ -1065,7 +1182,9 @@ extern "C" const char* sphericart_cuda_kernel_family(int kind, size_t l_max, int
 extern "C" int sphericart_cuda_device_wait_errors(void) {
     const int f = sph_b200::TileDispatch<float>::error_flags();
     const int d = sph_b200::TileDispatch<double>::error_flags();
-    return (f < 0 || d < 0) ? -1 : (f | d);
+    const int pf = sph_b200::panel_error_flags<float>();
+    const int pd = sph_b200::panel_error_flags<double>();
+    return (f < 0 || d < 0 || pf < 0 || pd < 0) ? -1 : (f | d | pf | pd);
 }
 
 #define SPH_CAPI_FAMILY(KIND, SFX, T)                                                                               \
