@@ -44,8 +44,12 @@ cudaError_t launch_panel(const PanelLaunchArgs<T>& a, int device, cudaStream_t s
 
 template <typename T, bool NORM, int TP>
 cudaError_t launch_panel_vjp(const PanelVjpLaunchArgs<T>& a, int device, cudaStream_t stream) {
+    if constexpr (TP < panel_values_ppt(int(sizeof(T)))) {
+        return cudaErrorInvalidValue;  // a batch holds at least one thread's points
+    } else {
     auto kernel = sph_panel_vjp_kernel<T, NORM, TP>;
-    if (a.threads < TP || a.threads > 256 || a.threads % TP != 0 ||
+    constexpr int LANES = TP / panel_values_ppt(int(sizeof(T)));
+    if (a.threads < TP || a.threads > 256 || a.threads % LANES != 0 ||
         a.smem < panel_vjp_smem_bytes<T>(a.l_max, TP, a.threads)) {
         return cudaErrorInvalidValue;
     }
@@ -59,12 +63,11 @@ cudaError_t launch_panel_vjp(const PanelVjpLaunchArgs<T>& a, int device, cudaStr
     k.n = a.n;
     k.xyz_grad = a.xyz_grad;
     k.tables = a.d_tables;
-    k.desc = static_cast<const PanelDesc*>(a.d_desc);
     k.l_max = a.l_max;
-    k.bulk = (a.bulk != 0 && TP * sizeof(T) >= 16) ? 1 : 0;  // a batch's span of packed rows must be a multiple of 16 bytes
-    k.tables_f64 = a.tables_f64;
+    k.bulk = a.bulk;
     kernel<<<grid, a.threads, a.smem, stream>>>(k);
     return cudaGetLastError();
+    }
 }
 
 }  // namespace

@@ -187,11 +187,9 @@ template <typename T> struct PanelVjpLaunchArgs {
     long long n;
     T* xyz_grad;
     const T* d_tables;
-    const void* d_desc;
     int l_max;
     int bulk;        // 1: the upstream rows may come through the TMA engine (sph_grad is 16-byte aligned)
-    int tables_f64;
-    int threads;     // a multiple of TPT
+    int threads;     // slices x (TPT / points per thread), at least TPT
     size_t smem;
     int iters;       // table batches per CTA, see work_grid()
 };

@@ -669,97 +669,110 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
 // ---------------------------------------------------------------------------------------------
 // Fused vector-Jacobian product with the maximum degree known only at run time:
 //   xyz_grad[i][a] = sum_k sph_grad[i][k] dY[i][a][k],
-// dY never in memory. Same division of labour as the forward kernel: a CTA takes batches of TPT
-// points; phase A builds the batch's c/s and Q tables (all threads, point-minor); in phase B thread
-// (point p, slice s) walks the pairs t = s, s + S, ... and accumulates the contraction (the gradient
-// columns are never formed, see eval_point_vjp in sph_core.cuh for the algebra); the S partial sums of
-// a point meet in shared memory, the linear unit-sphere chain rule is applied once to their total.
+// dY never in memory. A CTA takes batches of TPT points. Phase A builds the batch's c_m, s_m (all
+// threads, point-minor) - no Q table: as in the values-only forward path a slice owns whole rows, in
+// pairs (j, l_max - j) of constant total length, and carries the recurrences in registers - here two
+// of them, row l and row l-1, because the derivatives of row l need Q_{l-1}^{m+1} and Q_{l-1}^m. The
+// gradient columns are never formed (see eval_point_vjp in sph_core.cuh for the algebra): per (l, m)
+// the thread reads the two upstream entries g+, g- and accumulates four sums. A thread does this for
+// PPT points at once (their c_m, s_m arrive as one 16-byte load; float32: two points per packed
+// instruction). The partial sums of a point's slices meet in shared memory; the linear unit-sphere
+// chain rule is applied once to their total.
 // The batch's TPT rows of sph_grad are one contiguous span of the input: the TMA engine fetches it
 // (one bulk load when the rows are of odd length and packed, one per row into padded rows
 // otherwise), completion on an mbarrier that every thread waits for with a bounded number of polls
 // (on give-up the CTA records it in g_tile_wait_gave_up and returns: nothing else of it is in
 // flight); the next batch's rows are requested as soon as phase B is over, so the load runs under the
-// reduction and the next table phase. No output image, hence small CTAs footprints and many of them
-// per SM. Replaces the reference's backward (a gradients launch that materialises dsph, a product and
-// a reduction: sphericart-torch/python/sphericart/torch/register.py:90-108).
+// reduction and the next table phase. Replaces the reference's backward (a gradients launch that
+// materialises dsph, a product and a reduction: sphericart-torch/python/sphericart/torch/register.py:90-108).
 template <typename T> struct PanelVjpArgs {
     const T* xyz;
     const T* sph_grad;
     long long n;
     T* xyz_grad;
-    const T* tables;        // F then K
-    const PanelDesc* desc;
+    const T* tables;  // F then K
     int l_max;
-    int bulk;               // 1: sph_grad is 16-byte aligned, rows may come through the TMA engine
-    int tables_f64;
+    int bulk;         // 1: sph_grad is 16-byte aligned, rows may come through the TMA engine
 };
 
 // Dynamic shared memory of sph_panel_vjp_kernel, in bytes.
 template <typename T> __host__ __device__ constexpr size_t panel_vjp_smem_bytes(int l_max, int tpt, int threads) {
     const int nq = n_table(l_max);
     const int ny = n_columns(l_max);
-    return size_t(align16_elems<T>(2 * nq)) * sizeof(T) + size_t(nq) * sizeof(PanelDesc) +
-           size_t(align16_elems<T>(tpt * panel_point_state(l_max, 1)) + align16_elems<T>(tpt * panel_point_stride(1, ny, int(sizeof(T)))) +
-                  align16_elems<T>(3 * threads)) * sizeof(T) + 16;
+    return size_t(align16_elems<T>(2 * nq) + align16_elems<T>(tpt * panel_point_state(l_max, 0)) +
+                  align16_elems<T>(tpt * panel_point_stride(1, ny, int(sizeof(T)))) + align16_elems<T>(3 * threads * (16 / int(sizeof(T))))) *
+               sizeof(T) + 16;
 }
+
+// Points that share an arithmetic instruction: two in float32 (packed), one in float64.
+template <typename T> struct PointPack;
+template <> struct PointPack<float> {
+    using type = F2;
+    static constexpr int N = 2;
+    static __device__ __forceinline__ type make(const float* v) { return f2(v[0], v[1]); }
+    static __device__ __forceinline__ type all(float s) { return bc(s); }
+    static __device__ __forceinline__ float get(type v, int j) { return j == 0 ? v.v.x : v.v.y; }
+    static __device__ __forceinline__ type fma(type a, type b, type c) { return fma2(a, b, c); }
+    static __device__ __forceinline__ type minus(type a) { return neg(a); }
+};
+template <> struct PointPack<double> {
+    using type = double;
+    static constexpr int N = 1;
+    static __device__ __forceinline__ type make(const double* v) { return v[0]; }
+    static __device__ __forceinline__ type all(double s) { return s; }
+    static __device__ __forceinline__ double get(type v, int) { return v; }
+    static __device__ __forceinline__ type fma(type a, type b, type c) { return a * b + c; }
+    static __device__ __forceinline__ type minus(type a) { return -a; }
+};
 
 template <typename T, bool NORM, int TPT>
 __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constant__ PanelVjpArgs<T> a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    using PP = PointPack<T>;
+    using Pk = typename PP::type;
+    constexpr int PPT = panel_values_ppt(int(sizeof(T)));  // points per thread in phase B
+    constexpr int NPK = PPT / PP::N;                        // packs per thread
+    constexpr int LANES = TPT / PPT;                        // threads side by side in a slice
+    static_assert(TPT >= PPT, "a batch holds at least one thread's points");
     const int L = a.l_max;
     const int ny = (L + 1) * (L + 1);
     const int nq = (L + 1) * (L + 2) / 2;
     const int tid = threadIdx.x;
-    constexpr unsigned E = unsigned(TPT) * unsigned(sizeof(T));
-    // thread = (point of the batch, slice), in both phases
-    const int p = tid % TPT;
-    const int s = tid / TPT;
-    const int S = blockDim.x / TPT;
+    // phase A: thread = (point of the batch, table slice)
+    const int qa = tid % TPT;
+    const int sa = tid / TPT;
+    const int SA = blockDim.x / TPT;
+    // phase B: thread = (PPT points of the batch, LANES apart; slice of rows)
+    const int p = tid % LANES;
+    const int s = tid / LANES;
+    const int S = blockDim.x / LANES;
+    // table slot of phase A's point: the PPT points of a phase B thread (r = p + i LANES) take the
+    // neighbouring slots PPT p + i, so that one vector load fetches them all
+    const int qs = PPT * (qa % LANES) + qa / LANES;
 
-    // carve-up: F | K | descriptors | per-point state of a batch (point-minor) | the batch's rows of sph_grad | partial sums | mbarrier
+    // carve-up: F | K | per-point state of a batch (point-minor) | the batch's rows of sph_grad | partial sums | mbarrier
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
-    PanelDesc* sDesc = reinterpret_cast<PanelDesc*>(sF + align16_elems<T>(2 * nq));
-    T* state = reinterpret_cast<T*>(sDesc + nq);
-    T* sP = state;
-    T* sc = sP + 4 * TPT;
-    T* ss = sc + (L + 3) * TPT;
-    T* sQ = ss + (L + 3) * TPT;
-    T* rows = state + align16_elems<T>(TPT * panel_point_state(L, 1));
+    T* state = sF + align16_elems<T>(2 * nq);
+    T* sP = state;               // x, y, z, 1/r of slot q at sP[c * TPT + q]
+    T* sc = sP + 4 * TPT;        // c_m of slot q at sc[(m + 2) * TPT + q]
+    T* ss = sc + (L + 3) * TPT;  // s_m likewise
+    T* rows = state + align16_elems<T>(TPT * panel_point_state(L, 0));
     const int gst = panel_point_stride(1, ny, int(sizeof(T)));  // elements between neighbouring points' rows
-    T* red = rows + align16_elems<T>(TPT * gst);                // partial sums [3][blockDim]
-    unsigned long long* bar = reinterpret_cast<unsigned long long*>(red + align16_elems<T>(3 * int(blockDim.x)));
+    T* red = rows + align16_elems<T>(TPT * gst);                // partial sums [3][S][TPT]
+    unsigned long long* bar =
+        reinterpret_cast<unsigned long long*>(red + align16_elems<T>(3 * int(blockDim.x) * (16 / int(sizeof(T)))));
 
     for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
-    for (int t = tid; t < nq; t += blockDim.x) {
-        PanelDesc d = a.desc[t];
-        d.off0 *= int(E);
-        d.off1 *= int(E);
-        d.off2 *= int(E);
-        sDesc[t] = d;
-    }
     for (int e = tid; e < 2 * TPT; e += blockDim.x) {
         sc[e] = T(0);
         ss[e] = T(0);
-    }
-    for (int e = tid; e < PANEL_ROW_PAD * TPT; e += blockDim.x) sQ[e] = T(0);
-    for (int e = tid; e < (L + 1) * PANEL_ROW_PAD * TPT; e += blockDim.x) {
-        const int l = e / (PANEL_ROW_PAD * TPT);
-        const int r = e % (PANEL_ROW_PAD * TPT);
-        sQ[(panel_row_start(l) + l + 1) * TPT + r] = T(0);
     }
     if (tid == 0) {
         mbar_init(bar, 1);
         mbar_init_fence();
     }
     __syncthreads();
-
-    const unsigned f_addr = static_cast<unsigned>(__cvta_generic_to_shared(sF));
-    const unsigned desc_addr = static_cast<unsigned>(__cvta_generic_to_shared(sDesc));
-    const unsigned q_addr = static_cast<unsigned>(__cvta_generic_to_shared(sQ + p));
-    const unsigned c_addr = static_cast<unsigned>(__cvta_generic_to_shared(sc + p));
-    const unsigned s_addr = static_cast<unsigned>(__cvta_generic_to_shared(ss + p));
-    const unsigned g_addr = static_cast<unsigned>(__cvta_generic_to_shared(rows + p * gst));
 
     const long long nbatches = (a.n + TPT - 1) / TPT;
     const bool packed_rows = (ny & 1) != 0;
@@ -782,21 +795,34 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
         px = T(1);
         py = T(0);
         pz = T(0);
-        const long long ip = batch * TPT + p;
+        const long long ip = batch * TPT + qa;
         if (batch < nbatches && ip < a.n) {
             px = a.xyz[3 * ip + 0];
             py = a.xyz[3 * ip + 1];
             pz = a.xyz[3 * ip + 2];
         }
     };
+    // the PPT values of one table row, as one 16-byte load, packed
+    auto load_packs = [](const T* ptr, Pk (&v)[NPK]) {
+        if constexpr (sizeof(T) == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(ptr);
+            const float lo[2] = {t.x, t.y}, hi[2] = {t.z, t.w};
+            v[0] = PP::make(lo);
+            v[1] = PP::make(hi);
+        } else {
+            const double2 t = *reinterpret_cast<const double2*>(ptr);
+            v[0] = t.x;
+            v[1] = t.y;
+        }
+    };
 
     if (tid == 0) issue(blockIdx.x);
-    T next_x, next_y, next_z;
-    fetch_point(blockIdx.x, next_x, next_y, next_z);
+    T next_x = T(1), next_y = T(0), next_z = T(0);
+    if (sa < SA) fetch_point(blockIdx.x, next_x, next_y, next_z);
     unsigned phase = 0u;
     for (long long batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
-        // ---- phase A: the batch's tables
-        {
+        // ---- phase A: the batch's points and their c_m, s_m
+        if (sa < SA) {
             T x = next_x, y = next_y, z = next_z, ir = T(1);
             fetch_point(batch + gridDim.x, next_x, next_y, next_z);
             if constexpr (NORM) {
@@ -806,23 +832,19 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                 y *= ir;
                 z *= ir;
             }
-            if (s == 0) {
-                sP[0 * TPT + p] = x;
-                sP[1 * TPT + p] = y;
-                sP[2 * TPT + p] = z;
-                sP[3 * TPT + p] = ir;
+            if (sa == 0) {
+                sP[0 * TPT + qs] = x;
+                sP[1 * TPT + qs] = y;
+                sP[2 * TPT + qs] = z;
+                sP[3 * TPT + qs] = ir;
             }
-            if (a.tables_f64 != 0) {
-                panel_build_tables<T, double, TPT, true>(x, y, z, L, s, S, p, sc, ss, sQ, sK);
-            } else {
-                panel_build_tables<T, T, TPT, true>(x, y, z, L, s, S, p, sc, ss, sQ, sK);
-            }
+            panel_build_tables<T, T, TPT, false>(x, y, z, L, sa, SA, qs, sc, ss, nullptr, sK);
         }
         // ---- the batch's rows of sph_grad
         if (engine_batch(batch)) {
             if (!mbar_wait_bounded(bar, phase)) {
                 g_tile_wait_gave_up = 1;
-                return;  // the same for every thread of the CTA; nothing else is in flight
+                return;  // nothing else of this CTA is in flight
             }
             phase ^= 1u;
         } else {
@@ -834,62 +856,177 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                 for (int e = tid; e < ny; e += blockDim.x) rows[r * gst + e] = r < nvalid ? src[size_t(r) * ny + e] : T(0);
             }
         }
-        __syncthreads();  // tables and rows complete
+        __syncthreads();  // c, s, the points and the rows are complete
 
         // ---- phase B
-        const T x = sP[0 * TPT + p], y = sP[1 * TPT + p];
-        T ax = T(0), ay = T(0), az = T(0), aw = T(0);  // aw: the sum that x and y multiply
-        auto load = [&](int t) {
-            PanelDesc d;
-            asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(d.off0), "=r"(d.off1), "=r"(d.off2), "=r"(d.klm)
-                         : "r"(desc_addr + unsigned(t) * 16u));
-            const T f = lds_at<T, 0>(f_addr + unsigned(t) * unsigned(sizeof(T)));
-            return panel_load_pair<T, TPT, 1>(d, f, q_addr, c_addr, s_addr);
-        };
-        auto finish_pair = [&](const PairInputs<T, 1>& in) {
-            const T gp = lds_at<T, 0>(g_addr + unsigned(in.kp) * unsigned(sizeof(T)));
-            const T gm = lds_at<T, 0>(g_addr + unsigned(in.kp - 2 * in.m) * unsigned(sizeof(T)));
-            // m = 0: c_{-1} = s_{-1} = s_0 = 0 in the tables, so u = v = 0 and w = gp
-            const T w = gp * in.cm + gm * in.sm;
-            const T u = gp * in.cm1 + gm * in.sm1;
-            const T v = gm * in.cm1 - gp * in.sm1;
-            const T pqm = in.q * in.f * in.fm;
-            ax += pqm * u;
-            ay += pqm * v;
-            aw += in.f * in.q1a * w;
-            az += in.f * in.flm * in.q1b * w;
-        };
-        {
-            int t = s;
-            for (; t + S < nq; t += 2 * S) {
-                const PairInputs<T, 1> in0 = load(t);
-                const PairInputs<T, 1> in1 = load(t + S);
-                finish_pair(in0);
-                finish_pair(in1);
+        Pk ax[NPK], ay[NPK], az[NPK], aw[NPK];  // aw: the sum that x and y multiply
+#pragma unroll
+        for (int k = 0; k < NPK; ++k) ax[k] = ay[k] = az[k] = aw[k] = PP::all(T(0));
+        if (s < S) {
+            const int q0i = PPT * p;             // first of this thread's table slots
+            const T* cp = sc + 2 * TPT + q0i;    // c_m of the thread's points at cp[m * TPT ...]
+            const T* sp = ss + 2 * TPT + q0i;
+            const T* grow = rows + p * gst;      // row of point i at grow + i * LANES * gst
+            constexpr int PSTI = LANES;          // (in rows)
+            Pk zz[NPK], rho[NPK], tzz[NPK];
+            {
+                Pk px[NPK], py[NPK];
+                load_packs(sP + 0 * TPT + q0i, px);
+                load_packs(sP + 1 * TPT + q0i, py);
+                load_packs(sP + 2 * TPT + q0i, zz);
+#pragma unroll
+                for (int k = 0; k < NPK; ++k) {
+                    rho[k] = PP::fma(px[k], px[k], py[k] * py[k]);
+                    tzz[k] = zz[k] + zz[k];
+                }
             }
-            if (t < nq) finish_pair(load(t));
+            // upstream entries of column `col` (relative to the row start) for the thread's points
+            auto load_g = [&](int col, Pk (&g)[NPK]) {
+                T v[PPT];
+#pragma unroll
+                for (int i = 0; i < PPT; ++i) v[i] = grow[(i * PSTI) * gst + col];
+#pragma unroll
+                for (int k = 0; k < NPK; ++k) g[k] = PP::make(v + k * PP::N);
+            };
+            // one (l, m): q = Q_l^m, bn = Q_{l-1}^{m+1}, bc = Q_{l-1}^m (zeros where absent); cm, sm hold
+            // c_m, s_m on entry and c_{m-1}, s_{m-1} on exit (c_{-1} = s_{-1} = 0 from the tables' zero rows)
+            auto contract = [&](int l, int m, T f, const Pk (&q)[NPK], const Pk (&bn)[NPK], const Pk (&bcur)[NPK],
+                                Pk (&cm)[NPK], Pk (&sm)[NPK]) {
+                Pk cm1[NPK], sm1[NPK], gp[NPK], gm[NPK];
+                load_packs(cp + (m - 1) * TPT, cm1);
+                load_packs(sp + (m - 1) * TPT, sm1);
+                const int mid = l * l + l;
+                load_g(mid + m, gp);
+                load_g(mid - m, gm);
+                const Pk fm = PP::all(f * T(m)), flm = PP::all(f * T(l + m)), f1 = PP::all(f);
+#pragma unroll
+                for (int k = 0; k < NPK; ++k) {
+                    const Pk w = PP::fma(gp[k], cm[k], gm[k] * sm[k]);
+                    const Pk u = PP::fma(gp[k], cm1[k], gm[k] * sm1[k]);
+                    const Pk v = PP::fma(PP::minus(gp[k]), sm1[k], gm[k] * cm1[k]);
+                    const Pk pqm = q[k] * fm;
+                    ax[k] = PP::fma(pqm, u, ax[k]);
+                    ay[k] = PP::fma(pqm, v, ay[k]);
+                    aw[k] = PP::fma(f1 * bn[k], w, aw[k]);
+                    az[k] = PP::fma(flm * bcur[k], w, az[k]);
+                    cm[k] = cm1[k];
+                    sm[k] = sm1[k];
+                }
+            };
+            auto row_vjp = [&](int l) {  // l >= 1 (the row l = 0 has no derivative)
+                const T* Kl = sK + tri(l, 0);
+                const T* Kb = sK + tri(l - 1, 0);
+                const T* Fl = sF + tri(l, 0);
+                Pk cm[NPK], sm[NPK];
+                load_packs(cp + l * TPT, cm);
+                load_packs(sp + l * TPT, sm);
+                Pk q2[NPK], q1[NPK], b2[NPK], b1[NPK], zero[NPK];
+#pragma unroll
+                for (int k = 0; k < NPK; ++k) {
+                    zero[k] = PP::all(T(0));
+                    q1[k] = PP::all(Kl[l]);  // Q_l^l is tabulated
+                }
+                contract(l, l, Fl[l], q1, zero, zero, cm, sm);
+                // m = l - 1: Q_l^{l-1} = -z Q_l^l, Q_{l-1}^{l-1} tabulated
+                {
+                    Pk q0[NPK];
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        q0[k] = PP::minus(zz[k]) * q1[k];
+                        b1[k] = PP::all(Kb[l - 1]);
+                    }
+                    contract(l, l - 1, Fl[l - 1], q0, zero, b1, cm, sm);
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        q2[k] = q1[k];
+                        q1[k] = q0[k];
+                        b2[k] = zero[k];
+                    }
+                }
+                if (l < 2) return;
+                Pk tz[NPK];  // 2 (m + 1) z
+#pragma unroll
+                for (int k = 0; k < NPK; ++k) tz[k] = PP::all(T(l - 1)) * tzz[k];
+                // m = l - 2: the general step for row l, Q_{l-1}^{l-2} = -z Q_{l-1}^{l-1}
+                {
+                    Pk q0[NPK], b0[NPK];
+                    const Pk km = PP::all(Kl[l - 2]);
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        q0[k] = km * PP::fma(rho[k], q2[k], tz[k] * q1[k]);
+                        b0[k] = PP::minus(zz[k]) * b1[k];
+                    }
+                    contract(l, l - 2, Fl[l - 2], q0, b1, b0, cm, sm);
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        q2[k] = q1[k];
+                        q1[k] = q0[k];
+                        b2[k] = b1[k];
+                        b1[k] = b0[k];
+                        tz[k] = tz[k] + PP::minus(tzz[k]);
+                    }
+                }
+                for (int m = l - 3; m >= 0; --m) {
+                    Pk q0[NPK], b0[NPK];
+                    const Pk km = PP::all(Kl[m]), kb = PP::all(Kb[m]);
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        q0[k] = km * PP::fma(rho[k], q2[k], tz[k] * q1[k]);
+                        b0[k] = kb * PP::fma(rho[k], b2[k], tz[k] * b1[k]);
+                    }
+                    contract(l, m, Fl[m], q0, b1, b0, cm, sm);
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        q2[k] = q1[k];
+                        q1[k] = q0[k];
+                        b2[k] = b1[k];
+                        b1[k] = b0[k];
+                        tz[k] = tz[k] + PP::minus(tzz[k]);
+                    }
+                }
+            };
+            for (int j = s; 2 * j <= L; j += S) {
+                if (L - j >= 1) row_vjp(L - j);
+                if (L - j != j && j >= 1) row_vjp(j);
+            }
+            // x and y multiply the sums of their second terms once
+            {
+                Pk px[NPK], py[NPK];
+                load_packs(sP + 0 * TPT + q0i, px);
+                load_packs(sP + 1 * TPT + q0i, py);
+#pragma unroll
+                for (int k = 0; k < NPK; ++k) {
+                    ax[k] = PP::fma(px[k], aw[k], ax[k]);
+                    ay[k] = PP::fma(py[k], aw[k], ay[k]);
+                }
+            }
+            // partial sums of point r = p + i LANES, slice s: red[(c * S + s) * TPT + r]
+#pragma unroll
+            for (int i = 0; i < PPT; ++i) {
+                const int r = p + i * LANES;
+                red[(0 * S + s) * TPT + r] = PP::get(ax[i / PP::N], i % PP::N);
+                red[(1 * S + s) * TPT + r] = PP::get(ay[i / PP::N], i % PP::N);
+                red[(2 * S + s) * TPT + r] = PP::get(az[i / PP::N], i % PP::N);
+            }
         }
-        red[0 * blockDim.x + tid] = ax + x * aw;
-        red[1 * blockDim.x + tid] = ay + y * aw;
-        red[2 * blockDim.x + tid] = az;
         // the threads that finish the reduction read their point before the next table phase overwrites it
         T ux = T(0), uy = T(0), uz = T(0), ir = T(1);
-        if (s == 0) {
-            ux = x;
-            uy = y;
-            uz = sP[2 * TPT + p];
-            ir = sP[3 * TPT + p];
+        if (tid < TPT) {
+            const int slot = PPT * (tid % LANES) + tid / LANES;
+            ux = sP[0 * TPT + slot];
+            uy = sP[1 * TPT + slot];
+            uz = sP[2 * TPT + slot];
+            ir = sP[3 * TPT + slot];
         }
         fence_proxy_async_smem();  // the rows were read through ordinary loads and are written next by the engine
-        __syncthreads();           // partial sums complete; rows and tables free
+        __syncthreads();           // partial sums complete; rows, points and tables free
         if (tid == 0) issue(batch + gridDim.x);
-        if (s == 0) {
+        if (tid < TPT) {
             T gx = T(0), gy = T(0), gz = T(0);
             for (int j = 0; j < S; ++j) {
-                gx += red[0 * blockDim.x + j * TPT + p];
-                gy += red[1 * blockDim.x + j * TPT + p];
-                gz += red[2 * blockDim.x + j * TPT + p];
+                gx += red[(0 * S + j) * TPT + tid];
+                gy += red[(1 * S + j) * TPT + tid];
+                gz += red[(2 * S + j) * TPT + tid];
             }
             if constexpr (NORM) {
                 // the chain rule through r -> r/|r| is linear in the gradient: applied once to the sum
@@ -898,7 +1035,7 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                 gy = (gy - uy * t) * ir;
                 gz = (gz - uz * t) * ir;
             }
-            const long long ip = batch * TPT + p;
+            const long long ip = batch * TPT + tid;
             if (ip < a.n) {
                 a.xyz_grad[3 * ip + 0] = gx;
                 a.xyz_grad[3 * ip + 1] = gy;

@@ -439,44 +439,36 @@ size_t panel_vjp_bytes(int l_max, int batch, int threads, size_t elem) {
     const size_t ny = size_t(n_columns(l_max));
     const size_t q = 16 / elem;
     const size_t stride = ny % 2 != 0 ? ny : ((ny / q) % 2 == 0 ? ny + q : ny);
-    return band_align16(2 * nq, elem) * elem + nq * 16 +
-           (band_align16(size_t(batch) * size_t(panel_point_state(l_max, 1)), elem) + band_align16(size_t(batch) * stride, elem) +
-            band_align16(3 * size_t(threads), elem)) * elem + 16;
+    return (band_align16(2 * nq, elem) + band_align16(size_t(batch) * size_t(panel_point_state(l_max, 0)), elem) +
+            band_align16(size_t(batch) * stride, elem) + band_align16(3 * size_t(threads) * q, elem)) * elem + 16;
 }
 
-// The kernel has no output image, so its footprint is small: the plan looks for the most resident warps
-// (up to 32 per SM) with at least four pairs per thread, preferring batches of eight points (eight
-// neighbouring lanes read eight neighbouring table entries; rows of even length stay conflict-free).
+// Same shape rules as the values-only forward path, whose structure the kernel shares (a thread carries
+// 16 bytes' worth of points through one pair of rows): eight threads side by side where two CTAs fit an
+// SM, half as many otherwise; one slice per pair of rows (j, l_max - j).
 PanelVjpPlan make_panel_vjp_plan(int l_max, size_t elem, size_t smem_limit) {
     PanelVjpPlan best;
     if (l_max > PANEL_LMAX || knobs().no_panel != 0) return best;
-    const int nq = n_table(l_max);
+    const int ppt = panel_values_ppt(int(elem));
+    const int slices = l_max / 2 + 1;
+    const bool even_rows = n_columns(l_max) % 2 == 0;
     double best_score = -1.0;
-    const int batches[3] = {8, 4, 16};
-    for (int batch : batches) {
-        if (size_t(batch) * elem < 16) continue;  // a batch's packed rows must span a multiple of 16 bytes
+    for (int batch = 32; batch >= ppt; batch /= 2) {
         if (knobs().panel_batch > 0 && batch != knobs().panel_batch) continue;
-        for (int threads = 256; threads >= 64; threads -= 64) {
-            if (knobs().panel_threads > 0 && threads != knobs().panel_threads / batch * batch) continue;
-            const int slices = threads / batch;
-            if (slices < 1 || slices > nq) continue;
-            const size_t smem = panel_vjp_bytes(l_max, batch, threads, elem);
-            if (smem > smem_limit) continue;
-            long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
-            ctas = std::min<long long>(ctas, 2048 / threads);
-            ctas = std::min<long long>(ctas, 65536 / (64LL * threads));
-            if (ctas < 1) continue;
-            const double warps = std::min<double>(double(ctas * threads / 32), 32.0) / 32.0;
-            const int per_slice = (nq + slices - 1) / slices;
-            const double work = std::min(1.0, per_slice / 4.0) * double(nq) / (double(slices) * per_slice);
-            const double score = warps * work * (batch == 8 ? 1.0 : 0.9);
-            if (score > best_score + 1e-9) {
-                best_score = score;
-                best.batch = batch;
-                best.threads = threads;
-                best.smem = smem;
-                best.feasible = true;
-            }
+        const int lanes = batch / ppt;
+        if (even_rows && lanes > 8) continue;  // padded rows are conflict-free for eight threads side by side
+        const int threads = lanes * slices;
+        if (threads > 256 || threads < batch) continue;
+        const size_t smem = panel_vjp_bytes(l_max, batch, threads, elem);
+        if (smem > smem_limit) continue;
+        const long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
+        const double score = std::sqrt(std::min(lanes, 8) / 8.0) * (ctas >= 2 ? 1.0 : 0.7) * (0.85 + 0.05 * std::min<long long>(ctas, 3));
+        if (score > best_score + 1e-9) {
+            best_score = score;
+            best.batch = batch;
+            best.threads = threads;
+            best.smem = smem;
+            best.feasible = true;
         }
     }
     best.iters = resolve_iters(knobs().panel_iters, std::max(8, best.batch > 0 ? 256 / best.batch : 8));
@@ -688,9 +680,11 @@ cudaError_t panel_dispatch(int tp, int level, bool normalized, const PanelLaunch
 template <typename T>
 cudaError_t panel_vjp_dispatch(int batch, bool normalized, const PanelVjpLaunchArgs<T>& a, int device, cudaStream_t stream) {
     switch (batch) {
+        case 2: return PanelLaunch<T, 2>::run_vjp(normalized, a, device, stream);
         case 4: return PanelLaunch<T, 4>::run_vjp(normalized, a, device, stream);
         case 8: return PanelLaunch<T, 8>::run_vjp(normalized, a, device, stream);
         case 16: return PanelLaunch<T, 16>::run_vjp(normalized, a, device, stream);
+        case 32: return PanelLaunch<T, 32>::run_vjp(normalized, a, device, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -868,10 +862,8 @@ void run(size_t l_max_, bool normalized, const T* host_tables, CalculatorState<T
             a.n = n;
             a.xyz_grad = xyz_grad;
             a.d_tables = d_tables;
-            a.d_desc = reinterpret_cast<const unsigned char*>(d_tables) + desc_offset_bytes<T>(l_max);
             a.l_max = l_max;
             a.bulk = (aligned16(sph_grad) && knobs().no_bulk == 0) ? 1 : 0;
-            a.tables_f64 = knobs().panel_tables_f64;
             a.threads = vplan->threads;
             a.smem = vplan->smem;
             a.iters = vplan->iters;
