@@ -139,7 +139,7 @@ SPHERICART_EXPORT const char* sphericart_cuda_last_error(void);
 /* No counterpart in the reference. Name of the kernel family that serves a call on a B200:
  * kind 0, 1, 2 = values, + gradients, + Hessians; 3 = fused VJP; 4 = fused second-order VJP;
  * elem_bytes 4 (float) or 8 (double). Returns "sph_tile_kernel", "sph_vjp_tile_kernel",
- * "sph_vjp2_tile_kernel", "sph_panel_kernel" or "sph_band_kernel" (a static string; "" for arguments
+ * "sph_vjp2_tile_kernel", "sph_panel_kernel", "sph_panel_vjp_kernel" or "sph_band_kernel" (a static string; "" for arguments
  * out of range). Launches nothing; benchmarks and profiles use it to label what they time. */
 SPHERICART_EXPORT const char* sphericart_cuda_kernel_family(int kind, size_t l_max, int elem_bytes);
 

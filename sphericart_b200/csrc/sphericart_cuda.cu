@@ -400,8 +400,9 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                         // (float32 l_max = 24: 32 / 16 / 8 points per panel -> 0.79 / 0.64 / 0.56 of the copy
                         // peak; float64 l_max = 24: 16 / 8 points -> 0.77 / 0.67), half as many where only one
                         // would fit (float32 l_max = 28: 0.53 against 0.62).
+                        // (float64 l_max = 32: 16 points per panel on one CTA per SM 0.53, 8 points on three 0.47)
                         score = std::sqrt(std::min(lanes, 8) / 8.0) * balance / real_per_slice * (ctas >= 2 ? 1.0 : 0.7) *
-                                (0.85 + 0.05 * std::min<long long>(ctas, 3));
+                                (0.85 + 0.05 * std::min<long long>(ctas, 3)) * (tp >= 16 ? 1.0 : 0.85);
                     }
                     if (score > best_score + 1e-9) {
                         best_score = score;
@@ -462,7 +463,10 @@ PanelVjpPlan make_panel_vjp_plan(int l_max, size_t elem, size_t smem_limit) {
         const size_t smem = panel_vjp_bytes(l_max, batch, threads, elem);
         if (smem > smem_limit) continue;
         const long long ctas = std::min<long long>(32, (long long)(233472 / (smem + 1024)));
-        const double score = std::sqrt(std::min(lanes, 8) / 8.0) * (ctas >= 2 ? 1.0 : 0.7) * (0.85 + 0.05 * std::min<long long>(ctas, 3));
+        // (measured, fraction of the copy peak: float32 l_max = 24, 32 / 16 / 8 points per batch: 0.54 / 0.50 / 0.44;
+        // float64 l_max = 32, 16 / 8 points: 0.50 / 0.44; float64 l_max = 24, 32 / 16 / 8 points: 0.58 / 0.62 / 0.58)
+        const double score = std::sqrt(std::min(lanes, 8) / 8.0) * (ctas >= 2 ? 1.0 : 0.7) *
+                             (0.85 + 0.05 * std::min<long long>(ctas, 3)) * (batch >= 16 ? 1.0 : 0.85);
         if (score > best_score + 1e-9) {
             best_score = score;
             best.batch = batch;

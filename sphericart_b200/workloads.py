@@ -100,6 +100,8 @@ CONFIGS = {
     "aux_vjp_l16": (Workload("spherical_l16_f32_fwd_vjp", True, 16, 0, "f32", 1_048_576, 1016, vjp=True), "var2"),
     "aux_vjp2_l4": (Workload("spherical_l4_f32_fwd_vjp2", True, 4, 0, "f32", 4_194_304, 1024, vjp2=True), "var2"),
     "aux_vjp2_l16": (Workload("spherical_l16_f32_fwd_vjp2", True, 16, 0, "f32", 262_144, 1026, vjp2=True), "var2"),
+    "aux_vjp_l24": (Workload("spherical_l24_f32_fwd_vjp", True, 24, 0, "f32", 524_288, 1027, vjp=True), "var2"),
+    "aux_values_l24": (Workload("spherical_l24_f32_values", True, 24, 0, "f32", 524_288, 1028), "var2"),
 }
 
 
