@@ -239,6 +239,45 @@ __device__ __forceinline__ void panel_build_tables(T x, T y, T z, int L, int sa,
     }
 }
 
+// Points that share an arithmetic instruction: two in float32 (packed fma.rn.f32x2), one in float64.
+template <typename T> struct PointPack;
+template <> struct PointPack<float> {
+    using type = F2;
+    static constexpr int N = 2;
+    static __device__ __forceinline__ type make(const float* v) { return f2(v[0], v[1]); }
+    static __device__ __forceinline__ type all(float s) { return bc(s); }
+    static __device__ __forceinline__ float get(type v, int j) { return j == 0 ? v.v.x : v.v.y; }
+    static __device__ __forceinline__ type fma(type a, type b, type c) { return fma2(a, b, c); }
+    static __device__ __forceinline__ type minus(type a) { return neg(a); }
+};
+template <> struct PointPack<double> {
+    using type = double;
+    static constexpr int N = 1;
+    static __device__ __forceinline__ type make(const double* v) { return v[0]; }
+    static __device__ __forceinline__ type all(double s) { return s; }
+    static __device__ __forceinline__ double get(type v, int) { return v; }
+    static __device__ __forceinline__ type fma(type a, type b, type c) { return a * b + c; }
+    static __device__ __forceinline__ type minus(type a) { return -a; }
+};
+
+// 16 bytes of a point-minor table row (four float32 / two float64 neighbouring slots) as packs.
+template <typename T, int NPK>
+__device__ __forceinline__ void load_packs16(const T* ptr, typename PointPack<T>::type (&v)[NPK]) {
+    if constexpr (sizeof(T) == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(ptr);
+        v[0] = f2(t.x, t.y);
+        v[1] = f2(t.z, t.w);
+    } else {
+        const double2 t = *reinterpret_cast<const double2*>(ptr);
+        v[0] = t.x;
+        v[1] = t.y;
+    }
+}
+
+// Bytes of `count` table entries stored one pack each (the value broadcast to the pack's points), rounded
+// up to 16: the kernels that carry rows in registers read their constants in this form.
+__host__ __device__ constexpr size_t pack_table_bytes(int count) { return (size_t(count) * 8 + 15) / 16 * 16; }
+
 template <typename T, int LEVEL, bool NORM, int TPT>
 __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ PanelArgs<T> a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -272,10 +311,15 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     }
 
     // carve-up: F | K | descriptors | per-point state of a batch (point-minor) | slots x images
+    // (values only: F then K with every entry broadcast to a pack of points, nothing else)
+    using PP = PointPack<T>;
+    using Pk = typename PP::type;
     T* sF = reinterpret_cast<T*>(smem_raw);
     T* sK = sF + nq;
+    [[maybe_unused]] Pk* sF2 = reinterpret_cast<Pk*>(smem_raw);
+    [[maybe_unused]] Pk* sK2 = sF2 + nq;
     PanelDesc* sDesc = reinterpret_cast<PanelDesc*>(sF + align16_elems<T>(2 * nq));
-    T* state = reinterpret_cast<T*>(sDesc + (LEVEL >= 1 ? nq : 0));
+    T* state = LEVEL >= 1 ? reinterpret_cast<T*>(sDesc + nq) : reinterpret_cast<T*>(smem_raw + pack_table_bytes(2 * nq));
     T* sP = state;              // x, y, z, 1/r of point q at sP[c * TPT + q]
     T* sc = sP + 4 * TPT;       // c_m of point q at sc[(m + 2) * TPT + q]
     T* ss = sc + (L + 3) * TPT;  // s_m likewise
@@ -290,7 +334,11 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     const int slot_elems = reg0 + reg1 + reg2;
 
     // ---- once per CTA: constants, and the zeros that never change
-    for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
+    if constexpr (LEVEL >= 1) {
+        for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
+    } else {
+        for (int e = tid; e < 2 * nq; e += blockDim.x) sF2[e] = PP::all(a.tables[e]);
+    }
     for (int e = tid; e < 2 * TPT; e += blockDim.x) {
         sc[e] = T(0);
         ss[e] = T(0);
@@ -523,89 +571,106 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     const T* sp = ss + 2 * TPT + q0i;
                     T* out = image0 + p * st0;         // row of point i at out + i * pst
                     const int pst = lanes * st0;
-                    T zz[PPT], rho[PPT];
+                    constexpr int NPK = PPT / PP::N;
+                    Pk nzz[NPK], rho[NPK], tzz[NPK], ntzz[NPK];  // -z, x^2 + y^2, 2z, -2z
+                    {
+                        Pk px[NPK], py[NPK], pz[NPK];
+                        load_packs16<T, NPK>(sP + 0 * TPT + q0i, px);
+                        load_packs16<T, NPK>(sP + 1 * TPT + q0i, py);
+                        load_packs16<T, NPK>(sP + 2 * TPT + q0i, pz);
 #pragma unroll
-                    for (int i = 0; i < PPT; ++i) {
-                        const T px = sP[0 * TPT + q0i + i], py = sP[1 * TPT + q0i + i];
-                        zz[i] = sP[2 * TPT + q0i + i];
-                        rho[i] = px * px + py * py;
-                    }
-                    // the PPT values of one table row, as one 16-byte load
-                    auto load_vec = [](const T* ptr, T (&v)[PPT]) {
-                        if constexpr (sizeof(T) == 4) {
-                            const float4 t = *reinterpret_cast<const float4*>(ptr);
-                            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-                        } else {
-                            const double2 t = *reinterpret_cast<const double2*>(ptr);
-                            v[0] = t.x; v[1] = t.y;
+                        for (int k = 0; k < NPK; ++k) {
+                            rho[k] = PP::fma(px[k], px[k], py[k] * py[k]);
+                            nzz[k] = PP::minus(pz[k]);
+                            tzz[k] = pz[k] + pz[k];
+                            ntzz[k] = nzz[k] + nzz[k];
                         }
-                    };
-                    // writes F Q (c_m, s_m) of every point for one m; q holds Q_l^m per point
-                    auto emit = [&](T* mid, int m, T fm, const T (&q)[PPT]) {
-                        T cv[PPT], sv[PPT];
-                        load_vec(cp + m * TPT, cv);
-                        load_vec(sp + m * TPT, sv);
-                        if constexpr (sizeof(T) == 4) {
+                    }
+                    // writes F Q (c_m, s_m) of every point for one m; q holds Q_l^m per point; pp / pm point at
+                    // the columns +m / -m of each point's row
+                    auto emit = [&](T* const (&pp)[PPT], T* const (&pm)[PPT], int off, const T* cpm, const T* spm, Pk fm,
+                                    const Pk (&q)[NPK], bool minus_too) {
+                        Pk cv[NPK], sv[NPK];
+                        load_packs16<T, NPK>(cpm, cv);
+                        load_packs16<T, NPK>(spm, sv);
 #pragma unroll
-                            for (int i = 0; i < PPT; i += 2) {
-                                const F2 pq = f2(q[i], q[i + 1]) * bc(fm);
-                                const F2 yp = pq * f2(cv[i], cv[i + 1]);
-                                const F2 ym = pq * f2(sv[i], sv[i + 1]);
-                                mid[i * pst + m] = yp.v.x;
-                                mid[(i + 1) * pst + m] = yp.v.y;
-                                if (m > 0) {
-                                    mid[i * pst - m] = ym.v.x;
-                                    mid[(i + 1) * pst - m] = ym.v.y;
-                                }
-                            }
-                        } else {
+                        for (int k = 0; k < NPK; ++k) {
+                            const Pk pq = q[k] * fm;
+                            const Pk yp = pq * cv[k];
+                            const Pk ym = pq * sv[k];
 #pragma unroll
-                            for (int i = 0; i < PPT; ++i) {
-                                const T pq = q[i] * fm;
-                                mid[i * pst + m] = pq * cv[i];
-                                if (m > 0) mid[i * pst - m] = pq * sv[i];
+                            for (int j = 0; j < PP::N; ++j) {
+                                pp[k * PP::N + j][-off] = PP::get(yp, j);
+                                if (minus_too) pm[k * PP::N + j][off] = PP::get(ym, j);
                             }
                         }
                     };
                     auto row_values = [&](int l) {
-                        const T* Kl = sK + tri(l, 0);
-                        const T* Fl = sF + tri(l, 0);
-                        T* mid = out + l * l + l;
-                        T q2[PPT], q1[PPT];
-                        const T kll = Kl[l];  // Q_l^l is tabulated
+                        const Pk* Kl = sK2 + tri(l, 0);
+                        const Pk* Fl = sF2 + tri(l, 0);
+                        T* pp[PPT];  // column +m of each point's row
+                        T* pm[PPT];  // column -m
 #pragma unroll
-                        for (int i = 0; i < PPT; ++i) q2[i] = kll;
-                        emit(mid, l, Fl[l], q2);
-                        if (l >= 1) {
+                        for (int i = 0; i < PPT; ++i) {
+                            pp[i] = out + i * pst + l * l + 2 * l;
+                            pm[i] = out + i * pst + l * l;
+                        }
+                        const T* cpm = cp + l * TPT;
+                        const T* spm = sp + l * TPT;
+                        // the two newest values of the recurrence alternate between qa and qb
+                        Pk qa[NPK], qb[NPK];
 #pragma unroll
-                            for (int i = 0; i < PPT; ++i) q1[i] = -zz[i] * q2[i];  // Q_l^{l-1}
-                            emit(mid, l - 1, Fl[l - 1], q1);
-                            T tm = T(2 * (l - 1));  // 2 (m + 1)
-                            for (int m = l - 2; m >= 0; --m) {
-                                const T km = Kl[m];
-                                T q0[PPT];
-                                if constexpr (sizeof(T) == 4) {
+                        for (int k = 0; k < NPK; ++k) qa[k] = Kl[l];  // Q_l^l is tabulated
+                        emit(pp, pm, 0, cpm, spm, Fl[l], qa, l > 0);
+                        if (l == 0) return;
 #pragma unroll
-                                    for (int i = 0; i < PPT; i += 2) {
-                                        const F2 a1 = bc(tm) * f2(zz[i], zz[i + 1]) * f2(q1[i], q1[i + 1]);
-                                        const F2 r = bc(km) * fma2(f2(rho[i], rho[i + 1]), f2(q2[i], q2[i + 1]), a1);
-                                        q0[i] = r.v.x;
-                                        q0[i + 1] = r.v.y;
-                                    }
-                                } else {
+                        for (int k = 0; k < NPK; ++k) qb[k] = nzz[k] * qa[k];  // Q_l^{l-1}
+                        emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[l - 1], qb, l > 1);
+                        Pk tz[NPK];  // 2 (m + 1) z
 #pragma unroll
-                                    for (int i = 0; i < PPT; ++i) {
-                                        // one dependent operation per step: the coefficients are formed off the chain
-                                        q0[i] = (km * (tm * zz[i])) * q1[i] + (km * rho[i]) * q2[i];
-                                    }
-                                }
-                                emit(mid, m, Fl[m], q0);
+                        for (int k = 0; k < NPK; ++k) tz[k] = PP::all(T(l - 1)) * tzz[k];
+                        int m = l - 2;
 #pragma unroll
-                                for (int i = 0; i < PPT; ++i) {
-                                    q2[i] = q1[i];
-                                    q1[i] = q0[i];
-                                }
-                                tm -= T(2);
+                        for (int i = 0; i < PPT; ++i) {
+                            pp[i] -= 2;
+                            pm[i] += 2;
+                        }
+                        cpm -= 2 * TPT;
+                        spm -= 2 * TPT;
+                        // Q_l^m = K (2 (m+1) z Q_l^{m+1} + rho Q_l^{m+2}), two steps per turn: the new value takes the
+                        // place of the older of the two it was made from, so nothing is moved between registers
+                        for (; m >= 2; m -= 2) {
+#pragma unroll
+                            for (int k = 0; k < NPK; ++k) {
+                                qa[k] = Kl[m] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
+                                tz[k] = tz[k] + ntzz[k];
+                            }
+                            emit(pp, pm, 0, cpm, spm, Fl[m], qa, true);
+#pragma unroll
+                            for (int k = 0; k < NPK; ++k) {
+                                qb[k] = Kl[m - 1] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
+                                tz[k] = tz[k] + ntzz[k];
+                            }
+                            emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[m - 1], qb, true);
+#pragma unroll
+                            for (int i = 0; i < PPT; ++i) {
+                                pp[i] -= 2;
+                                pm[i] += 2;
+                            }
+                            cpm -= 2 * TPT;
+                            spm -= 2 * TPT;
+                        }
+                        if (m >= 0) {
+#pragma unroll
+                            for (int k = 0; k < NPK; ++k) {
+                                qa[k] = Kl[m] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
+                                tz[k] = tz[k] + ntzz[k];
+                            }
+                            emit(pp, pm, 0, cpm, spm, Fl[m], qa, m > 0);
+                            if (m == 1) {
+#pragma unroll
+                                for (int k = 0; k < NPK; ++k) qb[k] = Kl[0] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
+                                emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[0], qb, false);
                             }
                         }
                     };
@@ -695,35 +760,15 @@ template <typename T> struct PanelVjpArgs {
     int bulk;         // 1: sph_grad is 16-byte aligned, rows may come through the TMA engine
 };
 
-// Dynamic shared memory of sph_panel_vjp_kernel, in bytes.
+// Dynamic shared memory of sph_panel_vjp_kernel, in bytes: four tables of constants (F, K, F m, F (l + m), every
+// entry broadcast to a pack of points), the batch's points and c/s, its upstream rows, the partial sums, the mbarrier.
 template <typename T> __host__ __device__ constexpr size_t panel_vjp_smem_bytes(int l_max, int tpt, int threads) {
     const int nq = n_table(l_max);
     const int ny = n_columns(l_max);
-    return size_t(align16_elems<T>(2 * nq) + align16_elems<T>(tpt * panel_point_state(l_max, 0)) +
-                  align16_elems<T>(tpt * panel_point_stride(1, ny, int(sizeof(T)))) + align16_elems<T>(3 * threads * (16 / int(sizeof(T))))) *
-               sizeof(T) + 16;
+    return pack_table_bytes(4 * nq) +
+           size_t(align16_elems<T>(tpt * panel_point_state(l_max, 0)) + align16_elems<T>(tpt * panel_point_stride(1, ny, int(sizeof(T)))) +
+                  align16_elems<T>(3 * threads * (16 / int(sizeof(T))))) * sizeof(T) + 16;
 }
-
-// Points that share an arithmetic instruction: two in float32 (packed), one in float64.
-template <typename T> struct PointPack;
-template <> struct PointPack<float> {
-    using type = F2;
-    static constexpr int N = 2;
-    static __device__ __forceinline__ type make(const float* v) { return f2(v[0], v[1]); }
-    static __device__ __forceinline__ type all(float s) { return bc(s); }
-    static __device__ __forceinline__ float get(type v, int j) { return j == 0 ? v.v.x : v.v.y; }
-    static __device__ __forceinline__ type fma(type a, type b, type c) { return fma2(a, b, c); }
-    static __device__ __forceinline__ type minus(type a) { return neg(a); }
-};
-template <> struct PointPack<double> {
-    using type = double;
-    static constexpr int N = 1;
-    static __device__ __forceinline__ type make(const double* v) { return v[0]; }
-    static __device__ __forceinline__ type all(double s) { return s; }
-    static __device__ __forceinline__ double get(type v, int) { return v; }
-    static __device__ __forceinline__ type fma(type a, type b, type c) { return a * b + c; }
-    static __device__ __forceinline__ type minus(type a) { return -a; }
-};
 
 template <typename T, bool NORM, int TPT>
 __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constant__ PanelVjpArgs<T> a) {
@@ -750,10 +795,12 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
     // neighbouring slots PPT p + i, so that one vector load fetches them all
     const int qs = PPT * (qa % LANES) + qa / LANES;
 
-    // carve-up: F | K | per-point state of a batch (point-minor) | the batch's rows of sph_grad | partial sums | mbarrier
-    T* sF = reinterpret_cast<T*>(smem_raw);
-    T* sK = sF + nq;
-    T* state = sF + align16_elems<T>(2 * nq);
+    // carve-up: F | K | F m | F (l + m) (packs) | per-point state of a batch (point-minor) | the batch's rows of sph_grad | partial sums | mbarrier
+    Pk* sF2 = reinterpret_cast<Pk*>(smem_raw);
+    Pk* sK2 = sF2 + nq;
+    Pk* sFM2 = sK2 + nq;
+    Pk* sFLM2 = sFM2 + nq;
+    T* state = reinterpret_cast<T*>(smem_raw + pack_table_bytes(4 * nq));
     T* sP = state;               // x, y, z, 1/r of slot q at sP[c * TPT + q]
     T* sc = sP + 4 * TPT;        // c_m of slot q at sc[(m + 2) * TPT + q]
     T* ss = sc + (L + 3) * TPT;  // s_m likewise
@@ -763,7 +810,17 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
     unsigned long long* bar =
         reinterpret_cast<unsigned long long*>(red + align16_elems<T>(3 * int(blockDim.x) * (16 / int(sizeof(T)))));
 
-    for (int e = tid; e < 2 * nq; e += blockDim.x) sF[e] = a.tables[e];
+    for (int e = tid; e < nq; e += blockDim.x) {
+        int l = int((sqrtf(8.0f * float(e) + 1.0f) - 1.0f) * 0.5f);
+        while (tri(l + 1, 0) <= e) ++l;
+        while (tri(l, 0) > e) --l;
+        const int m = e - tri(l, 0);
+        const T f = a.tables[e];
+        sF2[e] = PP::all(f);
+        sK2[e] = PP::all(a.tables[nq + e]);
+        sFM2[e] = PP::all(f * T(m));
+        sFLM2[e] = PP::all(f * T(l + m));
+    }
     for (int e = tid; e < 2 * TPT; e += blockDim.x) {
         sc[e] = T(0);
         ss[e] = T(0);
@@ -802,20 +859,6 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
             pz = a.xyz[3 * ip + 2];
         }
     };
-    // the PPT values of one table row, as one 16-byte load, packed
-    auto load_packs = [](const T* ptr, Pk (&v)[NPK]) {
-        if constexpr (sizeof(T) == 4) {
-            const float4 t = *reinterpret_cast<const float4*>(ptr);
-            const float lo[2] = {t.x, t.y}, hi[2] = {t.z, t.w};
-            v[0] = PP::make(lo);
-            v[1] = PP::make(hi);
-        } else {
-            const double2 t = *reinterpret_cast<const double2*>(ptr);
-            v[0] = t.x;
-            v[1] = t.y;
-        }
-    };
-
     if (tid == 0) issue(blockIdx.x);
     T next_x = T(1), next_y = T(0), next_z = T(0);
     if (sa < SA) fetch_point(blockIdx.x, next_x, next_y, next_z);
@@ -838,7 +881,7 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                 sP[2 * TPT + qs] = z;
                 sP[3 * TPT + qs] = ir;
             }
-            panel_build_tables<T, T, TPT, false>(x, y, z, L, sa, SA, qs, sc, ss, nullptr, sK);
+            panel_build_tables<T, T, TPT, false>(x, y, z, L, sa, SA, qs, sc, ss, nullptr, nullptr);
         }
         // ---- the batch's rows of sph_grad
         if (engine_batch(batch)) {
@@ -867,122 +910,129 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
             const T* cp = sc + 2 * TPT + q0i;    // c_m of the thread's points at cp[m * TPT ...]
             const T* sp = ss + 2 * TPT + q0i;
             const T* grow = rows + p * gst;      // row of point i at grow + i * LANES * gst
-            constexpr int PSTI = LANES;          // (in rows)
-            Pk zz[NPK], rho[NPK], tzz[NPK];
+            Pk nzz[NPK], rho[NPK], tzz[NPK], ntzz[NPK];  // -z, x^2 + y^2, 2z, -2z
             {
-                Pk px[NPK], py[NPK];
-                load_packs(sP + 0 * TPT + q0i, px);
-                load_packs(sP + 1 * TPT + q0i, py);
-                load_packs(sP + 2 * TPT + q0i, zz);
+                Pk px[NPK], py[NPK], pz[NPK];
+                load_packs16<T, NPK>(sP + 0 * TPT + q0i, px);
+                load_packs16<T, NPK>(sP + 1 * TPT + q0i, py);
+                load_packs16<T, NPK>(sP + 2 * TPT + q0i, pz);
 #pragma unroll
                 for (int k = 0; k < NPK; ++k) {
                     rho[k] = PP::fma(px[k], px[k], py[k] * py[k]);
-                    tzz[k] = zz[k] + zz[k];
+                    nzz[k] = PP::minus(pz[k]);
+                    tzz[k] = pz[k] + pz[k];
+                    ntzz[k] = nzz[k] + nzz[k];
                 }
             }
-            // upstream entries of column `col` (relative to the row start) for the thread's points
-            auto load_g = [&](int col, Pk (&g)[NPK]) {
-                T v[PPT];
-#pragma unroll
-                for (int i = 0; i < PPT; ++i) v[i] = grow[(i * PSTI) * gst + col];
-#pragma unroll
-                for (int k = 0; k < NPK; ++k) g[k] = PP::make(v + k * PP::N);
-            };
-            // one (l, m): q = Q_l^m, bn = Q_{l-1}^{m+1}, bc = Q_{l-1}^m (zeros where absent); cm, sm hold
-            // c_m, s_m on entry and c_{m-1}, s_{m-1} on exit (c_{-1} = s_{-1} = 0 from the tables' zero rows)
-            auto contract = [&](int l, int m, T f, const Pk (&q)[NPK], const Pk (&bn)[NPK], const Pk (&bcur)[NPK],
-                                Pk (&cm)[NPK], Pk (&sm)[NPK]) {
-                Pk cm1[NPK], sm1[NPK], gp[NPK], gm[NPK];
-                load_packs(cp + (m - 1) * TPT, cm1);
-                load_packs(sp + (m - 1) * TPT, sm1);
-                const int mid = l * l + l;
-                load_g(mid + m, gp);
-                load_g(mid - m, gm);
-                const Pk fm = PP::all(f * T(m)), flm = PP::all(f * T(l + m)), f1 = PP::all(f);
+            // One (l, m). q = Q_l^m, bn = Q_{l-1}^{m+1}, bcur = Q_{l-1}^m (zeros where absent); cm, sm hold c_m, s_m;
+            // c_{m-1}, s_{m-1} are loaded into cm1, sm1 (c_{-1} = s_{-1} = 0 from the tables' zero rows); gp / gm point
+            // at the upstream entries of the columns +m / -m of each point, `off` columns further in.
+            auto contract = [&](int idx, int off, const T* cpm1, const T* spm1, const T* const (&gp)[PPT],
+                                const T* const (&gm)[PPT], const Pk (&q)[NPK], const Pk (&bn)[NPK], const Pk (&bcur)[NPK],
+                                const Pk (&cm)[NPK], const Pk (&sm)[NPK], Pk (&cm1)[NPK], Pk (&sm1)[NPK]) {
+                load_packs16<T, NPK>(cpm1, cm1);
+                load_packs16<T, NPK>(spm1, sm1);
+                const Pk f1 = sF2[idx], fm = sFM2[idx], flm = sFLM2[idx];
 #pragma unroll
                 for (int k = 0; k < NPK; ++k) {
-                    const Pk w = PP::fma(gp[k], cm[k], gm[k] * sm[k]);
-                    const Pk u = PP::fma(gp[k], cm1[k], gm[k] * sm1[k]);
-                    const Pk v = PP::fma(PP::minus(gp[k]), sm1[k], gm[k] * cm1[k]);
+                    T vp[PP::N], vm[PP::N];
+#pragma unroll
+                    for (int j = 0; j < PP::N; ++j) {
+                        vp[j] = gp[k * PP::N + j][-off];
+                        vm[j] = gm[k * PP::N + j][off];
+                    }
+                    const Pk g1 = PP::make(vp), g2 = PP::make(vm);
+                    const Pk w = PP::fma(g1, cm[k], g2 * sm[k]);
+                    const Pk u = PP::fma(g1, cm1[k], g2 * sm1[k]);
+                    const Pk v = PP::fma(PP::minus(g1), sm1[k], g2 * cm1[k]);
                     const Pk pqm = q[k] * fm;
                     ax[k] = PP::fma(pqm, u, ax[k]);
                     ay[k] = PP::fma(pqm, v, ay[k]);
                     aw[k] = PP::fma(f1 * bn[k], w, aw[k]);
                     az[k] = PP::fma(flm * bcur[k], w, az[k]);
-                    cm[k] = cm1[k];
-                    sm[k] = sm1[k];
                 }
             };
             auto row_vjp = [&](int l) {  // l >= 1 (the row l = 0 has no derivative)
-                const T* Kl = sK + tri(l, 0);
-                const T* Kb = sK + tri(l - 1, 0);
-                const T* Fl = sF + tri(l, 0);
-                Pk cm[NPK], sm[NPK];
-                load_packs(cp + l * TPT, cm);
-                load_packs(sp + l * TPT, sm);
-                Pk q2[NPK], q1[NPK], b2[NPK], b1[NPK], zero[NPK];
+                const int t0 = tri(l, 0);
+                const Pk* Kl = sK2 + t0;
+                const Pk* Kb = sK2 + tri(l - 1, 0);
+                const T* gp[PPT];  // upstream entry of column +m of each point
+                const T* gm[PPT];  // of column -m
+#pragma unroll
+                for (int i = 0; i < PPT; ++i) {
+                    gp[i] = grow + (i * LANES) * gst + l * l + 2 * l;
+                    gm[i] = grow + (i * LANES) * gst + l * l;
+                }
+                const T* cpm = cp + l * TPT;  // c_m of the current step
+                const T* spm = sp + l * TPT;
+                // the two newest values of each recurrence, and c/s of two neighbouring m, alternate between the
+                // a and b registers, so nothing is moved between steps
+                Pk qa[NPK], qb[NPK], ba[NPK], bb[NPK], ca[NPK], sa2[NPK], cb[NPK], sb[NPK], zero[NPK];
+                load_packs16<T, NPK>(cpm, cb);
+                load_packs16<T, NPK>(spm, sb);
 #pragma unroll
                 for (int k = 0; k < NPK; ++k) {
                     zero[k] = PP::all(T(0));
-                    q1[k] = PP::all(Kl[l]);  // Q_l^l is tabulated
+                    qa[k] = Kl[l];  // Q_l^l is tabulated
                 }
-                contract(l, l, Fl[l], q1, zero, zero, cm, sm);
+                // m = l
+                contract(t0 + l, 0, cpm - TPT, spm - TPT, gp, gm, qa, zero, zero, cb, sb, ca, sa2);
                 // m = l - 1: Q_l^{l-1} = -z Q_l^l, Q_{l-1}^{l-1} tabulated
-                {
-                    Pk q0[NPK];
 #pragma unroll
-                    for (int k = 0; k < NPK; ++k) {
-                        q0[k] = PP::minus(zz[k]) * q1[k];
-                        b1[k] = PP::all(Kb[l - 1]);
-                    }
-                    contract(l, l - 1, Fl[l - 1], q0, zero, b1, cm, sm);
-#pragma unroll
-                    for (int k = 0; k < NPK; ++k) {
-                        q2[k] = q1[k];
-                        q1[k] = q0[k];
-                        b2[k] = zero[k];
-                    }
+                for (int k = 0; k < NPK; ++k) {
+                    qb[k] = nzz[k] * qa[k];
+                    bb[k] = Kb[l - 1];
                 }
+                contract(t0 + l - 1, 1, cpm - 2 * TPT, spm - 2 * TPT, gp, gm, qb, zero, bb, ca, sa2, cb, sb);
                 if (l < 2) return;
                 Pk tz[NPK];  // 2 (m + 1) z
 #pragma unroll
-                for (int k = 0; k < NPK; ++k) tz[k] = PP::all(T(l - 1)) * tzz[k];
-                // m = l - 2: the general step for row l, Q_{l-1}^{l-2} = -z Q_{l-1}^{l-1}
-                {
-                    Pk q0[NPK], b0[NPK];
-                    const Pk km = PP::all(Kl[l - 2]);
-#pragma unroll
-                    for (int k = 0; k < NPK; ++k) {
-                        q0[k] = km * PP::fma(rho[k], q2[k], tz[k] * q1[k]);
-                        b0[k] = PP::minus(zz[k]) * b1[k];
-                    }
-                    contract(l, l - 2, Fl[l - 2], q0, b1, b0, cm, sm);
-#pragma unroll
-                    for (int k = 0; k < NPK; ++k) {
-                        q2[k] = q1[k];
-                        q1[k] = q0[k];
-                        b2[k] = b1[k];
-                        b1[k] = b0[k];
-                        tz[k] = tz[k] + PP::minus(tzz[k]);
-                    }
+                for (int k = 0; k < NPK; ++k) {
+                    tz[k] = PP::all(T(l - 1)) * tzz[k];
+                    // m = l - 2: the general step for row l, Q_{l-1}^{l-2} = -z Q_{l-1}^{l-1}
+                    qa[k] = Kl[l - 2] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
+                    ba[k] = nzz[k] * bb[k];
+                    tz[k] = tz[k] + ntzz[k];
                 }
-                for (int m = l - 3; m >= 0; --m) {
-                    Pk q0[NPK], b0[NPK];
-                    const Pk km = PP::all(Kl[m]), kb = PP::all(Kb[m]);
+                contract(t0 + l - 2, 2, cpm - 3 * TPT, spm - 3 * TPT, gp, gm, qa, bb, ba, cb, sb, ca, sa2);
+                int m = l - 3;
+#pragma unroll
+                for (int i = 0; i < PPT; ++i) {
+                    gp[i] -= 3;
+                    gm[i] += 3;
+                }
+                cpm -= 3 * TPT;
+                spm -= 3 * TPT;
+                for (; m >= 1; m -= 2) {
 #pragma unroll
                     for (int k = 0; k < NPK; ++k) {
-                        q0[k] = km * PP::fma(rho[k], q2[k], tz[k] * q1[k]);
-                        b0[k] = kb * PP::fma(rho[k], b2[k], tz[k] * b1[k]);
+                        qb[k] = Kl[m] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
+                        bb[k] = Kb[m] * PP::fma(rho[k], bb[k], tz[k] * ba[k]);
+                        tz[k] = tz[k] + ntzz[k];
                     }
-                    contract(l, m, Fl[m], q0, b1, b0, cm, sm);
+                    contract(t0 + m, 0, cpm - TPT, spm - TPT, gp, gm, qb, ba, bb, ca, sa2, cb, sb);
 #pragma unroll
                     for (int k = 0; k < NPK; ++k) {
-                        q2[k] = q1[k];
-                        q1[k] = q0[k];
-                        b2[k] = b1[k];
-                        b1[k] = b0[k];
-                        tz[k] = tz[k] + PP::minus(tzz[k]);
+                        qa[k] = Kl[m - 1] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
+                        ba[k] = Kb[m - 1] * PP::fma(rho[k], ba[k], tz[k] * bb[k]);
+                        tz[k] = tz[k] + ntzz[k];
                     }
+                    contract(t0 + m - 1, 1, cpm - 2 * TPT, spm - 2 * TPT, gp, gm, qa, bb, ba, cb, sb, ca, sa2);
+#pragma unroll
+                    for (int i = 0; i < PPT; ++i) {
+                        gp[i] -= 2;
+                        gm[i] += 2;
+                    }
+                    cpm -= 2 * TPT;
+                    spm -= 2 * TPT;
+                }
+                if (m == 0) {
+#pragma unroll
+                    for (int k = 0; k < NPK; ++k) {
+                        qb[k] = Kl[0] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
+                        bb[k] = Kb[0] * PP::fma(rho[k], bb[k], tz[k] * ba[k]);
+                    }
+                    contract(t0, 0, cpm - TPT, spm - TPT, gp, gm, qb, ba, bb, ca, sa2, cb, sb);
                 }
             };
             for (int j = s; 2 * j <= L; j += S) {
@@ -992,8 +1042,8 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
             // x and y multiply the sums of their second terms once
             {
                 Pk px[NPK], py[NPK];
-                load_packs(sP + 0 * TPT + q0i, px);
-                load_packs(sP + 1 * TPT + q0i, py);
+                load_packs16<T, NPK>(sP + 0 * TPT + q0i, px);
+                load_packs16<T, NPK>(sP + 1 * TPT + q0i, py);
 #pragma unroll
                 for (int k = 0; k < NPK; ++k) {
                     ax[k] = PP::fma(px[k], aw[k], ax[k]);

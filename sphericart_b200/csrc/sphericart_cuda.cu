@@ -313,7 +313,8 @@ size_t panel_image_bytes(int l_max, int level, int tp, size_t elem) {
 
 size_t panel_fixed_bytes(int l_max, int level, int batch, size_t elem) {
     const size_t nq = size_t(n_table(l_max));
-    const size_t consts = band_align16(2 * nq, elem) * elem + (level >= 1 ? nq * 16 : 0);
+    // (values only: F and K with every entry broadcast to a pack of points, 8 bytes each; no descriptors)
+    const size_t consts = level >= 1 ? band_align16(2 * nq, elem) * elem + nq * 16 : (2 * nq * 8 + 15) / 16 * 16;
     const size_t per_point = size_t(panel_point_state(l_max, level));
     return consts + band_align16(size_t(batch) * per_point, elem) * elem;
 }
@@ -440,8 +441,9 @@ size_t panel_vjp_bytes(int l_max, int batch, int threads, size_t elem) {
     const size_t ny = size_t(n_columns(l_max));
     const size_t q = 16 / elem;
     const size_t stride = ny % 2 != 0 ? ny : ((ny / q) % 2 == 0 ? ny + q : ny);
-    return (band_align16(2 * nq, elem) + band_align16(size_t(batch) * size_t(panel_point_state(l_max, 0)), elem) +
-            band_align16(size_t(batch) * stride, elem) + band_align16(3 * size_t(threads) * q, elem)) * elem + 16;
+    return (4 * nq * 8 + 15) / 16 * 16 +
+           (band_align16(size_t(batch) * size_t(panel_point_state(l_max, 0)), elem) + band_align16(size_t(batch) * stride, elem) +
+            band_align16(3 * size_t(threads) * q, elem)) * elem + 16;
 }
 
 // Same shape rules as the values-only forward path, whose structure the kernel shares (a thread carries
