@@ -18,9 +18,9 @@ constexpr int MAX_DEVICES = 64;
 // of the values, 4: VJP of (values, gradients). The crossovers were measured on a B200 for both
 // element types (fraction of the copy peak, tile / panel or band):
 //   values        l = 9..20: 1.00-1.04 / 0.29-0.57              -> tile wherever compiled
-//   gradients     float32 l = 9: 0.89 / 0.69, l = 10: 0.76 / 0.76, l = 11: 0.60 / 0.82;
-//                 float64 l = 8: 1.02 / 0.92, l = 9: 0.68 / 0.87, l = 10: 0.70 / 0.89
-//                                                               -> tile up to 10 (float32), 8 (float64)
+//   gradients     float32 l = 9: 0.90 / 0.70, l = 10: 0.77 / 0.90, l = 11: 0.60 / 0.82;
+//                 float64 l = 8: 1.03 / 0.87, l = 9: 0.68 / 0.87, l = 10: 0.70 / 0.89
+//                                                               -> tile up to 9 (float32), 8 (float64)
 //   Hessians      float32 l = 4: 0.88 / 0.86, l = 5: 0.57 / 0.67; float64 l = 4: 0.84 / 0.53, l = 5: 0.57 / 0.57
 //                                                               -> tile up to 4
 //   VJP           l = 9..20: 0.57-1.03 / 0.15-0.25 (band)       -> tile wherever compiled
@@ -28,7 +28,7 @@ constexpr int MAX_DEVICES = 64;
 //                                                               -> tile up to 10 (float32), 8 (float64)
 constexpr bool tile_serves(int kind, int l_max, int elem_bytes) {
     if (l_max > TILE_LMAX) return false;
-    if (kind == 1) return l_max <= (elem_bytes == 4 ? 10 : 8);
+    if (kind == 1) return l_max <= (elem_bytes == 4 ? 9 : 8);
     if (kind == 2) return l_max <= 4;
     if (kind == 4) return l_max <= (elem_bytes == 4 ? 10 : 8);
     // the VJP kernel keeps a tile's upstream rows in shared memory: at least two tiles per SM

@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     T* out = image0 + p * st0;         // row of point i at out + i * pst
                     const int pst = lanes * st0;
                     constexpr int NPK = PPT / PP::N;
-                    Pk nzz[NPK], rho[NPK], tzz[NPK], ntzz[NPK];  // -z, x^2 + y^2, 2z, -2z
+                    Pk nzz[NPK], rho[NPK], tzz[NPK];  // -z, x^2 + y^2, 2z
                     {
                         Pk px[NPK], py[NPK], pz[NPK];
                         load_packs16<T, NPK>(sP + 0 * TPT + q0i, px);
@@ -583,7 +583,6 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                             rho[k] = PP::fma(px[k], px[k], py[k] * py[k]);
                             nzz[k] = PP::minus(pz[k]);
                             tzz[k] = pz[k] + pz[k];
-                            ntzz[k] = nzz[k] + nzz[k];
                         }
                     }
                     // writes F Q (c_m, s_m) of every point for one m; q holds Q_l^m per point; pp / pm point at
@@ -626,9 +625,12 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
 #pragma unroll
                         for (int k = 0; k < NPK; ++k) qb[k] = nzz[k] * qa[k];  // Q_l^{l-1}
                         emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[l - 1], qb, l > 1);
-                        Pk tz[NPK];  // 2 (m + 1) z
+                        // 2 (m + 1) z as one product per step (a running difference would drift: float32 has no
+                        // error budget to spare at these degrees)
+                        T mp1 = T(l - 1);
+                        Pk tz[NPK];
 #pragma unroll
-                        for (int k = 0; k < NPK; ++k) tz[k] = PP::all(T(l - 1)) * tzz[k];
+                        for (int k = 0; k < NPK; ++k) tz[k] = PP::all(mp1) * tzz[k];
                         int m = l - 2;
 #pragma unroll
                         for (int i = 0; i < PPT; ++i) {
@@ -643,14 +645,15 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
 #pragma unroll
                             for (int k = 0; k < NPK; ++k) {
                                 qa[k] = Kl[m] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
-                                tz[k] = tz[k] + ntzz[k];
+                                tz[k] = PP::all(mp1 - T(1)) * tzz[k];
                             }
                             emit(pp, pm, 0, cpm, spm, Fl[m], qa, true);
 #pragma unroll
                             for (int k = 0; k < NPK; ++k) {
                                 qb[k] = Kl[m - 1] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
-                                tz[k] = tz[k] + ntzz[k];
+                                tz[k] = PP::all(mp1 - T(2)) * tzz[k];
                             }
+                            mp1 -= T(2);
                             emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[m - 1], qb, true);
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
@@ -664,7 +667,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
 #pragma unroll
                             for (int k = 0; k < NPK; ++k) {
                                 qa[k] = Kl[m] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
-                                tz[k] = tz[k] + ntzz[k];
+                                tz[k] = PP::all(mp1 - T(1)) * tzz[k];
                             }
                             emit(pp, pm, 0, cpm, spm, Fl[m], qa, m > 0);
                             if (m == 1) {
@@ -910,7 +913,7 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
             const T* cp = sc + 2 * TPT + q0i;    // c_m of the thread's points at cp[m * TPT ...]
             const T* sp = ss + 2 * TPT + q0i;
             const T* grow = rows + p * gst;      // row of point i at grow + i * LANES * gst
-            Pk nzz[NPK], rho[NPK], tzz[NPK], ntzz[NPK];  // -z, x^2 + y^2, 2z, -2z
+            Pk nzz[NPK], rho[NPK], tzz[NPK];  // -z, x^2 + y^2, 2z
             {
                 Pk px[NPK], py[NPK], pz[NPK];
                 load_packs16<T, NPK>(sP + 0 * TPT + q0i, px);
@@ -921,7 +924,6 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                     rho[k] = PP::fma(px[k], px[k], py[k] * py[k]);
                     nzz[k] = PP::minus(pz[k]);
                     tzz[k] = pz[k] + pz[k];
-                    ntzz[k] = nzz[k] + nzz[k];
                 }
             }
             // One (l, m). q = Q_l^m, bn = Q_{l-1}^{m+1}, bcur = Q_{l-1}^m (zeros where absent); cm, sm hold c_m, s_m;
@@ -985,15 +987,18 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                 }
                 contract(t0 + l - 1, 1, cpm - 2 * TPT, spm - 2 * TPT, gp, gm, qb, zero, bb, ca, sa2, cb, sb);
                 if (l < 2) return;
-                Pk tz[NPK];  // 2 (m + 1) z
+                // 2 (m + 1) z as one product per step (a running difference would drift)
+                T mp1 = T(l - 1);
+                Pk tz[NPK];
 #pragma unroll
                 for (int k = 0; k < NPK; ++k) {
-                    tz[k] = PP::all(T(l - 1)) * tzz[k];
+                    tz[k] = PP::all(mp1) * tzz[k];
                     // m = l - 2: the general step for row l, Q_{l-1}^{l-2} = -z Q_{l-1}^{l-1}
                     qa[k] = Kl[l - 2] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
                     ba[k] = nzz[k] * bb[k];
-                    tz[k] = tz[k] + ntzz[k];
+                    tz[k] = PP::all(mp1 - T(1)) * tzz[k];
                 }
+                mp1 -= T(1);
                 contract(t0 + l - 2, 2, cpm - 3 * TPT, spm - 3 * TPT, gp, gm, qa, bb, ba, cb, sb, ca, sa2);
                 int m = l - 3;
 #pragma unroll
@@ -1008,15 +1013,16 @@ __global__ void __launch_bounds__(256) sph_panel_vjp_kernel(const __grid_constan
                     for (int k = 0; k < NPK; ++k) {
                         qb[k] = Kl[m] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
                         bb[k] = Kb[m] * PP::fma(rho[k], bb[k], tz[k] * ba[k]);
-                        tz[k] = tz[k] + ntzz[k];
+                        tz[k] = PP::all(mp1 - T(1)) * tzz[k];
                     }
                     contract(t0 + m, 0, cpm - TPT, spm - TPT, gp, gm, qb, ba, bb, ca, sa2, cb, sb);
 #pragma unroll
                     for (int k = 0; k < NPK; ++k) {
                         qa[k] = Kl[m - 1] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
                         ba[k] = Kb[m - 1] * PP::fma(rho[k], ba[k], tz[k] * bb[k]);
-                        tz[k] = tz[k] + ntzz[k];
+                        tz[k] = PP::all(mp1 - T(2)) * tzz[k];
                     }
+                    mp1 -= T(2);
                     contract(t0 + m - 1, 1, cpm - 2 * TPT, spm - 2 * TPT, gp, gm, qa, bb, ba, cb, sb, ca, sa2);
 #pragma unroll
                     for (int i = 0; i < PPT; ++i) {
