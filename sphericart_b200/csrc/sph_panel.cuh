@@ -585,13 +585,10 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                             tzz[k] = pz[k] + pz[k];
                         }
                     }
-                    // writes F Q (c_m, s_m) of every point for one m; q holds Q_l^m per point; pp / pm point at
-                    // the columns +m / -m of each point's row
-                    auto emit = [&](T* const (&pp)[PPT], T* const (&pm)[PPT], int off, const T* cpm, const T* spm, Pk fm,
+                    // writes F Q (c_m, s_m) of every point for one m; q holds Q_l^m per point, cv / sv the points' c_m, s_m;
+                    // pp / pm point at the columns +m / -m of each point's row
+                    auto emit = [&](T* const (&pp)[PPT], T* const (&pm)[PPT], int off, const Pk (&cv)[NPK], const Pk (&sv)[NPK], Pk fm,
                                     const Pk (&q)[NPK], bool minus_too) {
-                        Pk cv[NPK], sv[NPK];
-                        load_packs16<T, NPK>(cpm, cv);
-                        load_packs16<T, NPK>(spm, sv);
 #pragma unroll
                         for (int k = 0; k < NPK; ++k) {
                             const Pk pq = q[k] * fm;
@@ -617,20 +614,21 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                         const T* cpm = cp + l * TPT;
                         const T* spm = sp + l * TPT;
                         // the two newest values of the recurrence alternate between qa and qb
-                        Pk qa[NPK], qb[NPK];
+                        Pk qa[NPK], qb[NPK], c0[NPK], s0[NPK], c1[NPK], s1[NPK];
+                        load_packs16<T, NPK>(cpm, c0);
+                        load_packs16<T, NPK>(spm, s0);
+                        load_packs16<T, NPK>(cpm - TPT, c1);  // (l = 0: the zero rows)
+                        load_packs16<T, NPK>(spm - TPT, s1);
 #pragma unroll
                         for (int k = 0; k < NPK; ++k) qa[k] = Kl[l];  // Q_l^l is tabulated
-                        emit(pp, pm, 0, cpm, spm, Fl[l], qa, l > 0);
+                        emit(pp, pm, 0, c0, s0, Fl[l], qa, l > 0);
                         if (l == 0) return;
 #pragma unroll
                         for (int k = 0; k < NPK; ++k) qb[k] = nzz[k] * qa[k];  // Q_l^{l-1}
-                        emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[l - 1], qb, l > 1);
+                        emit(pp, pm, 1, c1, s1, Fl[l - 1], qb, l > 1);
                         // 2 (m + 1) z as one product per step (a running difference would drift: float32 has no
                         // error budget to spare at these degrees)
                         T mp1 = T(l - 1);
-                        Pk tz[NPK];
-#pragma unroll
-                        for (int k = 0; k < NPK; ++k) tz[k] = PP::all(mp1) * tzz[k];
                         int m = l - 2;
 #pragma unroll
                         for (int i = 0; i < PPT; ++i) {
@@ -640,21 +638,22 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                         cpm -= 2 * TPT;
                         spm -= 2 * TPT;
                         // Q_l^m = K (2 (m+1) z Q_l^{m+1} + rho Q_l^{m+2}), two steps per turn: the new value takes the
-                        // place of the older of the two it was made from, so nothing is moved between registers
+                        // place of the older of the two it was made from, so nothing is moved between registers, and
+                        // both steps' table entries are requested before the first step's stores
                         for (; m >= 2; m -= 2) {
-#pragma unroll
-                            for (int k = 0; k < NPK; ++k) {
-                                qa[k] = Kl[m] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
-                                tz[k] = PP::all(mp1 - T(1)) * tzz[k];
-                            }
-                            emit(pp, pm, 0, cpm, spm, Fl[m], qa, true);
-#pragma unroll
-                            for (int k = 0; k < NPK; ++k) {
-                                qb[k] = Kl[m - 1] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
-                                tz[k] = PP::all(mp1 - T(2)) * tzz[k];
-                            }
+                            load_packs16<T, NPK>(cpm, c0);
+                            load_packs16<T, NPK>(spm, s0);
+                            load_packs16<T, NPK>(cpm - TPT, c1);
+                            load_packs16<T, NPK>(spm - TPT, s1);
+                            const Pk k0 = Kl[m], k1 = Kl[m - 1], f0 = Fl[m], f1 = Fl[m - 1];
+                            const Pk t0 = PP::all(mp1), t1 = PP::all(mp1 - T(1));
                             mp1 -= T(2);
-                            emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[m - 1], qb, true);
+#pragma unroll
+                            for (int k = 0; k < NPK; ++k) qa[k] = k0 * PP::fma(rho[k], qa[k], t0 * tzz[k] * qb[k]);
+                            emit(pp, pm, 0, c0, s0, f0, qa, true);
+#pragma unroll
+                            for (int k = 0; k < NPK; ++k) qb[k] = k1 * PP::fma(rho[k], qb[k], t1 * tzz[k] * qa[k]);
+                            emit(pp, pm, 1, c1, s1, f1, qb, true);
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
                                 pp[i] -= 2;
@@ -664,16 +663,18 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                             spm -= 2 * TPT;
                         }
                         if (m >= 0) {
+                            load_packs16<T, NPK>(cpm, c0);
+                            load_packs16<T, NPK>(spm, s0);
+                            load_packs16<T, NPK>(cpm - TPT, c1);  // (m = 0: the zero rows, not used)
+                            load_packs16<T, NPK>(spm - TPT, s1);
+                            const Pk t0 = PP::all(mp1), t1 = PP::all(mp1 - T(1));
 #pragma unroll
-                            for (int k = 0; k < NPK; ++k) {
-                                qa[k] = Kl[m] * PP::fma(rho[k], qa[k], tz[k] * qb[k]);
-                                tz[k] = PP::all(mp1 - T(1)) * tzz[k];
-                            }
-                            emit(pp, pm, 0, cpm, spm, Fl[m], qa, m > 0);
+                            for (int k = 0; k < NPK; ++k) qa[k] = Kl[m] * PP::fma(rho[k], qa[k], t0 * tzz[k] * qb[k]);
+                            emit(pp, pm, 0, c0, s0, Fl[m], qa, m > 0);
                             if (m == 1) {
 #pragma unroll
-                                for (int k = 0; k < NPK; ++k) qb[k] = Kl[0] * PP::fma(rho[k], qb[k], tz[k] * qa[k]);
-                                emit(pp, pm, 1, cpm - TPT, spm - TPT, Fl[0], qb, false);
+                                for (int k = 0; k < NPK; ++k) qb[k] = Kl[0] * PP::fma(rho[k], qb[k], t1 * tzz[k] * qa[k]);
+                                emit(pp, pm, 1, c1, s1, Fl[0], qb, false);
                             }
                         }
                     };
