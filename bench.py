@@ -56,8 +56,8 @@ NCU_TRAFFIC = {
     "spherical_l8_f32_grad": {"points": 524288, "dram_bytes": 627.0e6},
     "solid_l6_f32_grad_n1e6": {"points": 1000000, "dram_bytes": 737.5e6},
     "spherical_l4_f32_fwd_vjp_n5e7": {"points": 4194304, "dram_bytes": 412.3e6 + 514.0e6},
-    "spherical_l16_f32_hess_n2e6": {"points": 65536, "dram_bytes": 926.4e6},
-    "spherical_l32_f64_grad_n1e6": {"points": 32768, "dram_bytes": 1083.2e6},
+    "spherical_l16_f32_hess_n2e6": {"points": 65536, "dram_bytes": 926.5e6},
+    "spherical_l32_f64_grad_n1e6": {"points": 32768, "dram_bytes": 1087.5e6},
 }
 
 
