@@ -547,14 +547,16 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                 };
                 if constexpr (LEVEL >= 1) {
                     int t = s;
-                    // two pairs in flight per thread
-                    for (; t + S < nq; t += 2 * S) {
+                    // two pairs in flight per thread (one for float64 Hessians: two pairs' inputs and thirteen outputs per
+                    // column cost registers that are better spent on a second CTA per SM)
+                    constexpr bool ONE_IN_FLIGHT = sizeof(T) == 8 && LEVEL == 2;
+                    for (; !ONE_IN_FLIGHT && t + S < nq; t += 2 * S) {
                         const PairInputs<T, LEVEL> in0 = load(t);
                         const PairInputs<T, LEVEL> in1 = load(t + S);
                         finish_pair(in0);
                         finish_pair(in1);
                     }
-                    if (t < nq) finish_pair(load(t));
+                    for (; t < nq; t += S) finish_pair(load(t));
                 } else {
                     // Values only: no Q table. A slice takes whole rows, in pairs (j, l_max - j) of constant
                     // total length, carries each row's recurrence in registers (the reference's own scheme,
