@@ -513,6 +513,7 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
     constexpr int S0 = NY + PAD, S1 = 3 * NY + PAD;
     // padded rows (see tile_row_pad) arrive as one bulk load per row and array, issued by the row's
     // lane; worthwhile from 256-byte rows on, shorter padded rows are staged by the warp
+    const bool aligned16_in = use_bulk != 0;
     if constexpr (PAD != 0 && NY * sizeof(T) < 256) use_bulk = 0;
     T* img_s = reinterpret_cast<T*>(smem_raw) + size_t(warp) * TILE_POINTS * (S0 + S1);
     T* img_d = img_s + TILE_POINTS * S0;
@@ -569,11 +570,16 @@ sph_vjp2_tile_kernel(const T* __restrict__ xyz, const T* __restrict__ sph_grad, 
             phase ^= 1u;
         } else {
             __syncwarp();  // previous tile's reads of the images are complete
-            if (has_value_grad) {
-                const T* src = sph_grad + first * NY;
-                for (int e = lane; e < TILE_POINTS * NY; e += 32) img_s[e + PAD * (e / NY)] = (e < npts * NY) ? src[e] : T(0);
-            }
-            {
+            if (PAD != 0 && aligned16_in) {
+                // short padded rows: 16-byte pieces, unrolled so that the loads overlap (rows past the end of
+                // the input keep whatever they hold: their lanes write no result)
+                if (has_value_grad) copy_rows_in_16<T, NY, S0, TILE_POINTS>(img_s, sph_grad + first * NY, npts, lane);
+                copy_rows_in_16<T, 3 * NY, S1, TILE_POINTS>(img_d, dsph_grad + first * 3 * NY, npts, lane);
+            } else {
+                if (has_value_grad) {
+                    const T* src = sph_grad + first * NY;
+                    for (int e = lane; e < TILE_POINTS * NY; e += 32) img_s[e + PAD * (e / NY)] = (e < npts * NY) ? src[e] : T(0);
+                }
                 const T* src = dsph_grad + first * 3 * NY;
                 for (int e = lane; e < TILE_POINTS * 3 * NY; e += 32)
                     img_d[e + PAD * (e / (3 * NY))] = (e < npts * 3 * NY) ? src[e] : T(0);
