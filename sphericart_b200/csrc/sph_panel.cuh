@@ -289,7 +289,6 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     const int slots = a.slots;
     const bool bulk = a.bulk != 0;
     const bool packed_rows = (ny & 1) != 0;  // odd row length: the image is the exact picture of global memory
-    [[maybe_unused]] const bool rotate_pairs = !packed_rows && tp > 8;
     constexpr unsigned E = unsigned(TPT) * unsigned(sizeof(T));
     constexpr int Q16 = 16 / int(sizeof(T));
 
@@ -381,7 +380,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
     T next_x = T(1), next_y = T(0), next_z = T(0);
     if (sa < SA) fetch_point(blockIdx.x, next_x, next_y, next_z);
     int slot = 0;
-    int committed = 0;  // first warp only: bulk-store groups committed so far (every lane commits one per panel)
+    int committed = 0;  // thread 0 only: bulk-store groups committed so far
     for (long long batch = blockIdx.x; batch < nbatches; batch += gridDim.x) {
         const long long batch_first = batch * TPT;
 
@@ -436,7 +435,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
 
             // the engine must be done reading this slot's previous image before phase B overwrites it:
             // of the groups committed so far all but the last slots - 1 must have been read
-            if (tid < 32 && committed >= slots) bulk_wait_read_pending(slots - 1);
+            if (tid == 0 && committed >= slots) bulk_wait_read_pending(slots - 1);
             __syncthreads();  // tables complete, slot free
 
             if (s < S) {
@@ -550,34 +549,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                     // two pairs in flight per thread (one for float64 Hessians: two pairs' inputs and thirteen outputs per
                     // column cost registers that are better spent on a second CTA per SM)
                     constexpr bool ONE_IN_FLIGHT = sizeof(T) == 8 && LEVEL == 2;
-                    if (rotate_pairs) {
-                        // Rows of even length, more than eight points side by side: points eight apart share their
-                        // banks (rows are an odd number of 16-byte groups apart). A slice then takes the pairs four
-                        // at a time and each group of eight points walks its four in a different rotation, so that
-                        // at any moment the groups write columns that differ by one to three elements.
-                        const int rot = (p >> 3) & 3;
-                        for (int c = 4 * s; c < nq; c += 4 * S) {
-                            const int ta = c + rot, tb = c + ((rot + 1) & 3), tc = c + ((rot + 2) & 3), td = c + ((rot + 3) & 3);
-                            if (ONE_IN_FLIGHT) {
-                                if (ta < nq) finish_pair(load(ta));
-                                if (tb < nq) finish_pair(load(tb));
-                                if (tc < nq) finish_pair(load(tc));
-                                if (td < nq) finish_pair(load(td));
-                            } else {
-                                // (a pair index past the end is replaced by the last pair, whose columns are then
-                                // written twice with the same values: no branch in the common path)
-                                const PairInputs<T, LEVEL> in0 = load(ta < nq ? ta : nq - 1);
-                                const PairInputs<T, LEVEL> in1 = load(tb < nq ? tb : nq - 1);
-                                finish_pair(in0);
-                                finish_pair(in1);
-                                const PairInputs<T, LEVEL> in2 = load(tc < nq ? tc : nq - 1);
-                                const PairInputs<T, LEVEL> in3 = load(td < nq ? td : nq - 1);
-                                finish_pair(in2);
-                                finish_pair(in3);
-                            }
-                        }
-                    }
-                    int t = rotate_pairs ? nq : s;
+                    int t = s;
                     for (; !ONE_IN_FLIGHT && t + S < nq; t += 2 * S) {
                         const PairInputs<T, LEVEL> in0 = load(t);
                         const PairInputs<T, LEVEL> in1 = load(t + S);
@@ -734,16 +706,17 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
                         if constexpr (LEVEL >= 1) copy_out(gd, image1, shift1, nvalid * 3 * ny);
                         if constexpr (LEVEL >= 2) copy_out(gdd, image2, shift2, nvalid * 9 * ny);
                     }
-                } else if (tid < nvalid) {
-                    // every point's row is 16-byte aligned on both sides: one store per point and array, issued by
-                    // the first warp's lanes side by side (a panel has at most 32 points)
-                    const int r = tid;
-                    bulk_store_smem_to_global(gsph + size_t(r) * ny, image0 + r * st0, ny_b);
-                    if constexpr (LEVEL >= 1) bulk_store_smem_to_global(gd + size_t(r) * 3 * ny, image1 + r * st1, 3 * ny_b);
-                    if constexpr (LEVEL >= 2) bulk_store_smem_to_global(gdd + size_t(r) * 9 * ny, image2 + r * st2, 9 * ny_b);
+                } else if (tid == 0) {
+                    // every point's row is 16-byte aligned on both sides: one store per point and array (issued by one
+                    // thread: spreading the issue over a warp's lanes measured 1 - 3 % slower, 10 % for values only)
+                    for (int r = 0; r < nvalid; ++r) {
+                        bulk_store_smem_to_global(gsph + size_t(r) * ny, image0 + r * st0, ny_b);
+                        if constexpr (LEVEL >= 1) bulk_store_smem_to_global(gd + size_t(r) * 3 * ny, image1 + r * st1, 3 * ny_b);
+                        if constexpr (LEVEL >= 2) bulk_store_smem_to_global(gdd + size_t(r) * 9 * ny, image2 + r * st2, 9 * ny_b);
+                    }
                 }
-                if (tid < 32) {
-                    bulk_commit();  // (an empty group for the lanes that issued nothing)
+                if (tid == 0) {
+                    bulk_commit();
                     ++committed;
                 }
             } else {
@@ -762,7 +735,7 @@ __global__ void __launch_bounds__(256) sph_panel_kernel(const __grid_constant__ 
         // follows phase B of this batch's last panel)
     }
     // shared memory must outlive the engine's reads
-    if (tid < 32 && committed > 0) bulk_wait_read_all();
+    if (tid == 0 && committed > 0) bulk_wait_read_all();
 }
 
 // ---------------------------------------------------------------------------------------------

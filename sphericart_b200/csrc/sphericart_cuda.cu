@@ -419,6 +419,19 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
             }
         }
     }
+    // Float32 gradients with rows of even length at moderate degrees: the score above settles on CTAs of two warps
+    // (eight points, eight slices); table batches of sixteen points with sixteen slices measured better
+    // (l_max = 11 / 13 / 15: 0.79 / 0.79 / 0.78 -> 0.83 / 0.82 / 0.87 of the copy peak; from l_max = 17 on and
+    // in float64 the score's own choice is the best measured).
+    if (level == 1 && elem == 4 && even_rows && best.feasible && best.tp == 8 && best.batch == 8 && best.threads < 128 &&
+        k.panel_batch <= 0 && k.panel_points <= 0 && k.panel_threads <= 0) {
+        const size_t smem = panel_fixed_bytes(l_max, level, 16, elem) + panel_image_bytes(l_max, level, 8, elem);
+        if (smem <= smem_limit && 233472 / (smem + 1024) >= 4) {
+            best.batch = 16;
+            best.threads = 128;
+            best.smem = smem;
+        }
+    }
     // Each CTA stages the constants once; enough table batches per CTA amortise that: at least eight,
     // and at least 256 points (measured: 8 batches per CTA 3 - 10 % faster than 4 and 15 - 25 % faster
     // than 1; l_max = 32 float64 gradients with batches of four points: 32 / 64 batches -> 0.73 / 0.80).
