@@ -432,6 +432,36 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
             best.smem = smem;
         }
     }
+    // Shapes measured on a B200 over twelve to twenty-five candidates per case (1.5 GB launches, fraction of the copy
+    // peak, the score's choice -> the shape taken here). Hessians:
+    //   float32 l_max 11: 0.85 -> 0.90   12: 0.74 -> 0.88   13: 0.78 -> 0.82   14: 0.84 -> 0.91   15: 0.75 -> 0.83
+    //                 17: 0.81 -> 0.86   18: 0.75 -> 0.85   19: 0.71 -> 0.86
+    //   float64 l_max  7: 0.76 -> 0.83   13: 0.74 -> 0.85   15: 0.75 -> 0.77   16: 0.77 -> 0.82   20: 0.72 -> 0.76
+    //                 24: 0.59 -> 0.66
+    // gradients: float32 l_max 16: 0.86 -> 0.90   21: 0.78 -> 0.82   26: 0.71 -> 0.75; float64 l_max 28: 0.59 -> 0.62.
+    // Where a swept case is not listed (Hessians: float32 l_max = 16, 20, 24, float64 l_max = 5, 10; gradients: float32
+    // l_max = 18, 20, 22, float64 l_max = 16 ... 24) the score's choice was the best measured or within 2 % of it; the
+    // other degrees were not swept. For Hessians small panels of four, two or one point with about four warps per CTA
+    // win: several CTAs per SM hide each other's barriers.
+    if (level >= 1 && best.feasible && k.panel_batch <= 0 && k.panel_points <= 0 && k.panel_threads <= 0 && k.panel_slots <= 0) {
+        struct Shape { int level, elem, l_max, batch, tp, threads; };
+        static const Shape measured[] = {
+            {2, 4, 11, 8, 4, 64},  {2, 4, 12, 8, 4, 128}, {2, 4, 13, 8, 4, 96},  {2, 4, 14, 8, 4, 96},  {2, 4, 15, 8, 4, 128},
+            {2, 4, 17, 4, 2, 128}, {2, 4, 18, 4, 2, 128}, {2, 4, 19, 4, 2, 96},  {2, 8, 7, 16, 8, 128}, {2, 8, 13, 8, 2, 128},
+            {2, 8, 15, 4, 2, 128}, {2, 8, 16, 4, 2, 128}, {2, 8, 20, 4, 1, 128}, {2, 8, 24, 2, 1, 96},
+            {1, 4, 16, 16, 16, 192}, {1, 4, 21, 8, 4, 96}, {1, 4, 26, 8, 4, 192}, {1, 8, 28, 4, 2, 128}};
+        for (const Shape& m : measured) {
+            if (m.level != level || m.l_max != l_max || size_t(m.elem) != elem) continue;
+            const size_t smem = panel_fixed_bytes(l_max, level, m.batch, elem) + panel_image_bytes(l_max, level, m.tp, elem);
+            if (smem <= smem_limit) {
+                best.batch = m.batch;
+                best.tp = m.tp;
+                best.slots = 1;
+                best.threads = m.threads;
+                best.smem = smem;
+            }
+        }
+    }
     // Each CTA stages the constants once; enough table batches per CTA amortise that: at least eight,
     // and at least 256 points (measured: 8 batches per CTA 3 - 10 % faster than 4 and 15 - 25 % faster
     // than 1; l_max = 32 float64 gradients with batches of four points: 32 / 64 batches -> 0.73 / 0.80).
