@@ -1,8 +1,8 @@
 // "Panel" kernels: forward evaluation (values, gradients, Hessians) for any maximum degree
 // (run-time l_max) with a whole CTA working on a panel of tp consecutive points at a time
 // (tp = 1 ... 32). They serve the cases with rows too long for the compile-time tile kernels (see
-// the dispatch in sphericart_cuda.cu); the fused backward passes of those cases stay with the band
-// kernel.
+// the dispatch in sphericart_cuda.cu). The fused first-order backward of those cases is the second
+// kernel of this file (sph_panel_vjp_kernel); the second-order backward stays with the band kernel.
 //
 // Work split. For a panel, thread t of a CTA is (point p = t mod tp, slice s = t / tp);
 // S = blockDim.x / tp slices share each point. Neighbouring lanes therefore hold DIFFERENT POINTS and
@@ -17,8 +17,10 @@
 //     Q_l^m with the reference's downward-in-m recurrence
 //     (sphericart/include/templates_core.hpp:123,155,202), rows dealt to the slices in pairs
 //     (l, l_max - l) of constant total length. The recurrence is a serial chain, so batching several
-//     panels' points gives this phase its parallelism. Carried in float64 for both element types and
-//     rounded once on storing, as in the band kernel. Four zeros follow every diagonal, a block of
+//     panels' points gives this phase its parallelism. Carried in the element type (in float64 on
+//     request); four steps per turn with the constants loaded ahead of the chain. Values-only calls
+//     build no Q table at all: their slices carry whole rows in registers (see phase B of LEVEL 0).
+//     Four zeros follow every diagonal, a block of
 //     zeros stands for the rows -1 and -2, and c, s carry two zeros before m = 0, so that every "term
 //     absent" case of the derivative formulas reads a zero.
 //  B. Pairs, panel by panel. Slice s evaluates the pairs t = s, s + S, ... of the flattened
@@ -32,11 +34,13 @@
 //     aligned by itself; rows get 16 bytes of padding where needed to keep neighbouring points an odd
 //     number of 16-byte groups apart, and leave as one bulk store per point and array.
 //     A CTA owns a ring of `slots` images: a panel's image is only waited for when its slot comes
-//     round again, so the engine drains one image while the CTA fills the next. What bounds these
-//     kernels is the number of image bytes an SM keeps in flight towards HBM, which is why the launch
-//     plan fills the shared memory with images first.
+//     round again, so the engine drains one image while the CTA fills the next (the launch plan has
+//     never found more than one slot to pay: see make_panel_plan in sphericart_cuda.cu). What bounds
+//     these kernels is the number of image bytes an SM keeps in flight towards HBM and the time its
+//     CTAs spend at their barriers.
 //
-// No communication between CTAs or GPUs, no spin-wait. Replaces spherical_harmonics_kernel
+// No communication between CTAs or GPUs; the only waits are on this CTA's own TMA copies (bounded
+// polls in the VJP kernel). Replaces spherical_harmonics_kernel
 // (sphericart/src/sphericart_impl.cu:207-615).
 #pragma once
 
