@@ -396,14 +396,21 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
                         // it the independent work that the other levels get from many warps; the kernel is bound
                         // by shared-memory traffic (image writes, the engine's reads, the c/s loads), and four
                         // slices share a warp, so bank conflicts between slices vary with l_max. Measured: one
-                        // pair of rows per thread is best (two: 0.49 against 0.79, float32 l_max = 24); eight
-                        // threads side by side (32 / 16 points per panel) where two CTAs fit an SM
-                        // (float32 l_max = 24: 32 / 16 / 8 points per panel -> 0.79 / 0.64 / 0.56 of the copy
-                        // peak; float64 l_max = 24: 16 / 8 points -> 0.77 / 0.67), half as many where only one
-                        // would fit (float32 l_max = 28: 0.53 against 0.62).
-                        // (float64 l_max = 32: 16 points per panel on one CTA per SM 0.53, 8 points on three 0.47)
-                        score = std::sqrt(std::min(lanes, 8) / 8.0) * balance / real_per_slice * (ctas >= 2 ? 1.0 : 0.7) *
-                                (0.85 + 0.05 * std::min<long long>(ctas, 3)) * (tp >= 16 ? 1.0 : 0.85);
+                        // pair of rows per thread is best (two: 0.49 against 0.79, float32 l_max = 24). Float32:
+                        // eight threads side by side (32 points per panel) where two CTAs fit an SM (l_max = 24:
+                        // 32 / 16 / 8 points -> 0.72 / 0.54 / 0.54 of the copy peak), half as many where only one
+                        // would (l_max = 28: 0.55 against 0.61). Float64: four threads side by side (8 points per
+                        // panel) at every degree measured (l_max = 22 / 26 / 32: 0.80 / 0.81 / 0.69 against
+                        // 0.63 / 0.65 / 0.60 with 16 points).
+                        // (rows of even length were only measured with eight threads side by side: float64 l_max = 21: 0.92)
+                        const bool narrow = elem == 8 && !even_rows;
+                        const int target = narrow ? 4 : 8;
+                        const double side = lanes == target ? 1.0 : (lanes > target ? 0.8 : std::sqrt(double(lanes) / target));
+                        // (a table batch larger than the panel measured lower: float64 l_max = 26, batches of 16 / 8
+                        // points for panels of 8: 0.59 / 0.81; partly filled warps do not count against a shape here)
+                        const double dealt = double(items) / (double(real_slices) * real_per_slice);
+                        score = side * dealt / real_per_slice * (ctas >= 2 ? 1.0 : 0.7) * (0.85 + 0.05 * std::min<long long>(ctas, 3)) *
+                                (tp >= (narrow ? 8 : 16) ? 1.0 : 0.85) * (batch == tp ? 1.0 : 0.9);
                     }
                     if (score > best_score + 1e-9) {
                         best_score = score;
@@ -443,13 +450,15 @@ PanelPlan make_panel_plan(int l_max, int level, size_t elem, size_t smem_limit, 
     // l_max = 18, 20, 22, float64 l_max = 16 ... 24) the score's choice was the best measured or within 2 % of it; the
     // other degrees were not swept. For Hessians small panels of four, two or one point with about four warps per CTA
     // win: several CTAs per SM hide each other's barriers.
-    if (level >= 1 && best.feasible && k.panel_batch <= 0 && k.panel_points <= 0 && k.panel_threads <= 0 && k.panel_slots <= 0) {
+    // Values only, float32 l_max = 22: 16 points per panel 0.70 against 0.59 with 32.
+    if (best.feasible && k.panel_batch <= 0 && k.panel_points <= 0 && k.panel_threads <= 0 && k.panel_slots <= 0) {
         struct Shape { int level, elem, l_max, batch, tp, threads; };
         static const Shape measured[] = {
             {2, 4, 11, 8, 4, 64},  {2, 4, 12, 8, 4, 128}, {2, 4, 13, 8, 4, 96},  {2, 4, 14, 8, 4, 96},  {2, 4, 15, 8, 4, 128},
             {2, 4, 17, 4, 2, 128}, {2, 4, 18, 4, 2, 128}, {2, 4, 19, 4, 2, 96},  {2, 8, 7, 16, 8, 128}, {2, 8, 13, 8, 2, 128},
             {2, 8, 15, 4, 2, 128}, {2, 8, 16, 4, 2, 128}, {2, 8, 20, 4, 1, 128}, {2, 8, 24, 2, 1, 96},
-            {1, 4, 16, 16, 16, 192}, {1, 4, 21, 8, 4, 96}, {1, 4, 26, 8, 4, 192}, {1, 8, 28, 4, 2, 128}};
+            {1, 4, 16, 16, 16, 192}, {1, 4, 21, 8, 4, 96}, {1, 4, 26, 8, 4, 192}, {1, 8, 28, 4, 2, 128},
+            {0, 4, 22, 16, 16, 48}};
         for (const Shape& m : measured) {
             if (m.level != level || m.l_max != l_max || size_t(m.elem) != elem) continue;
             const size_t smem = panel_fixed_bytes(l_max, level, m.batch, elem) + panel_image_bytes(l_max, level, m.tp, elem);
