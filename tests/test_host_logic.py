@@ -177,3 +177,32 @@ def test_out_buffers_are_validated_before_they_reach_a_kernel():
         check(([1.0], good[1]), xyz, shapes, require_cuda=False)          # not a tensor at all
     with pytest.raises(ValueError, match="xyz_grad"):
         check(torch.empty((5, 4), dtype=torch.float64), xyz, [(5, 3)], names=("xyz_grad",), require_cuda=False)
+
+
+def test_kernel_family_map():
+    """Which kernel family serves which call, asked of the library itself (no launch, no GPU needed): the
+    compile-time tile kernels up to their measured crossovers, the run-time-degree panel kernels above
+    (forward levels and the first-order VJP), the band kernel for the second-order VJP above the tile
+    range and for rows too long for a panel image."""
+    from sphericart_b200 import _c_lib
+
+    def switches(kind, elem, l_top):
+        out, prev = [], None
+        for l_max in range(0, l_top + 1):
+            family = _c_lib.kernel_family(kind, l_max, elem)
+            if family != prev:
+                out.append((l_max, family))
+                prev = family
+        return out
+
+    assert switches(0, 4, 28) == [(0, "sph_tile_kernel"), (21, "sph_panel_kernel")]
+    assert switches(0, 8, 40) == [(0, "sph_tile_kernel"), (21, "sph_panel_kernel")]
+    assert switches(1, 4, 28) == [(0, "sph_tile_kernel"), (10, "sph_panel_kernel")]
+    assert switches(1, 8, 40) == [(0, "sph_tile_kernel"), (9, "sph_panel_kernel"), (37, "sph_band_kernel")]
+    assert switches(2, 4, 28) == [(0, "sph_tile_kernel"), (5, "sph_panel_kernel")]
+    assert switches(2, 8, 40) == [(0, "sph_tile_kernel"), (5, "sph_panel_kernel"), (31, "sph_band_kernel")]
+    assert switches(3, 4, 28) == [(0, "sph_vjp_tile_kernel"), (21, "sph_panel_vjp_kernel")]
+    assert switches(3, 8, 40) == [(0, "sph_vjp_tile_kernel"), (21, "sph_panel_vjp_kernel")]
+    assert switches(4, 4, 28) == [(0, "sph_vjp2_tile_kernel"), (11, "sph_band_kernel")]
+    assert switches(4, 8, 40) == [(0, "sph_vjp2_tile_kernel"), (9, "sph_band_kernel")]
+    assert _c_lib.kernel_family(7, 4, 4) == "" and _c_lib.kernel_family(1, 4, 2) == ""
