@@ -3,8 +3,9 @@
 The reference's ctypes front end loads a single ``libsphericart`` and binds, at load time, the 36
 CPU functions and the 20 CUDA functions of ``sphericart/include/sphericart.h``
 (``python/src/sphericart/_c_lib.py:41-400``). ``oracle/Makefile`` (target ``combined``) links the
-reference's own CPU translation units with this repository's CUDA objects into
-``oracle/_ref/libsphericart_combined.so``; these tests check that the result is what that front
+reference's own CPU translation units into ``oracle/_ref/libsphericart_combined.so`` with this
+repository's CUDA library as its dependency, so that one load handle answers for all 56 functions
+(a maintainer's build links the CUDA objects in directly); these tests check that the result is what that front
 end needs: every symbol binds (through the reference's own ``setup_functions`` where the
 reference checkout is present), the CPU half computes what the reference CPU library computes, and
 the CUDA half - this repository's kernels - answers through the very same library handle.
